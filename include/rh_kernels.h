@@ -1,0 +1,161 @@
+/*
+ * rh_kernels.h — C ABI of librh_kernels.so: B200 (sm_100a) implementations of
+ * runtherder's row-wise decoder-layer kernels.
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless the parameter is documented as host.
+ *    bf16 tensors are passed as void* (16-bit patterns), FP8 E4M3 as uint8_t*.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *  - All work is enqueued on `stream`; no call synchronises, allocates or keeps a
+ *    pointer, so every call may be recorded into a CUDA graph.  positions /
+ *    at_pos / token ids are read on the device at execution time.
+ *  - Row starts must be 16-byte aligned (bf16 row length a multiple of 8).
+ *  - Return value: RH_OK or an rh_status error; rh_last_error_string() gives the
+ *    reason for the last failure on the calling thread.  Nothing is launched
+ *    when an error is returned.  There is no CPU fallback of any kind.
+ *
+ * The reference has no C ABI: its boundary is a set of C++ free functions in
+ * namespace runtherder::kernels.  Each entry point below names the reference
+ * declaration it stands in for (paths relative to the reference's root); the
+ * C++ functions with the reference's exact signatures are exported by the same
+ * library (see rh_dropin.hpp) and forward to these.
+ */
+#ifndef RH_KERNELS_H
+#define RH_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum rh_status {
+    RH_OK = 0,
+    RH_ERR_INVALID_ARG = 1,     /* null pointer, non-positive count, eps <= 0, forbidden aliasing */
+    RH_ERR_UNSUPPORTED_DIM = 2, /* row length not a multiple of 8 / beyond the supported maximum */
+    RH_ERR_MISALIGNED = 3,      /* a pointer is not 16-byte aligned */
+    RH_ERR_LAUNCH = 4,          /* the CUDA runtime rejected the launch */
+    RH_ERR_CUDA = 5             /* another CUDA runtime call failed (host-buffer helpers only) */
+} rh_status;
+
+#define RH_MAX_ROW_DIM 16384 /* longest row of the CTA-per-row kernels (reference: rmsnorm.cu:205-208) */
+#define RH_MAX_HEAD_DIM 256  /* reference: rope.cu:12 */
+
+int rh_version(void);
+const char* rh_status_string(int status);
+const char* rh_last_error_string(void);
+
+/* ---- Drop-in entry points (one per reference kernel) ------------------------------------ */
+
+/* y = (x / rms(x)) * g per row; y may alias x.
+ * Replaces runtherder::kernels::rmsnorm_bf16_forward
+ * (include/runtherder/kernels/rmsnorm.cuh:15-22, src/kernels/rmsnorm.cu:214-224). */
+int rh_rmsnorm_bf16(void* y, const void* x, const void* g, int num_tokens, int hidden_dim, float eps,
+                    void* stream);
+
+/* h_out = bf16(x + residual); y = (h / rms(h)) * g with the unrounded fp32 h.
+ * h_out may alias residual; y must differ from h_out.
+ * Replaces rmsnorm_add_bf16_forward (rmsnorm.cuh:36-45, rmsnorm.cu:226-238). */
+int rh_rmsnorm_add_bf16(void* y, void* h_out, const void* x, const void* residual, const void* g,
+                        int num_tokens, int hidden_dim, float eps, void* stream);
+
+/* Per-token symmetric INT8: x_scale = amax/127, q = clamp(rn(x * (127/amax)), -127, 127);
+ * a zero row gives scale 0 and codes 0.
+ * Replaces quantize_per_token_int8 (include/runtherder/kernels/quantization.cuh:17-22,
+ * src/kernels/quantization.cu:116-149). */
+int rh_quantize_per_token_int8(int8_t* q, float* x_scale, const void* x, int num_tokens, int dim,
+                               void* stream);
+
+/* y[m,n] = bf16(acc * x_scale[row] * w_scale[col]) — the W8A8 GEMM epilogue.
+ * Replaces dequantize_w8a8 (quantization.cuh:31-37, quantization.cu:175-191). */
+int rh_dequantize_w8a8(void* y, const int32_t* acc, const float* x_scale, const void* w_scale, int m,
+                       int n, void* stream);
+
+/* Per-row FP8 E4M3: scale = amax/448, q = e4m3_satfinite(x * (448/amax)), written at
+ * destination row (row + *at_pos * rows_per_pos); *at_pos is read on the device.
+ * Replaces quantize_kv_fp8 (quantization.cuh:50-57, quantization.cu:272-309). */
+int rh_quantize_kv_fp8(uint8_t* q, float* scale, const void* x, const int* at_pos, int rows_per_pos,
+                       int num_rows, int head_dim, void* stream);
+
+/* y = silu(gate) * up over n elements; y may alias gate or up.
+ * Replaces swiglu_bf16_forward (include/runtherder/kernels/activation.cuh:16-21,
+ * src/kernels/activation.cu:45-58).  n is 64-bit here; the C++ shim keeps the int. */
+int rh_swiglu_bf16(void* y, const void* gate, const void* up, long long n, void* stream);
+
+/* In-place rotate-half RoPE on q [T,Hq,D] and k [T,Hkv,D] from a frequency table.
+ * Replaces rope_bf16 (include/runtherder/kernels/rope.cuh:16-25, src/kernels/rope.cu:59-81). */
+int rh_rope_bf16(void* q, void* k, const int* positions, const float* inv_freq, int seq_len,
+                 int num_q_heads, int num_kv_heads, int head_dim, void* stream);
+
+/* out[i,:] = table[ids[i],:].
+ * Replaces embedding_lookup_bf16_forward (include/runtherder/kernels/embedding.cuh:14-20,
+ * src/kernels/embedding.cu:40-54). */
+int rh_embedding_lookup_bf16(void* out, const void* table, const int* token_ids, int num_tokens,
+                             int hidden_dim, void* stream);
+
+/* ---- Fused entry points (new; each equals a chain of the reference's calls) --------------- */
+
+/* [residual add +] RMSNorm + per-token INT8 quantisation in one pass over the row.
+ * Equals rmsnorm_add_bf16_forward (or rmsnorm_bf16_forward when residual == NULL) followed by
+ * quantize_per_token_int8 of the stored bf16 result — the sequence
+ * src/model/supported/llama/llama3.cu:211-226 + src/kernels/matmul.cu:138 issues.
+ * h_out is written only when residual != NULL (may alias residual); y is optional (NULL skips
+ * the bf16 store). */
+int rh_rmsnorm_add_quant_int8(int8_t* q, float* x_scale, void* h_out, void* y_or_null, const void* x,
+                              const void* residual_or_null, const void* g, int num_tokens,
+                              int hidden_dim, float eps, void* stream);
+
+/* SwiGLU + per-token INT8 quantisation of the bf16-rounded product, one pass per row.
+ * Equals swiglu_bf16_forward + quantize_per_token_int8 (llama3.cu:248-251 + matmul.cu:138).
+ * y is optional and may alias gate or up. */
+int rh_swiglu_quant_int8(int8_t* q, float* x_scale, void* y_or_null, const void* gate, const void* up,
+                         int num_tokens, int inter_dim, void* stream);
+
+/* [per-head RMSNorm of q and k] + RoPE + FP8 KV-cache append, one launch.
+ * Equals (qwen3.cu:189-194 when q_norm/k_norm are given) rmsnorm_bf16_forward on q and k rows,
+ * rope_bf16 (llama3.cu:228-230), then KVCache::append = quantize_kv_fp8 of the rotated k and of v
+ * (include/runtherder/engine/kv_cache.h:62-78).  q is rotated in place; the rotated bf16 k is
+ * written to k_out when it is not NULL (k_out may alias k_in).  k_cache/v_cache/k_scale/v_scale are
+ * the layer's slabs ([max_seq, Hkv, D] E4M3 and [max_seq, Hkv] fp32); slot = *at_pos + token.
+ * head_dim must be a multiple of 16. */
+int rh_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v_in,
+                   const void* q_norm_or_null, const void* k_norm_or_null, float eps,
+                   const int* positions, const float* inv_freq, uint8_t* k_cache, float* k_scale,
+                   uint8_t* v_cache, float* v_scale, const int* at_pos, int seq_len, int num_q_heads,
+                   int num_kv_heads, int head_dim, void* stream);
+
+/* ---- Host-side tables (HOST pointers, no GPU involved) ----------------------------------- */
+
+/* out[i] = (float) pow((double)theta, -2i/D), i < D/2.
+ * Replaces rope_inv_freq_plain (src/model/supported/llama/llama.cu:128-143). */
+int rh_rope_inv_freq_plain(float* out_host, int head_dim, float theta_base);
+
+/* Llama-3 long-context rescaling of the plain table.
+ * Replaces rope_inv_freq_llama3 (src/model/supported/llama/llama3.cu:26-60). */
+int rh_rope_inv_freq_llama3(float* out_host, int head_dim, float theta_base, float factor,
+                            float low_freq_factor, float high_freq_factor,
+                            int original_max_position_embeddings);
+
+/* ---- Synthetic benchmark inputs (device generators, counter-based, reproducible) --------- */
+
+/* out[i] = bf16(N(0,1)(start+i) * std * chan_scale[(start+i) % ncols]); chan_scale may be NULL. */
+int rh_synth_normal_bf16(void* out, size_t count, uint64_t seed, uint64_t tensor_id, uint64_t start,
+                         float std, const float* chan_scale, int ncols, void* stream);
+/* out[i] = bf16(U[lo,hi)) */
+int rh_synth_uniform_bf16(void* out, size_t count, uint64_t seed, uint64_t tensor_id, uint64_t start,
+                          float lo, float hi, void* stream);
+/* out[i] = U{0..modulus-1} */
+int rh_synth_ids_i32(int32_t* out, size_t count, uint64_t seed, uint64_t tensor_id, uint64_t start,
+                     int32_t modulus, void* stream);
+
+/* ---- Tuning knobs (process-wide; for experiments, defaults are the tuned values) --------- */
+
+/* key: "rows_ctas_per_sm", "swiglu_ctas_per_sm", "rope_warps_per_cta", ...; value <= 0 restores
+ * the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
+int rh_tune(const char* key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RH_KERNELS_H */

@@ -1,0 +1,326 @@
+// RoPE on Q and K, optionally preceded by Qwen3's per-head RMSNorm and followed by
+// the FP8 E4M3 KV-cache append of the rotated K and of V — one launch for what the
+// reference issues as rmsnorm x2, rope, quantize_kv_fp8 x2.
+//
+// Layout.  A head row of D bf16 values is D/8 vectors; the rotate-half pairs are
+// (i, i+D/2), i.e. vector v of the lower half pairs with vector v + D/16 of the
+// upper half.  D/16 lanes own one head row: lane `sub` holds lower vector `sub` and
+// upper vector `sub + D/16`, so both members of every pair, the head's sum of squares
+// and its amax live inside one lane group and need only shuffles.  A warp carries
+// 32/(D/16) head rows at a time ("a group": 4 rows at D = 128) and walks a chunk of
+// consecutive groups of ONE token, so cos/sin of the token's 8 angles per lane are
+// computed once and reused for every head of the chunk (the reference recomputes
+// them for each of the Hq+Hkv heads).
+//
+// Numerics follow the reference kernels operation for operation:
+//   norm  (src/kernels/rmsnorm.cu:77-135 at hidden_dim = D): per-vector FMA chain, then
+//          the shuffle tree — lower+upper vector first (the tree's offset-D/16 level),
+//          then offsets D/32 ... 1; y = bf16((h*rrms)*g)
+//   rope  (src/kernels/rope.cu:35-54): theta = float(pos)*inv_freq[i]; __sincosf;
+//          bf16(a*c - b*s), bf16(a*s + b*c) on the bf16-rounded inputs
+//   fp8   (src/kernels/quantization.cu:210-250): amax of the bf16 row; scale = amax/448;
+//          e4m3(x * (448/amax)); destination row = token*Hkv + head + at_pos*Hkv
+#include "rh_common.cuh"
+
+namespace rh {
+
+namespace {
+
+struct RopeArgs {
+    void* q;
+    void* k_out;
+    const void* k_in;
+    const void* v_in;
+    const void* q_norm;
+    const void* k_norm;
+    float eps;
+    const int* positions;
+    const float* inv_freq;
+    uint8_t* k_cache;
+    float* k_scale;
+    uint8_t* v_cache;
+    float* v_scale;
+    const int* at_pos;
+    int seq_len;
+    int num_q_heads;
+    int num_kv_heads;
+    int groups_per_item;  // head groups one warp handles for its token
+    int items_per_token;
+};
+
+// The rotation, written as the reference writes it so the compiler makes the same
+// multiply-add contraction choices.
+__device__ __forceinline__ void rotate(float a, float b, float c, float s, float& lo, float& hi) {
+    lo = a * c - b * s;
+    hi = a * s + b * c;
+}
+
+template <int D, bool kNorm, bool kKV>
+__global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
+    constexpr int kLanesPerHead = D / 16;
+    constexpr int kHeadsPerGroup = 32 / kLanesPerHead;
+    constexpr int kVecsPerRow = D / 8;
+
+    const int lane = threadIdx.x & 31;
+    const int sub = lane % kLanesPerHead;
+    const int hslot = lane / kLanesPerHead;
+    const int warps_per_cta = blockDim.x >> 5;
+    const long long item = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
+    const long long num_items = static_cast<long long>(p.seq_len) * p.items_per_token;
+    if (item >= num_items) return;  // whole warps only: shuffles below stay convergent
+
+    const int token = static_cast<int>(item / p.items_per_token);
+    const int chunk = static_cast<int>(item % p.items_per_token);
+    const int Hq = p.num_q_heads, Hkv = p.num_kv_heads;
+    const int rows = Hq + (kKV ? 2 * Hkv : Hkv);
+    const int groups = (rows + kHeadsPerGroup - 1) / kHeadsPerGroup;
+    const int g_begin = chunk * p.groups_per_item;
+    const int g_end = min(groups, g_begin + p.groups_per_item);
+
+    // cos/sin of this lane's eight angles
+    float cs[8], sn[8];
+    {
+        const float pos = static_cast<float>(p.positions[token]);
+        const float4 f0 = __ldg(reinterpret_cast<const float4*>(p.inv_freq) + 2 * sub);
+        const float4 f1 = __ldg(reinterpret_cast<const float4*>(p.inv_freq) + 2 * sub + 1);
+        const float fr[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) __sincosf(pos * fr[j], &sn[j], &cs[j]);
+    }
+    long long slot_base = 0;
+    if constexpr (kKV) slot_base = static_cast<long long>(*p.at_pos) * Hkv;
+
+    // role of head row r: 0 = Q, 1 = K, 2 = V, 3 = none
+    auto row_src = [&](int r, int& role) -> const uint4* {
+        if (r < Hq) {
+            role = 0;
+            return static_cast<const uint4*>(p.q) + (static_cast<size_t>(token) * Hq + r) * kVecsPerRow;
+        }
+        if (r < Hq + Hkv) {
+            role = 1;
+            return static_cast<const uint4*>(p.k_in) + (static_cast<size_t>(token) * Hkv + (r - Hq)) * kVecsPerRow;
+        }
+        if (kKV && r < rows) {
+            role = 2;
+            return static_cast<const uint4*>(p.v_in) + (static_cast<size_t>(token) * Hkv + (r - Hq - Hkv)) * kVecsPerRow;
+        }
+        role = 3;
+        return nullptr;
+    };
+
+    int role_next;
+    const uint4* src_next = row_src(g_begin * kHeadsPerGroup + hslot, role_next);
+    uint4 lo_next = make_uint4(0, 0, 0, 0), hi_next = make_uint4(0, 0, 0, 0);
+    if (role_next != 3) {
+        lo_next = ld_stream(src_next + sub);
+        hi_next = ld_stream(src_next + sub + kLanesPerHead);
+    }
+
+    for (int g = g_begin; g < g_end; ++g) {
+        const int r = g * kHeadsPerGroup + hslot;
+        const int role = role_next;
+        const uint4 lo_v = lo_next, hi_v = hi_next;
+        if (g + 1 < g_end) {  // prefetch the next group's rows while this one is processed
+            src_next = row_src(r + kHeadsPerGroup, role_next);
+            if (role_next != 3) {
+                lo_next = ld_stream(src_next + sub);
+                hi_next = ld_stream(src_next + sub + kLanesPerHead);
+            }
+        }
+
+        float a[8], b[8];
+        unpack8(lo_v, a);
+        unpack8(hi_v, b);
+
+        if constexpr (kNorm) {
+            // every lane runs the shuffles; only Q and K rows keep the result
+            float ss_lo = 0.0f, ss_hi = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss_lo = __fmaf_rn(a[j], a[j], ss_lo);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss_hi = __fmaf_rn(b[j], b[j], ss_hi);
+            const float total = group_sum<kLanesPerHead>(ss_lo + ss_hi);
+            const float rrms = rsqrtf(total / static_cast<float>(D) + p.eps);
+            if (role <= 1) {
+                const uint4* w = static_cast<const uint4*>(role == 0 ? p.q_norm : p.k_norm);
+                float gl[8], gh[8];
+                unpack8(ld_weight(w + sub), gl);
+                unpack8(ld_weight(w + sub + kLanesPerHead), gh);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    a[j] = round_bf16(a[j] * rrms * gl[j]);
+                    b[j] = round_bf16(b[j] * rrms * gh[j]);
+                }
+            }
+        }
+
+        uint4 out_lo = lo_v, out_hi = hi_v;
+        if (role <= 1) {
+            float ol[8], oh[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) rotate(a[j], b[j], cs[j], sn[j], ol[j], oh[j]);
+            out_lo = pack8(ol);
+            out_hi = pack8(oh);
+        }
+        if (role == 0 || (role == 1 && p.k_out != nullptr)) {
+            uint4* dst = (role == 0)
+                             ? static_cast<uint4*>(p.q) + (static_cast<size_t>(token) * Hq + r) * kVecsPerRow
+                             : static_cast<uint4*>(p.k_out) + (static_cast<size_t>(token) * Hkv + (r - Hq)) * kVecsPerRow;
+            st_vec(dst + sub, out_lo);
+            st_vec(dst + sub + kLanesPerHead, out_hi);
+        }
+
+        if constexpr (kKV) {
+            float fl[8], fh[8];
+            unpack8(out_lo, fl);
+            unpack8(out_hi, fh);
+            float amax = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fmaxf(fabsf(fl[j]), fabsf(fh[j])));
+            amax = group_max<kLanesPerHead>(amax);
+            const float inv = (amax > 0.0f) ? (448.0f / amax) : 0.0f;
+            if (role == 1 || role == 2) {
+                const int kv_head = (role == 1) ? (r - Hq) : (r - Hq - Hkv);
+                const long long dst_row = static_cast<long long>(token) * Hkv + kv_head + slot_base;
+                uint8_t* cache = (role == 1) ? p.k_cache : p.v_cache;
+                float* scale = (role == 1) ? p.k_scale : p.v_scale;
+                if (sub == 0) scale[dst_row] = amax / 448.0f;
+                uint2* c = reinterpret_cast<uint2*>(cache + static_cast<size_t>(dst_row) * D);
+                st_vec8(c + sub, pack_e4m3x8(fl, inv));
+                st_vec8(c + sub + kLanesPerHead, pack_e4m3x8(fh, inv));
+            }
+        }
+    }
+}
+
+// Any even head_dim <= 256 that is not a multiple of 16: one thread per rotation pair.
+__global__ void rope_generic_kernel(__nv_bfloat16* q, __nv_bfloat16* k, const int* positions,
+                                    const float* inv_freq, long long total_pairs, int num_q_heads,
+                                    int num_kv_heads, int head_dim) {
+    const int half = head_dim >> 1;
+    const int heads = num_q_heads + num_kv_heads;
+    for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_pairs;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int i = static_cast<int>(idx % half);
+        const long long th = idx / half;
+        const int head = static_cast<int>(th % heads);
+        const long long token = th / heads;
+        float s, c;
+        __sincosf(static_cast<float>(positions[token]) * inv_freq[i], &s, &c);
+        __nv_bfloat16* row = (head < num_q_heads)
+                                 ? q + (token * num_q_heads + head) * head_dim
+                                 : k + (token * num_kv_heads + (head - num_q_heads)) * head_dim;
+        const float a = __bfloat162float(row[i]);
+        const float b = __bfloat162float(row[i + half]);
+        float lo, hi;
+        rotate(a, b, c, s, lo, hi);
+        row[i] = __float2bfloat16(lo);
+        row[i + half] = __float2bfloat16(hi);
+    }
+}
+
+template <int D>
+int launch_rope(RopeArgs p, bool norm, bool kv, cudaStream_t stream) {
+    constexpr int kHeadsPerGroup = 32 / (D / 16);
+    const int rows = p.num_q_heads + (kv ? 2 : 1) * p.num_kv_heads;
+    const int groups = (rows + kHeadsPerGroup - 1) / kHeadsPerGroup;
+    // Enough warps to fill the machine first; beyond that, fewer and longer warps so the
+    // cos/sin of a token are shared by more of its heads.
+    const long long target_items = static_cast<long long>(host::num_sms()) * 32;
+    long long gpi = (static_cast<long long>(p.seq_len) * groups) / target_items;
+    if (gpi < 1) gpi = 1;
+    if (gpi > groups) gpi = groups;
+    p.groups_per_item = static_cast<int>(gpi);
+    p.items_per_token = (groups + p.groups_per_item - 1) / p.groups_per_item;
+    const long long items = static_cast<long long>(p.seq_len) * p.items_per_token;
+    int warps = host::tuning(host::kRopeWarpsPerCta);
+    if (warps <= 0) warps = 4;
+    if (warps > 8) warps = 8;
+    const long long grid = (items + warps - 1) / warps;
+    RH_REQUIRE(grid <= 0x7fffffffLL, RH_ERR_UNSUPPORTED_DIM, "rope: too many rows for one launch");
+    const unsigned g = static_cast<unsigned>(grid), b = static_cast<unsigned>(warps * 32);
+    if (kv) {
+        if (norm) rope_kv_kernel<D, true, true><<<g, b, 0, stream>>>(p);
+        else rope_kv_kernel<D, false, true><<<g, b, 0, stream>>>(p);
+    } else {
+        if (norm) rope_kv_kernel<D, true, false><<<g, b, 0, stream>>>(p);
+        else rope_kv_kernel<D, false, false><<<g, b, 0, stream>>>(p);
+    }
+    return host::check_launch("rope_kv_kernel");
+}
+
+int dispatch_rope(const RopeArgs& p, int head_dim, bool norm, bool kv, cudaStream_t stream) {
+    switch (head_dim) {
+        case 16: return launch_rope<16>(p, norm, kv, stream);
+        case 32: return launch_rope<32>(p, norm, kv, stream);
+        case 64: return launch_rope<64>(p, norm, kv, stream);
+        case 128: return launch_rope<128>(p, norm, kv, stream);
+        case 256: return launch_rope<256>(p, norm, kv, stream);
+        default: return -1;
+    }
+}
+
+int check_rope(const char* who, int seq_len, int hq, int hkv, int d) {
+    RH_REQUIRE(seq_len >= 1, RH_ERR_INVALID_ARG, "%s: seq_len must be >= 1", who);
+    RH_REQUIRE(hq >= 1, RH_ERR_INVALID_ARG, "%s: num_q_heads must be >= 1", who);
+    RH_REQUIRE(hkv >= 1, RH_ERR_INVALID_ARG, "%s: num_kv_heads must be >= 1", who);
+    RH_REQUIRE(d >= 2, RH_ERR_UNSUPPORTED_DIM, "%s: head_dim must be >= 2", who);
+    RH_REQUIRE(d % 2 == 0, RH_ERR_UNSUPPORTED_DIM, "%s: head_dim must be even", who);
+    RH_REQUIRE(d <= RH_MAX_HEAD_DIM, RH_ERR_UNSUPPORTED_DIM, "%s: head_dim exceeds %d", who, RH_MAX_HEAD_DIM);
+    return RH_OK;
+}
+
+}  // namespace
+
+}  // namespace rh
+
+using namespace rh;
+
+extern "C" int rh_rope_bf16(void* q, void* k, const int* positions, const float* inv_freq, int seq_len,
+                            int num_q_heads, int num_kv_heads, int head_dim, void* stream) {
+    if (int e = check_rope("rh_rope_bf16", seq_len, num_q_heads, num_kv_heads, head_dim)) return e;
+    RH_REQUIRE(q && k && positions && inv_freq, RH_ERR_INVALID_ARG, "rh_rope_bf16: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool fast = (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+                      host::aligned16(q) && host::aligned16(k) && host::aligned16(inv_freq);
+    if (fast) {
+        RopeArgs p{};
+        p.q = q; p.k_out = k; p.k_in = k; p.positions = positions; p.inv_freq = inv_freq;
+        p.seq_len = seq_len; p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads;
+        return dispatch_rope(p, head_dim, false, false, s);
+    }
+    const long long pairs = static_cast<long long>(seq_len) * (num_q_heads + num_kv_heads) * (head_dim / 2);
+    long long grid = (pairs + 255) / 256;
+    const long long cap = static_cast<long long>(host::num_sms()) * 16;
+    if (grid > cap) grid = cap;
+    rope_generic_kernel<<<static_cast<unsigned>(grid), 256, 0, s>>>(
+        static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), positions, inv_freq, pairs,
+        num_q_heads, num_kv_heads, head_dim);
+    return host::check_launch("rope_generic_kernel");
+}
+
+extern "C" int rh_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v_in,
+                              const void* q_norm_or_null, const void* k_norm_or_null, float eps,
+                              const int* positions, const float* inv_freq, uint8_t* k_cache,
+                              float* k_scale, uint8_t* v_cache, float* v_scale, const int* at_pos,
+                              int seq_len, int num_q_heads, int num_kv_heads, int head_dim,
+                              void* stream) {
+    if (int e = check_rope("rh_rope_kv_fp8", seq_len, num_q_heads, num_kv_heads, head_dim)) return e;
+    RH_REQUIRE(q && k_in && v_in && positions && inv_freq && k_cache && k_scale && v_cache && v_scale,
+               RH_ERR_INVALID_ARG, "rh_rope_kv_fp8: null pointer");
+    RH_REQUIRE(at_pos != nullptr, RH_ERR_INVALID_ARG, "rh_rope_kv_fp8: at_pos must not be null");
+    const bool norm = q_norm_or_null != nullptr || k_norm_or_null != nullptr;
+    RH_REQUIRE(!norm || (q_norm_or_null && k_norm_or_null), RH_ERR_INVALID_ARG,
+               "rh_rope_kv_fp8: q_norm and k_norm must be given together");
+    RH_REQUIRE(!norm || eps > 0.0f, RH_ERR_INVALID_ARG, "rh_rope_kv_fp8: eps must be > 0");
+    RH_REQUIRE(head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256,
+               RH_ERR_UNSUPPORTED_DIM, "rh_rope_kv_fp8: head_dim must be 16, 32, 64, 128 or 256 (got %d)", head_dim);
+    RH_REQUIRE(host::aligned16(q) && host::aligned16(k_out_or_null) && host::aligned16(k_in) &&
+                   host::aligned16(v_in) && host::aligned16(q_norm_or_null) && host::aligned16(k_norm_or_null) &&
+                   host::aligned16(inv_freq) && (reinterpret_cast<uintptr_t>(k_cache) & 7u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(v_cache) & 7u) == 0,
+               RH_ERR_MISALIGNED, "rh_rope_kv_fp8: pointers must be 16-byte aligned (caches: 8)");
+    RopeArgs p{q, k_out_or_null, k_in, v_in, q_norm_or_null, k_norm_or_null, eps, positions, inv_freq,
+               k_cache, k_scale, v_cache, v_scale, at_pos, seq_len, num_q_heads, num_kv_heads, 0, 0};
+    return dispatch_rope(p, head_dim, norm, true, static_cast<cudaStream_t>(stream));
+}

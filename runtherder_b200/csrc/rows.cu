@@ -1,0 +1,384 @@
+// CTA-per-row kernels: [residual add +] RMSNorm [+ per-token INT8 quantisation],
+// stand-alone per-token INT8 quantisation, and per-row FP8 quantisation of long rows.
+//
+// Layout.  A row of `dim` bf16 values is `dim/8` 128-bit vectors.  A CTA of 256
+// threads owns one row at a time; thread t holds vectors t, t+256, ... (at most
+// eight) in registers, so the row is read from HBM exactly once and every output
+// (h_out, y, codes, scale) is produced from that single read.  The grid is sized
+// to the machine and each CTA walks rows blockIdx.x, blockIdx.x+gridDim.x, ...,
+// keeping the norm gains in registers across rows.
+//
+// Numerics.  The sum of squares follows the reference kernel's fp32 order exactly
+// (src/kernels/rmsnorm.cu:77-113: per-thread fused multiply-add chain over its
+// vectors in order, shuffle tree per warp, then the same tree over the eight warp
+// partials), so rrms — and with it every bf16 output and every INT8 code — is
+// bit-identical to the reference's CUDA kernel.  amax reductions are exact in any
+// order.
+#include "rh_common.cuh"
+
+namespace rh {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+constexpr int kRowWarps = kRowThreads / 32;
+
+enum : unsigned {
+    kFNorm = 1u,    // RMS-normalise (else the row is quantised as it is)
+    kFAdd = 2u,     // h = x + residual, h_out written
+    kFStoreY = 4u,  // write the bf16 normalised row
+    kFInt8 = 8u,    // write INT8 codes + amax/127
+    kFFp8 = 16u,    // write E4M3 codes + amax/448 at the at_pos-relative destination row
+};
+
+struct RowArgs {
+    void* y;
+    void* h_out;
+    const void* x;
+    const void* residual;
+    const void* g;
+    void* codes;
+    float* scale;
+    const int* at_pos;
+    int rows_per_pos;
+    long long num_rows;
+    int dim;
+    float eps;
+};
+
+template <int VPT, unsigned F>
+__global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
+    constexpr bool kNorm = (F & kFNorm) != 0, kAdd = (F & kFAdd) != 0, kStoreY = (F & kFStoreY) != 0;
+    constexpr bool kInt8 = (F & kFInt8) != 0, kFp8 = (F & kFFp8) != 0, kQuant = kInt8 || kFp8;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_vecs = a.dim / kVec;
+
+    __shared__ float s_ss[2][kRowWarps];
+    __shared__ float s_mx[2][kRowWarps];
+
+    uint4 gw[VPT];
+    if constexpr (kNorm) {
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            const int i = tid + s * kRowThreads;
+            if (i < n_vecs) gw[s] = ld_weight(static_cast<const uint4*>(a.g) + i);
+        }
+    }
+    const float dim_f = static_cast<float>(a.dim);
+    long long slot_base = 0;
+    if constexpr (kFp8) slot_base = static_cast<long long>(*a.at_pos) * a.rows_per_pos;
+
+    int parity = 0;
+    for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
+        const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(n_vecs);
+        const uint4* x_row = static_cast<const uint4*>(a.x) + row_off;
+
+        uint4 xv[VPT], rv[VPT];
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            const int i = tid + s * kRowThreads;
+            if (i < n_vecs) {
+                xv[s] = ld_stream(x_row + i);
+                if constexpr (kAdd) rv[s] = ld_stream(static_cast<const uint4*>(a.residual) + row_off + i);
+            }
+        }
+
+        uint32_t yw[VPT][4];  // the row as the next kernel would read it back: packed bf16
+
+        if constexpr (kNorm) {
+            float h[VPT][8];
+            float ss = 0.0f;
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                const int i = tid + s * kRowThreads;
+                if (i < n_vecs) {
+                    unpack8(xv[s], h[s]);
+                    if constexpr (kAdd) {
+                        float r[8];
+                        unpack8(rv[s], r);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) h[s][j] += r[j];
+                        st_vec(static_cast<uint4*>(a.h_out) + row_off + i, pack8(h[s]));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss = __fmaf_rn(h[s][j], h[s][j], ss);
+                }
+            }
+            ss = group_sum<32>(ss);
+            if (lane == 0) s_ss[parity][warp] = ss;
+            __syncthreads();
+            const float total = group_sum<kRowWarps>(s_ss[parity][lane & (kRowWarps - 1)]);
+            const float rrms = rsqrtf(total / dim_f + a.eps);
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                const int i = tid + s * kRowThreads;
+                if (i < n_vecs) {
+                    float g[8], yf[8];
+                    unpack8(gw[s], g);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) yf[j] = h[s][j] * rrms * g[j];
+                    const uint4 p = pack8(yf);
+                    yw[s][0] = p.x; yw[s][1] = p.y; yw[s][2] = p.z; yw[s][3] = p.w;
+                    if constexpr (kStoreY) st_vec(static_cast<uint4*>(a.y) + row_off + i, p);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                yw[s][0] = xv[s].x; yw[s][1] = xv[s].y; yw[s][2] = xv[s].z; yw[s][3] = xv[s].w;
+            }
+        }
+
+        if constexpr (kQuant) {
+            // Row amax of the bf16 values.  The packed NaN-propagating max tells, for free,
+            // whether this thread holds a non-finite value; the reference's fmaxf skips NaN.
+            uint32_t m2 = 0u;
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                const int i = tid + s * kRowThreads;
+                if (i < n_vecs) {
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s][w]));
+                }
+            }
+            const float m_lo = bf_lo(m2), m_hi = bf_hi(m2);
+            const bool finite = (m_lo <= 3.0e38f) && (m_hi <= 3.0e38f);  // false for Inf and NaN
+            float amax = fmaxf(m_lo, m_hi);
+            if (!finite) {
+                amax = 0.0f;
+#pragma unroll
+                for (int s = 0; s < VPT; ++s) {
+                    const int i = tid + s * kRowThreads;
+                    if (i < n_vecs) {
+#pragma unroll
+                        for (int w = 0; w < 4; ++w)
+                            amax = fmaxf(amax, fmaxf(fabsf(bf_lo(yw[s][w])), fabsf(bf_hi(yw[s][w]))));
+                    }
+                }
+            }
+            amax = group_max<32>(amax);
+            if (lane == 0) s_mx[parity][warp] = amax;
+            __syncthreads();
+            amax = group_max<kRowWarps>(s_mx[parity][lane & (kRowWarps - 1)]);
+
+            constexpr float kQMax = kInt8 ? 127.0f : 448.0f;
+            const float inv = (amax > 0.0f) ? (kQMax / amax) : 0.0f;
+            const long long dst_row = row + slot_base;
+            if (tid == 0) a.scale[dst_row] = amax / kQMax;
+            uint2* c_row = static_cast<uint2*>(a.codes) + static_cast<size_t>(dst_row) * n_vecs;
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                const int i = tid + s * kRowThreads;
+                if (i < n_vecs) {
+                    if (kInt8 && finite && inv <= 3.0e38f) {  // an overflowed inverse (subnormal amax) takes the exact path
+                        st_vec8(c_row + i, pack_int8x8_fast(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), inv));
+                    } else {
+                        float yf[8];
+                        unpack8(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), yf);
+                        st_vec8(c_row + i, kInt8 ? pack_int8x8(yf, inv) : pack_e4m3x8(yf, inv));
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Short rows (dim <= 256): kLanes = next power of two >= dim/8 lanes own one row, one
+// vector each, so a warp carries 32/kLanes rows and no lane idles.  The reference
+// runs these with one 256-thread CTA per row (16 threads busy at dim 128); its
+// summation tree over the first kLanes lanes is what group_sum<kLanes> reproduces.
+template <int kLanes, unsigned F>
+__global__ void __launch_bounds__(kRowThreads) short_rows_kernel(const RowArgs a) {
+    constexpr bool kNorm = (F & kFNorm) != 0, kAdd = (F & kFAdd) != 0, kStoreY = (F & kFStoreY) != 0;
+    constexpr bool kInt8 = (F & kFInt8) != 0, kFp8 = (F & kFFp8) != 0, kQuant = kInt8 || kFp8;
+    constexpr int kRowsPerCta = kRowThreads / kLanes;
+
+    const int n_vecs = a.dim / kVec;
+    const int sub = threadIdx.x % kLanes;
+    const bool active = sub < n_vecs;
+    const float dim_f = static_cast<float>(a.dim);
+
+    uint4 gw = make_uint4(0, 0, 0, 0);
+    if (kNorm && active) gw = ld_weight(static_cast<const uint4*>(a.g) + sub);
+    long long slot_base = 0;
+    if constexpr (kFp8) slot_base = static_cast<long long>(*a.at_pos) * a.rows_per_pos;
+
+    const long long stride = static_cast<long long>(gridDim.x) * kRowsPerCta;
+    // All lanes of a warp run the same number of iterations (shuffles need the full warp).
+    const long long first = static_cast<long long>(blockIdx.x) * kRowsPerCta;
+    for (long long base = first; base < a.num_rows; base += stride) {
+        const long long row = base + threadIdx.x / kLanes;
+        const bool live = active && row < a.num_rows;
+        const size_t off = static_cast<size_t>(row) * n_vecs + sub;
+
+        uint4 xv = make_uint4(0, 0, 0, 0), rv = make_uint4(0, 0, 0, 0);
+        if (live) {
+            xv = ld_stream(static_cast<const uint4*>(a.x) + off);
+            if constexpr (kAdd) rv = ld_stream(static_cast<const uint4*>(a.residual) + off);
+        }
+
+        uint4 yv = xv;
+        if constexpr (kNorm) {
+            float h[8], g[8], yf[8];
+            unpack8(xv, h);
+            if constexpr (kAdd) {
+                float r[8];
+                unpack8(rv, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[j] += r[j];
+                if (live) st_vec(static_cast<uint4*>(a.h_out) + off, pack8(h));
+            }
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss = __fmaf_rn(h[j], h[j], ss);
+            const float total = group_sum<kLanes>(ss);
+            const float rrms = rsqrtf(total / dim_f + a.eps);
+            unpack8(gw, g);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) yf[j] = h[j] * rrms * g[j];
+            yv = pack8(yf);
+            if (kStoreY && live) st_vec(static_cast<uint4*>(a.y) + off, yv);
+        }
+        if constexpr (kQuant) {
+            float yf[8];
+            unpack8(yv, yf);
+            float amax = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(yf[j]));
+            amax = group_max<kLanes>(amax);
+            constexpr float kQMax = kInt8 ? 127.0f : 448.0f;
+            const float inv = (amax > 0.0f) ? (kQMax / amax) : 0.0f;
+            const long long dst_row = row + slot_base;
+            if (live) {
+                if (sub == 0) a.scale[dst_row] = amax / kQMax;
+                st_vec8(static_cast<uint2*>(a.codes) + static_cast<size_t>(dst_row) * n_vecs + sub,
+                        kInt8 ? pack_int8x8(yf, inv) : pack_e4m3x8(yf, inv));
+            }
+        }
+    }
+}
+
+// Grid = resident CTAs of this instantiation on the whole device (queried once), so each
+// CTA keeps its gains in registers and walks its share of the rows.
+template <int VPT, unsigned F>
+void launch_long(const RowArgs& a, cudaStream_t stream) {
+    static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F>), kRowThreads);
+    const int tuned = host::tuning(host::kRowsCtasPerSm);
+    const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
+    const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
+    rows_kernel<VPT, F><<<grid, kRowThreads, 0, stream>>>(a);
+}
+
+template <unsigned F>
+int launch_rows(const RowArgs& a, cudaStream_t stream) {
+    const int n_vecs = a.dim / kVec;
+    if (n_vecs <= 32) {
+        int lanes = 1;
+        while (lanes < n_vecs) lanes <<= 1;
+        const long long rows_per_cta = kRowThreads / lanes;
+        const long long want = (a.num_rows + rows_per_cta - 1) / rows_per_cta;
+        const long long cap = static_cast<long long>(host::num_sms()) * 8;
+        const int grid = static_cast<int>(want < cap ? want : cap);
+        switch (lanes) {
+            case 1: short_rows_kernel<1, F><<<grid, kRowThreads, 0, stream>>>(a); break;
+            case 2: short_rows_kernel<2, F><<<grid, kRowThreads, 0, stream>>>(a); break;
+            case 4: short_rows_kernel<4, F><<<grid, kRowThreads, 0, stream>>>(a); break;
+            case 8: short_rows_kernel<8, F><<<grid, kRowThreads, 0, stream>>>(a); break;
+            case 16: short_rows_kernel<16, F><<<grid, kRowThreads, 0, stream>>>(a); break;
+            default: short_rows_kernel<32, F><<<grid, kRowThreads, 0, stream>>>(a); break;
+        }
+        return host::check_launch("short_rows_kernel");
+    }
+    const int vpt = (n_vecs + kRowThreads - 1) / kRowThreads;
+    if (vpt <= 1) launch_long<1, F>(a, stream);
+    else if (vpt <= 2) launch_long<2, F>(a, stream);
+    else if (vpt <= 4) launch_long<4, F>(a, stream);
+    else launch_long<8, F>(a, stream);
+    return host::check_launch("rows_kernel");
+}
+
+int check_rows(const char* who, long long num_rows, int dim) {
+    RH_REQUIRE(num_rows >= 1, RH_ERR_INVALID_ARG, "%s: row count must be >= 1 (got %lld)", who, num_rows);
+    RH_REQUIRE(dim >= kVec, RH_ERR_UNSUPPORTED_DIM, "%s: row length must be >= 8 (got %d)", who, dim);
+    RH_REQUIRE(dim % kVec == 0, RH_ERR_UNSUPPORTED_DIM, "%s: row length must be divisible by 8 (got %d)", who, dim);
+    RH_REQUIRE(dim <= RH_MAX_ROW_DIM, RH_ERR_UNSUPPORTED_DIM, "%s: row length %d exceeds %d", who, dim,
+               RH_MAX_ROW_DIM);
+    return RH_OK;
+}
+
+}  // namespace
+
+}  // namespace rh
+
+using namespace rh;
+
+extern "C" int rh_rmsnorm_bf16(void* y, const void* x, const void* g, int num_tokens, int hidden_dim,
+                               float eps, void* stream) {
+    if (int e = check_rows("rh_rmsnorm_bf16", num_tokens, hidden_dim)) return e;
+    RH_REQUIRE(y && x && g, RH_ERR_INVALID_ARG, "rh_rmsnorm_bf16: null pointer");
+    RH_REQUIRE(eps > 0.0f, RH_ERR_INVALID_ARG, "rh_rmsnorm_bf16: eps must be > 0");
+    RH_REQUIRE(host::aligned16(y) && host::aligned16(x) && host::aligned16(g), RH_ERR_MISALIGNED,
+               "rh_rmsnorm_bf16: pointers must be 16-byte aligned");
+    RowArgs a{y, nullptr, x, nullptr, g, nullptr, nullptr, nullptr, 0, num_tokens, hidden_dim, eps};
+    return launch_rows<kFNorm | kFStoreY>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rh_rmsnorm_add_bf16(void* y, void* h_out, const void* x, const void* residual,
+                                   const void* g, int num_tokens, int hidden_dim, float eps,
+                                   void* stream) {
+    if (int e = check_rows("rh_rmsnorm_add_bf16", num_tokens, hidden_dim)) return e;
+    RH_REQUIRE(y && h_out && x && residual && g, RH_ERR_INVALID_ARG, "rh_rmsnorm_add_bf16: null pointer");
+    RH_REQUIRE(eps > 0.0f, RH_ERR_INVALID_ARG, "rh_rmsnorm_add_bf16: eps must be > 0");
+    RH_REQUIRE(y != h_out, RH_ERR_INVALID_ARG, "rh_rmsnorm_add_bf16: y and h_out must be distinct buffers");
+    RH_REQUIRE(host::aligned16(y) && host::aligned16(h_out) && host::aligned16(x) &&
+                   host::aligned16(residual) && host::aligned16(g),
+               RH_ERR_MISALIGNED, "rh_rmsnorm_add_bf16: pointers must be 16-byte aligned");
+    RowArgs a{y, h_out, x, residual, g, nullptr, nullptr, nullptr, 0, num_tokens, hidden_dim, eps};
+    return launch_rows<kFNorm | kFAdd | kFStoreY>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rh_quantize_per_token_int8(int8_t* q, float* x_scale, const void* x, int num_tokens,
+                                          int dim, void* stream) {
+    if (int e = check_rows("rh_quantize_per_token_int8", num_tokens, dim)) return e;
+    RH_REQUIRE(q && x_scale && x, RH_ERR_INVALID_ARG, "rh_quantize_per_token_int8: null pointer");
+    RH_REQUIRE(host::aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, RH_ERR_MISALIGNED,
+               "rh_quantize_per_token_int8: x must be 16-byte and q 8-byte aligned");
+    RowArgs a{nullptr, nullptr, x, nullptr, nullptr, q, x_scale, nullptr, 0, num_tokens, dim, 0.0f};
+    return launch_rows<kFInt8>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rh_quantize_kv_fp8(uint8_t* q, float* scale, const void* x, const int* at_pos,
+                                  int rows_per_pos, int num_rows, int head_dim, void* stream) {
+    if (int e = check_rows("rh_quantize_kv_fp8", num_rows, head_dim)) return e;
+    RH_REQUIRE(q && scale && x, RH_ERR_INVALID_ARG, "rh_quantize_kv_fp8: null pointer");
+    RH_REQUIRE(at_pos != nullptr, RH_ERR_INVALID_ARG, "rh_quantize_kv_fp8: at_pos must not be null");
+    RH_REQUIRE(rows_per_pos >= 1, RH_ERR_INVALID_ARG, "rh_quantize_kv_fp8: rows_per_pos must be >= 1");
+    RH_REQUIRE(host::aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, RH_ERR_MISALIGNED,
+               "rh_quantize_kv_fp8: x must be 16-byte and q 8-byte aligned");
+    RowArgs a{nullptr, nullptr, x, nullptr, nullptr, q, scale, at_pos, rows_per_pos, num_rows, head_dim, 0.0f};
+    return launch_rows<kFFp8>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rh_rmsnorm_add_quant_int8(int8_t* q, float* x_scale, void* h_out, void* y_or_null,
+                                         const void* x, const void* residual_or_null, const void* g,
+                                         int num_tokens, int hidden_dim, float eps, void* stream) {
+    if (int e = check_rows("rh_rmsnorm_add_quant_int8", num_tokens, hidden_dim)) return e;
+    RH_REQUIRE(q && x_scale && x && g, RH_ERR_INVALID_ARG, "rh_rmsnorm_add_quant_int8: null pointer");
+    RH_REQUIRE(eps > 0.0f, RH_ERR_INVALID_ARG, "rh_rmsnorm_add_quant_int8: eps must be > 0");
+    RH_REQUIRE(residual_or_null == nullptr || h_out != nullptr, RH_ERR_INVALID_ARG,
+               "rh_rmsnorm_add_quant_int8: h_out is required when a residual is given");
+    RH_REQUIRE(y_or_null == nullptr || y_or_null != h_out, RH_ERR_INVALID_ARG,
+               "rh_rmsnorm_add_quant_int8: y and h_out must be distinct buffers");
+    RH_REQUIRE(host::aligned16(x) && host::aligned16(g) && host::aligned16(h_out) &&
+                   host::aligned16(y_or_null) && host::aligned16(residual_or_null) &&
+                   (reinterpret_cast<uintptr_t>(q) & 7u) == 0,
+               RH_ERR_MISALIGNED, "rh_rmsnorm_add_quant_int8: pointers must be 16-byte aligned (q: 8)");
+    RowArgs a{y_or_null, h_out, x, residual_or_null, g, q, x_scale, nullptr, 0, num_tokens, hidden_dim, eps};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (residual_or_null) {
+        return y_or_null ? launch_rows<kFNorm | kFAdd | kFStoreY | kFInt8>(a, s)
+                         : launch_rows<kFNorm | kFAdd | kFInt8>(a, s);
+    }
+    return y_or_null ? launch_rows<kFNorm | kFStoreY | kFInt8>(a, s) : launch_rows<kFNorm | kFInt8>(a, s);
+}
