@@ -1,0 +1,456 @@
+#!/usr/bin/env python
+"""Benchmark of the fused row-wise layer ops on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (default N=1)
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU implementation
+
+Workload (config.workload): the Llama-3.1-8B-shaped throughput sweep — T=65536 token rows, hidden 4096,
+32 Q / 8 KV heads x 128, intermediate 14336, vocab 128256, seed 1.  A step is one pass of its four ops
+over the batch, one launch each: embedding gather, residual add + RMSNorm + INT8 quantisation, llama3
+RoPE + FP8 KV append, SwiGLU + INT8 quantisation.  With N GPUs the rows are split into N contiguous
+blocks (strong scaling, no collective on the data path).
+
+value  = algorithmic HBM bytes of a step / device time of the step, whole job (GB/s), inputs resident.
+e2e    = the same bytes / wall time of a step driven from pinned HOST buffers (H2D + kernels + D2H).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "fused-layer-op HBM GB/s"
+FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    p.add_argument("--config", default="c4")
+    p.add_argument("--rows", type=int, default=0, help="override the row count (smaller captures)")
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-cpu", action="store_true")
+    p.add_argument("--no-refcuda", action="store_true")
+    p.add_argument("--cpu-seconds", type=float, default=15.0)
+    return p.parse_args()
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def step_bytes_per_row(cfg):
+    ops = [("embedding", cfg.bytes_embedding()), ("norm_quant", cfg.bytes_norm_quant()),
+           ("rope_kv", cfg.bytes_rope_kv()), ("swiglu_quant", cfg.bytes_swiglu_quant())]
+    return ops, sum(b for _, b in ops)
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks: sampled through NVML (read-only) while the timed region runs
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+        self.period = period_s
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's host implementation (its test helpers, compiled unmodified) where it
+# has one, the oracle port for the pieces it lacks (INT8 quantisation, gather); rows over all cores.
+# ------------------------------------------------------------------------------------------------
+def cpu_rows_per_second(cfg, total_rows: int, threads: int):
+    """Runs the four ops of a step on `total_rows` synthetic rows on the host; returns (seconds, kind)."""
+    import numpy as np
+    sys.path.insert(0, str(ROOT / "tests"))
+    from oracle_lib import Oracle, load_ref_host, ptr
+    from runtherder_b200 import synth
+    from runtherder_b200.rope_tables import inv_freq_for
+
+    orc = Oracle()
+    ref = load_ref_host()
+    H, I, D, Hq, Hkv = cfg.hidden, cfg.inter, cfg.head_dim, cfg.q_heads, cfg.kv_heads
+    s = cfg.seed
+    g = orc.synth_uniform(H, s, synth.T_G_ATTN, 0.5, 1.5)
+    table_rows = 4096                                     # a window of the table: the gather cost is per row
+    table = orc.synth_normal(table_rows * H, s, synth.T_TABLE, 0, 0.02).reshape(table_rows, H)
+    cs = synth.outlier_channel_scale(H, s, synth.T_X)
+
+    def work(block):
+        b, e = block
+        n = e - b
+        x = orc.synth_normal(n * H, s, synth.T_X, b * H, 1.0, cs, H).reshape(n, H)
+        r = orc.synth_normal(n * H, s, synth.T_RES, b * H, 1.0, cs, H).reshape(n, H)
+        q = orc.synth_normal(n * Hq * D, s, synth.T_Q, b * Hq * D).reshape(n, Hq, D)
+        k = orc.synth_normal(n * Hkv * D, s, synth.T_K, b * Hkv * D).reshape(n, Hkv, D)
+        v = orc.synth_normal(n * Hkv * D, s, synth.T_V, b * Hkv * D).reshape(n * Hkv, D)
+        gate = orc.synth_normal(n * I, s, synth.T_GATE, b * I).reshape(n, I)
+        up = orc.synth_normal(n * I, s, synth.T_UP, b * I).reshape(n, I)
+        ids = (orc.synth_ids(n, s, synth.T_IDS, cfg.vocab, b) % table_rows).astype(np.int32)
+        t0 = time.perf_counter()
+        orc.embedding(table, ids)
+        if ref is not None:
+            y, h = np.empty_like(x), np.empty_like(x)
+            ref.refhost_rmsnorm_add(ptr(y), ptr(h), ptr(x), ptr(r), ptr(g), n, H, cfg.eps)
+        else:
+            y, h = orc.rmsnorm_add(x, r, g, cfg.eps)
+        orc.quant_int8(y)
+        if ref is not None:   # the reference's host RoPE takes theta and a start position (plain table)
+            ref.refhost_rope(ptr(q), cfg.start_pos + b, n, Hq, D, cfg.rope_theta)
+            ref.refhost_rope(ptr(k), cfg.start_pos + b, n, Hkv, D, cfg.rope_theta)
+            kq, ks = np.empty(n * Hkv * D, np.uint8), np.empty(n * Hkv, np.float32)
+            ref.refhost_quantize_kv(ptr(kq), ptr(ks), ptr(k), n * Hkv, D)
+            ref.refhost_quantize_kv(ptr(kq), ptr(ks), ptr(v), n * Hkv, D)
+            act = np.empty_like(gate)
+            ref.refhost_swiglu(ptr(act), ptr(gate), ptr(up), n * I)
+        else:
+            pos = np.arange(cfg.start_pos + b, cfg.start_pos + e, dtype=np.int32)
+            inv = inv_freq_for(cfg)
+            orc.rope_table(q, pos, inv)
+            k = orc.rope_table(k, pos, inv)
+            orc.quant_kv(k.reshape(n * Hkv, D))
+            orc.quant_kv(v)
+            act = orc.swiglu(gate, up)
+        orc.quant_int8(act)
+        return time.perf_counter() - t0
+
+    per = max(1, total_rows // threads)
+    blocks = [(b, min(total_rows, b + per)) for b in range(0, total_rows, per)]
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        busy = list(pool.map(work, blocks))
+    wall = time.perf_counter() - t0
+    # input generation is not part of the measured work: scale the wall time by the busy share
+    gen_overhead = max(0.0, wall - max(busy))
+    return max(busy), ("reference" if ref is not None else "port"), gen_overhead
+
+
+def cpu_baseline(cfg, seconds: float):
+    threads = os.cpu_count() or 1
+    probe_rows = 4 * threads
+    t, kind, _ = cpu_rows_per_second(cfg, probe_rows, threads)
+    rate = probe_rows / max(t, 1e-9)
+    rows = int(min(max(rate * seconds, 8 * threads), 65536))
+    rows -= rows % threads
+    t, kind, _ = cpu_rows_per_second(cfg, rows, threads)
+    _, per_row = step_bytes_per_row(cfg)
+    return {"value": rows * per_row / t / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+            "rows_per_s": rows / t,
+            "sample": f"{rows} of {cfg.tokens} token rows of the same four ops, row-parallel over {threads} host "
+                      f"threads; {'reference test helpers (double precision) for norm, RoPE, FP8 KV, SwiGLU; ' if kind == 'reference' else ''}"
+                      f"oracle port for INT8 quantisation and the gather (the reference has no host code for them)"}
+
+
+def run_reference_arm(args, cfg):
+    """The reference's own CPU implementation of the path, timed in K bounded steps on this host."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    _, per_row = step_bytes_per_row(cfg)
+    budget = 90.0
+    probe_rows = 4 * threads
+    t, kind, _ = cpu_rows_per_second(cfg, probe_rows, threads)
+    rate = probe_rows / max(t, 1e-9)
+    rows = int(min(max(rate * budget / (args.steps + args.warmup), 2 * threads), 16384))
+    rows -= rows % threads
+    for _ in range(args.warmup):
+        cpu_rows_per_second(cfg, rows, threads)
+    total = 0.0
+    for _ in range(args.steps):
+        t, kind, _ = cpu_rows_per_second(cfg, rows, threads)
+        total += t
+    ms = total / args.steps * 1e3
+    value = rows * per_row / (total / args.steps) / 1e9
+    sample = (f"each step = {rows} of {cfg.tokens} token rows through the four ops on {threads} host threads "
+              f"(reference test helpers where the reference has host code, oracle port for INT8 quantisation and gather)")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in / int8+fp8 out (fp64 host arithmetic)",
+            "data": "synthetic", "token_rows_per_s": rows / (total / args.steps),
+            "config": {"workload": cfg.name, "rows_per_step": rows},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    from runtherder_b200.configs import CONFIGS
+    cfg = CONFIGS[args.config]
+    if args.rows:
+        cfg = cfg.with_tokens(args.rows)
+    if args.impl == "reference":
+        run_reference_arm(args, cfg)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from runtherder_b200 import host_path, layer_ops, synth
+    from runtherder_b200.sharding import shard_bounds
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    T = cfg.tokens
+    b, e = shard_bounds(T, world, rank)
+    rows = e - b
+    ops, per_row = step_bytes_per_row(cfg)
+    ins = synth.make_inputs(cfg, rows=rows, row_offset=b, device=dev)
+    outs = layer_ops.alloc_outputs(cfg, rows, device=dev, slots=rows)
+    torch.cuda.synchronize()
+
+    def step():
+        return host_path.sweep_step(cfg, ins, outs)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    # ---- timed region: K steps, an event after every launch so each kernel's duration is known ----
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
+    launches = 0
+    from runtherder_b200 import kernels as Kn
+    H = cfg.hidden
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        for s in range(K):
+            ev[s][0].record()
+            Kn.embedding_lookup_bf16_forward(outs["emb"], ins["table"], ins["ids"], rows, H)
+            ev[s][1].record()
+            Kn.rmsnorm_add_quant_int8(outs["q_attn_in"], outs["s_attn_in"], outs["h_attn"], None, ins["x"],
+                                      ins["residual"], ins["g_attn"], rows, H, cfg.eps)
+            ev[s][2].record()
+            Kn.rope_kv_fp8(ins["q"], None, ins["k"], ins["v"], None, None, cfg.eps, ins["positions"], ins["inv_freq"],
+                           outs["k_cache"], outs["k_scale"], outs["v_cache"], outs["v_scale"], outs["at_pos"], rows,
+                           cfg.q_heads, cfg.kv_heads, cfg.head_dim)
+            ev[s][3].record()
+            Kn.swiglu_quant_int8(outs["q_mlp"], outs["s_mlp"], None, ins["gate"], ins["up"], rows, cfg.inter)
+            ev[s][4].record()
+            launches += 4
+        torch.cuda.synchronize()
+    elapsed_ms = ev[0][0].elapsed_time(ev[K - 1][4])
+    barrier()
+    elapsed_ms = max_over_ranks(elapsed_ms)
+    op_ms = [statistics.mean(ev[s][j].elapsed_time(ev[s][j + 1]) for s in range(K)) for j in range(4)]
+    op_ms = [max_over_ranks(m) for m in op_ms]
+
+    peak, peak_kind = measured_peak()
+    ms_per_step = elapsed_ms / K
+    total_bytes = T * per_row
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+    op_table = {}
+    for (name, bpr), ms in zip(ops, op_ms):
+        # per-GPU figures: this rank's rows / its kernel time (max over ranks)
+        gbs = rows * bpr / (ms * 1e-3) / 1e9
+        op_table[name] = {"ms": round(ms, 4), "gbs_per_gpu": round(gbs, 1), "frac_of_" + peak_kind: round(gbs / peak, 4),
+                          "frac_of_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 4), "bytes_per_row": bpr}
+    dom = max(range(4), key=lambda j: op_ms[j])
+    dom_name, dom_bpr = ops[dom]
+    achieved = rows * dom_bpr / (op_ms[dom] * 1e-3) / 1e9
+    traffic_file = ROOT / "profiles" / "dram_traffic.json"
+    traffic = None
+    if traffic_file.exists():
+        try:
+            per_row_traffic = json.loads(traffic_file.read_text()).get(dom_name, {}).get("dram_bytes_per_row")
+            traffic = None if per_row_traffic is None else per_row_traffic * rows
+        except Exception:
+            traffic = None
+    roofline = {"bound": "hbm", "kernel": dom_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": traffic,
+                "algorithmic_bytes_per_launch": rows * dom_bpr}
+
+    line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in, fp32 math, int8/fp8-e4m3 out",
+            "data": "synthetic", "token_rows_per_s": round(T / (ms_per_step * 1e-3), 1),
+            "frac_of_hbm_peak": {peak_kind: round(value / (peak * world), 4),
+                                 "nominal_8TBs": round(value / (NOMINAL_HBM_GBS * world), 4)},
+            "config": {"workload": cfg.name, "token_rows": T, "rows_per_gpu": rows, "hidden": cfg.hidden,
+                       "inter": cfg.inter, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
+                       "vocab": cfg.vocab, "seed": cfg.seed, "ops_per_step": [n for n, _ in ops],
+                       "algorithmic_bytes_per_row": per_row, "parallelism": f"rows/{world}",
+                       "l2": "every op streams more than the 126 MB L2 per launch (inputs larger than L2)"},
+            "ops": op_table, "roofline": roofline, "gpu_launches": launches, "clocks": clocks.summary()}
+
+    # ---- the reference's own CUDA kernels on the same buffers (rank 0, N=1) ----
+    if world == 1 and not args.no_refcuda:
+        try:
+            line["ref_cuda"] = time_reference_cuda(cfg, ins, outs, rows, per_row, max(3, min(K, 20)))
+        except Exception as exc:  # library absent: report, do not fail the bench
+            line["ref_cuda"] = {"unavailable": str(exc)[:200]}
+
+    # ---- end to end from pinned host buffers ----
+    if not args.no_e2e:
+        line["e2e"] = time_end_to_end(cfg, ins, rows, total_bytes, world, barrier, max_over_ranks,
+                                      steps=max(3, min(K, 8)), dev=dev)
+
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(cfg, args.cpu_seconds)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def time_reference_cuda(cfg, ins, outs, rows, per_row, reps):
+    """The reference's kernels (sm_100a build) for the same four ops, as its layer code issues them:
+    gather; rmsnorm_add then quantize_per_token_int8 once per consumer GEMM (x3 for q/k/v); rope then two
+    quantize_kv_fp8; swiglu then quantize_per_token_int8.  Also timed with the repeated quantisation
+    issued once ("dedup")."""
+    import torch
+    sys.path.insert(0, str(ROOT / "tests"))
+    from gpu_util import RefCuda
+    ref = RefCuda()
+    T, H, I = rows, cfg.hidden, cfg.inter
+    normed = torch.empty_like(ins["x"])
+    act = torch.empty_like(ins["gate"])
+
+    def seq(n_quant):
+        ref.embedding_lookup_bf16_forward(outs["emb"], ins["table"], ins["ids"], T, H)
+        ref.rmsnorm_add_bf16_forward(normed, outs["h_attn"], ins["x"], ins["residual"], ins["g_attn"], T, H, cfg.eps)
+        for _ in range(n_quant):
+            ref.quantize_per_token_int8(outs["q_attn_in"], outs["s_attn_in"], normed, T, H)
+        ref.rope_bf16(ins["q"], ins["k"], ins["positions"], ins["inv_freq"], T, cfg.q_heads, cfg.kv_heads, cfg.head_dim)
+        ref.quantize_kv_fp8(outs["k_cache"], outs["k_scale"], ins["k"], outs["at_pos"], cfg.kv_heads, T * cfg.kv_heads, cfg.head_dim)
+        ref.quantize_kv_fp8(outs["v_cache"], outs["v_scale"], ins["v"], outs["at_pos"], cfg.kv_heads, T * cfg.kv_heads, cfg.head_dim)
+        ref.swiglu_bf16_forward(act, ins["gate"], ins["up"], T * I)
+        ref.quantize_per_token_int8(outs["q_mlp"], outs["s_mlp"], act, T, I)
+        return 7 + n_quant
+
+    k_backup = ins["k"].clone()
+    out = {}
+    for label, nq in (("as_issued", 3), ("dedup", 1)):
+        for _ in range(3):
+            n = seq(nq)
+        torch.cuda.synchronize()
+        a, bb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            seq(nq)
+        bb.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(bb) / reps
+        out[label] = {"ms_per_step": round(ms, 4), "launches_per_step": n,
+                      "value": round(rows * per_row / (ms * 1e-3) / 1e9, 1), "unit": "GB/s (same algorithmic bytes)"}
+    ins["k"].copy_(k_backup)
+    out["what"] = "reference src/kernels/*.cu compiled for sm_100a, same device buffers, same process"
+    return out
+
+
+def time_end_to_end(cfg, ins, rows, total_bytes, world, barrier, max_over_ranks, steps, dev):
+    import torch
+    from runtherder_b200 import host_path
+    weights = {k: ins[k] for k in ("g_attn", "inv_freq", "table")}
+    host_in = {k: ins[k].to("cpu").pin_memory() for k in host_path.INPUTS_INT8}
+    runner = host_path.HostSweep(cfg, rows, weights, chunk_rows=4096, n_streams=3, device=dev)
+    host_out = runner.alloc_host_outputs()
+    h2d, d2h = runner.bytes_per_step(host_in, host_out)
+    for _ in range(2):
+        runner.run(host_in, host_out)
+    barrier()
+    t0 = time.perf_counter()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    n = 0
+    for _ in range(steps):
+        n += runner.run(host_in, host_out)
+    b.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    ms = max_over_ranks(max(a.elapsed_time(b), wall * 1e3)) / steps
+    barrier()
+    return {"value": round(total_bytes / (ms * 1e-3) / 1e9, 2), "unit": "GB/s", "ms_per_step": round(ms, 3),
+            "steps": steps, "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+            "launches_per_step": n // steps,
+            "what": "pinned host inputs -> H2D -> four fused kernels -> D2H of every output, 4096-row chunks over 3 streams"}
+
+
+if __name__ == "__main__":
+    main()

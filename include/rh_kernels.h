@@ -149,9 +149,19 @@ int rh_synth_uniform_bf16(void* out, size_t count, uint64_t seed, uint64_t tenso
 int rh_synth_ids_i32(int32_t* out, size_t count, uint64_t seed, uint64_t tensor_id, uint64_t start,
                      int32_t modulus, void* stream);
 
+/* ---- Self-check ------------------------------------------------------------------------------ */
+
+/* The kernels replace three IEEE divisions of the reference (amax/qmax, qmax/amax, 1/(1+e)) by
+ * refined reciprocals.  This runs, on the current device, an exhaustive comparison of those sequences
+ * with IEEE division over every operand they can meet and writes mismatch counts to
+ * mismatches_host[0..7] (HOST pointer): [0] sigmoid reciprocal with one refinement step (the default), [1] with two, [2],[3] 127/amax and 448/amax, [4],[5] amax/127 and amax/448, [6],[7] unused.
+ * Everything the library uses by default must read 0.  Diagnostic: allocates, synchronises. */
+int rh_selftest(unsigned int* mismatches_host);
+
 /* ---- Tuning knobs (process-wide; for experiments, defaults are the tuned values) --------- */
 
-/* key: "rows_ctas_per_sm", "swiglu_ctas_per_sm", "rope_warps_per_cta", ...; value <= 0 restores
+/* key: "rows_ctas_per_sm", "swiglu_ctas_per_sm", "rope_warps_per_cta", "embed_ctas_per_sm",
+ * "swiglu_threads" (256|512), "swiglu_rcp_steps" (1|2|3 = IEEE division); value <= 0 restores
  * the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
 int rh_tune(const char* key, int value);
 

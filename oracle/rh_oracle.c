@@ -142,6 +142,18 @@ ORC_API void orc_rmsnorm_add(uint16_t* y, uint16_t* h_out, const uint16_t* x,
 /* amax starts at 0; x_scale = amax/127; inv = amax>0 ? 127/amax : 0;        */
 /* q = clamp(round_half_even(x*inv), -127, 127).  All IEEE fp32.             */
 /* ------------------------------------------------------------------------ */
+/* clamp(__float2int_rn(p), -127, 127).  The device conversion rounds half to even, maps NaN to 0
+ * and saturates out-of-range values (so +-Inf end at +-127 after the clamp). */
+static inline int int8_code(float p) {
+    if (isnan(p)) return 0;
+    if (p >= 127.5f) return 127;
+    if (p <= -127.5f) return -127;
+    long qi = lrintf(p);                 /* default mode: ties to even */
+    if (qi > 127) qi = 127;
+    if (qi < -127) qi = -127;
+    return (int)qi;
+}
+
 ORC_API void orc_quantize_per_token_int8(int8_t* q, float* x_scale, const uint16_t* x,
                                          long num_tokens, int dim) {
     for (long row = 0; row < num_tokens; ++row) {
@@ -152,11 +164,7 @@ ORC_API void orc_quantize_per_token_int8(int8_t* q, float* x_scale, const uint16
         x_scale[row] = amax / 127.0f;
         float inv = (amax > 0.0f) ? (127.0f / amax) : 0.0f;
         for (int j = 0; j < dim; ++j) {
-            float p = orc_bf16_to_f32(xr[j]) * inv;
-            long qi = lrintf(p);                 /* default mode: ties to even, as __float2int_rn */
-            if (qi > 127) qi = 127;
-            if (qi < -127) qi = -127;
-            qr[j] = (int8_t)qi;
+            qr[j] = (int8_t)int8_code(orc_bf16_to_f32(xr[j]) * inv);
         }
     }
 }

@@ -55,7 +55,46 @@ int tuning(int slot) { return g_tuning[slot].load(std::memory_order_relaxed); }
 
 }  // namespace rh::host
 
+namespace rh {
+namespace {
+
+// Exhaustive check of the division-free sequences in rh_common.cuh against IEEE division, over every
+// operand they can meet: all 65536 bf16 gate values for the sigmoid reciprocal, all non-NaN
+// non-negative bf16 values for the quantisation scale and inverse scale.
+__global__ void selftest_kernel(unsigned int* mismatches) {
+    const unsigned int bits = blockIdx.x * blockDim.x + threadIdx.x;   // 0 .. 65535
+    const float g = __uint_as_float(bits << 16);
+    if (g >= kGateExactBelow) {   // the range the kernels send down the refined-reciprocal path (NaN excluded)
+        const unsigned int want = __float_as_uint(sigmoid_reference(g));
+        if (__float_as_uint(sigmoid2<1>(splat2(g)).x) != want) atomicAdd(&mismatches[0], 1u);
+        if (__float_as_uint(sigmoid2<2>(splat2(g)).y) != want) atomicAdd(&mismatches[1], 1u);
+    }
+    if (bits <= 0x7f80u) {                                             // +0 .. +Inf
+        const float amax = g;
+        const float inv127 = (amax > 0.0f) ? (127.0f / amax) : 0.0f, inv448 = (amax > 0.0f) ? (448.0f / amax) : 0.0f;
+        if (__float_as_uint(quant_inv_scale<127>(amax)) != __float_as_uint(inv127)) atomicAdd(&mismatches[2], 1u);
+        if (__float_as_uint(quant_inv_scale<448>(amax)) != __float_as_uint(inv448)) atomicAdd(&mismatches[3], 1u);
+        if (__float_as_uint(quant_scale<127>(amax)) != __float_as_uint(amax / 127.0f)) atomicAdd(&mismatches[4], 1u);
+        if (__float_as_uint(quant_scale<448>(amax)) != __float_as_uint(amax / 448.0f)) atomicAdd(&mismatches[5], 1u);
+    }
+}
+
+}  // namespace
+}  // namespace rh
+
 using namespace rh;
+
+extern "C" int rh_selftest(unsigned int* mismatches_host) {
+    RH_REQUIRE(mismatches_host != nullptr, RH_ERR_INVALID_ARG, "rh_selftest: null pointer");
+    unsigned int* dev = nullptr;
+    if (cudaMalloc(&dev, 8 * sizeof(unsigned int)) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selftest: cudaMalloc failed");
+    cudaMemset(dev, 0, 8 * sizeof(unsigned int));
+    selftest_kernel<<<256, 256>>>(dev);
+    const cudaError_t err = cudaMemcpy(mismatches_host, dev, 8 * sizeof(unsigned int), cudaMemcpyDeviceToHost);
+    cudaFree(dev);
+    if (err != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selftest: %s", cudaGetErrorString(err));
+    return RH_OK;
+}
 
 extern "C" int rh_version(void) { return 100; }
 
@@ -76,7 +115,8 @@ extern "C" const char* rh_last_error_string(void) { return host::g_last_error; }
 extern "C" int rh_tune(const char* key, int value) {
     static const char* const kNames[host::kTuneSlots] = {"rows_ctas_per_sm", "swiglu_ctas_per_sm",
                                                          "rope_warps_per_cta", "embed_ctas_per_sm",
-                                                         "elem_ctas_per_sm"};
+                                                         "elem_ctas_per_sm", "swiglu_threads",
+                                                         "swiglu_rcp_steps"};
     RH_REQUIRE(key != nullptr, RH_ERR_INVALID_ARG, "rh_tune: null key");
     for (int i = 0; i < host::kTuneSlots; ++i) {
         if (std::strcmp(key, kNames[i]) == 0) {

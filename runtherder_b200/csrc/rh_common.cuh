@@ -53,6 +53,37 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
 }
 
+// Blackwell issues two independent IEEE fp32 operations per instruction on a register pair
+// (FMUL2 / FADD2 / FFMA2); each half rounds exactly like the scalar instruction, so results do
+// not change — only the number of issue slots does.  A packed bf16 word maps onto one pair.
+// They are issued through PTX with an explicit .rn.  Beware: a paired multiply feeding a paired add
+// is merged into a paired fused multiply-add regardless (intrinsics and PTX alike), so no code here
+// lets a mul2_rn result flow straight into an add2_rn where the double rounding matters.
+__device__ __forceinline__ unsigned long long f2_bits(float2 v) {
+    return (static_cast<unsigned long long>(__float_as_uint(v.y)) << 32) | __float_as_uint(v.x);
+}
+__device__ __forceinline__ float2 bits_f2(unsigned long long b) {
+    return make_float2(__uint_as_float(static_cast<uint32_t>(b)), __uint_as_float(static_cast<uint32_t>(b >> 32)));
+}
+__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+    return bits_f2(d);
+}
+__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+    return bits_f2(d);
+}
+__device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)), "l"(f2_bits(c)));
+    return bits_f2(d);
+}
+__device__ __forceinline__ float2 bf2_to_f2(uint32_t w) { return make_float2(bf_lo(w), bf_hi(w)); }
+__device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
+__device__ __forceinline__ float2 neg2(float2 v) { return make_float2(-v.x, -v.y); }
+
 // Round-to-nearest-even fp32 -> bf16 of two values, packed (lo in bits 0..15).
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -94,16 +125,21 @@ __device__ __forceinline__ uint32_t max_nan_bf16x2(uint32_t a, uint32_t b) {
 // INT8 code of p = y*inv without the conversion unit: adding 1.5*2^23 leaves
 // round_half_even(p) in the low mantissa byte (two's complement).  |p| <= 127.0001 for a
 // finite row, so the reference's clamp never engages; valid only for finite p.
-__device__ __forceinline__ uint32_t int8_code_fast(float y, float inv) {
-    return __float_as_uint(__fadd_rn(__fmul_rn(y, inv), 12582912.0f));
+// The product is a paired multiply, the additions are scalar: a paired add directly behind a paired
+// multiply gets merged into a paired fused multiply-add even with explicit .rn on both, and the
+// single rounding then breaks exact .5 ties (y = amax/2 gives 63.5 -> must round to 64, not 63).
+__device__ __forceinline__ float2 int8_code_fast2(uint32_t w, float2 inv2) {
+    const float2 p = mul2_rn(bf2_to_f2(w), inv2);
+    return make_float2(__fadd_rn(p.x, 12582912.0f), __fadd_rn(p.y, 12582912.0f));
 }
 __device__ __forceinline__ uint2 pack_int8x8_fast(const uint4& w, float inv) {
-    const uint32_t c0 = int8_code_fast(bf_lo(w.x), inv), c1 = int8_code_fast(bf_hi(w.x), inv);
-    const uint32_t c2 = int8_code_fast(bf_lo(w.y), inv), c3 = int8_code_fast(bf_hi(w.y), inv);
-    const uint32_t c4 = int8_code_fast(bf_lo(w.z), inv), c5 = int8_code_fast(bf_hi(w.z), inv);
-    const uint32_t c6 = int8_code_fast(bf_lo(w.w), inv), c7 = int8_code_fast(bf_hi(w.w), inv);
-    const uint32_t lo = __byte_perm(__byte_perm(c0, c1, 0x0040), __byte_perm(c2, c3, 0x0040), 0x5410);
-    const uint32_t hi = __byte_perm(__byte_perm(c4, c5, 0x0040), __byte_perm(c6, c7, 0x0040), 0x5410);
+    const float2 inv2 = splat2(inv);
+    const float2 c0 = int8_code_fast2(w.x, inv2), c1 = int8_code_fast2(w.y, inv2);
+    const float2 c2 = int8_code_fast2(w.z, inv2), c3 = int8_code_fast2(w.w, inv2);
+    const uint32_t lo = __byte_perm(__byte_perm(__float_as_uint(c0.x), __float_as_uint(c0.y), 0x0040),
+                                    __byte_perm(__float_as_uint(c1.x), __float_as_uint(c1.y), 0x0040), 0x5410);
+    const uint32_t hi = __byte_perm(__byte_perm(__float_as_uint(c2.x), __float_as_uint(c2.y), 0x0040),
+                                    __byte_perm(__float_as_uint(c3.x), __float_as_uint(c3.y), 0x0040), 0x5410);
     return make_uint2(lo, hi);
 }
 
@@ -121,6 +157,60 @@ __device__ __forceinline__ uint2 pack_e4m3x8(const float (&y)[8], float inv) {
     return make_uint2(w[0], w[1]);
 }
 
+// ---- correctly rounded divisions without the division subroutine ------------------------------
+//
+// The reference computes scale = amax / qmax and inv = qmax / amax with IEEE division, and the
+// sigmoid as 1.0f / (1.0f + e).  nvcc's division is a reciprocal approximation, refinement steps,
+// a range check and a branch to a slow path.  The sequences below give the same correctly rounded
+// results for the operand ranges that occur (amax is a bf16 value, qmax is 127 or 448; d = 1 + e >= 1)
+// — rh_selftest() proves it exhaustively on the device it runs on — and fall back to `/` outside.
+
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+// a / b from an approximate reciprocal r of b: quotient, exact remainder, correction (twice).
+__device__ __forceinline__ float div_refine(float a, float b, float r) {
+    float q = a * r;
+    q = __fmaf_rn(__fmaf_rn(-b, q, a), r, q);
+    q = __fmaf_rn(__fmaf_rn(-b, q, a), r, q);
+    return q;
+}
+template <int kQMax>
+__device__ __forceinline__ float quant_inv_scale(float amax) {   // kQMax / amax, 0 for a zero row
+    constexpr float qmax = static_cast<float>(kQMax);
+    if (amax >= 1.0e-30f && amax <= 1.0e30f) return div_refine(qmax, amax, rcp_approx(amax));
+    return (amax > 0.0f) ? (qmax / amax) : 0.0f;
+}
+template <int kQMax>
+__device__ __forceinline__ float quant_scale(float amax) {       // amax / kQMax
+    constexpr float qmax = static_cast<float>(kQMax);
+    if (amax >= 1.0e-30f && amax <= 1.0e30f) return div_refine(amax, qmax, 1.0f / qmax);
+    return amax / qmax;
+}
+// sigmoid of two gates, s = 1 / (1 + e), e = __expf(-g) = ex2.approx.ftz(-g * log2(e)), with the
+// reciprocal refined kSteps times.  Valid for g >= kGateExactBelow (1 + e stays far below the range
+// where its reciprocal turns subnormal); callers send smaller gates down the IEEE-division path.
+constexpr float kGateExactBelow = -85.0f;
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+template <int kSteps>
+__device__ __forceinline__ float2 sigmoid2(float2 g) {
+    const float2 t = mul2_rn(g, splat2(-1.4426950408889634f));
+    const float2 d = add2_rn(make_float2(ex2_approx(t.x), ex2_approx(t.y)), splat2(1.0f));
+    const float2 nd = neg2(d);
+    float2 r = make_float2(rcp_approx(d.x), rcp_approx(d.y));
+    r = fma2_rn(r, fma2_rn(nd, r, splat2(1.0f)), r);
+    if (kSteps >= 2) r = fma2_rn(fma2_rn(nd, r, splat2(1.0f)), r, r);
+    return r;
+}
+// The reference's expression, verbatim (src/kernels/activation.cu:36).
+__device__ __forceinline__ float sigmoid_reference(float g) { return 1.0f / (1.0f + __expf(-g)); }
+
 // ---- reductions ----------------------------------------------------------------------------
 //
 // The sum-of-squares must reproduce the reference kernel's fp32 summation tree
@@ -134,6 +224,11 @@ __device__ __forceinline__ float group_sum(float v) {
 #pragma unroll
     for (int o = kLanes / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
+}
+// Max of non-negative, non-NaN floats over the warp: their bit patterns order like unsigned
+// integers, so one integer warp reduction replaces the five-step shuffle tree.
+__device__ __forceinline__ float warp_max_nonneg(float v) {
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
 }
 template <int kLanes>
 __device__ __forceinline__ float group_max(float v) {
@@ -156,7 +251,8 @@ int resident_ctas(const void* kernel, int threads, size_t dyn_smem = 0);  // CTA
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kTuneSlots };
+enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kSwigluThreads,
+                kSwigluRcpSteps, kTuneSlots };
 
 }  // namespace rh::host
 

@@ -48,11 +48,15 @@ struct RopeArgs {
     int items_per_token;
 };
 
-// The rotation, written as the reference writes it so the compiler makes the same
-// multiply-add contraction choices.
+// The rotation.  The reference writes `a*c - b*s` and `a*s + b*c` (src/kernels/rope.cu:53-54) and
+// nvcc contracts each into one product plus a fused multiply-add on the FIRST product; the
+// contraction is spelled out here because it is part of the result's bits and the compiler picks
+// a different one when the expression is inlined into a larger body.
 __device__ __forceinline__ void rotate(float a, float b, float c, float s, float& lo, float& hi) {
-    lo = a * c - b * s;
-    hi = a * s + b * c;
+    const float2 t = mul2_rn(splat2(b), make_float2(s, c));                    // {b*s, b*c}
+    const float2 r = fma2_rn(splat2(a), make_float2(c, s), make_float2(-t.x, t.y));
+    lo = r.x;
+    hi = r.y;
 }
 
 template <int D, bool kNorm, bool kKV>

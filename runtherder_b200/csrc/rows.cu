@@ -66,6 +66,8 @@ __global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
         }
     }
     const float dim_f = static_cast<float>(a.dim);
+    const bool dim_pow2 = (a.dim & (a.dim - 1)) == 0;  // then ss/dim is an exact scaling
+    const float inv_dim = 1.0f / dim_f;
     long long slot_base = 0;
     if constexpr (kFp8) slot_base = static_cast<long long>(*a.at_pos) * a.rows_per_pos;
 
@@ -93,13 +95,18 @@ __global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
             for (int s = 0; s < VPT; ++s) {
                 const int i = tid + s * kRowThreads;
                 if (i < n_vecs) {
-                    unpack8(xv[s], h[s]);
                     if constexpr (kAdd) {
-                        float r[8];
-                        unpack8(rv[s], r);
+                        const uint32_t xw[4] = {xv[s].x, xv[s].y, xv[s].z, xv[s].w};
+                        const uint32_t rw[4] = {rv[s].x, rv[s].y, rv[s].z, rv[s].w};
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) h[s][j] += r[j];
+                        for (int k = 0; k < 4; ++k) {
+                            const float2 hh = add2_rn(bf2_to_f2(xw[k]), bf2_to_f2(rw[k]));
+                            h[s][2 * k] = hh.x;
+                            h[s][2 * k + 1] = hh.y;
+                        }
                         st_vec(static_cast<uint4*>(a.h_out) + row_off + i, pack8(h[s]));
+                    } else {
+                        unpack8(xv[s], h[s]);
                     }
 #pragma unroll
                     for (int j = 0; j < 8; ++j) ss = __fmaf_rn(h[s][j], h[s][j], ss);
@@ -109,18 +116,20 @@ __global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
             if (lane == 0) s_ss[parity][warp] = ss;
             __syncthreads();
             const float total = group_sum<kRowWarps>(s_ss[parity][lane & (kRowWarps - 1)]);
-            const float rrms = rsqrtf(total / dim_f + a.eps);
+            const float rrms = rsqrtf((dim_pow2 ? total * inv_dim : total / dim_f) + a.eps);
 #pragma unroll
             for (int s = 0; s < VPT; ++s) {
                 const int i = tid + s * kRowThreads;
                 if (i < n_vecs) {
-                    float g[8], yf[8];
-                    unpack8(gw[s], g);
+                    const uint32_t gws[4] = {gw[s].x, gw[s].y, gw[s].z, gw[s].w};
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) yf[j] = h[s][j] * rrms * g[j];
-                    const uint4 p = pack8(yf);
-                    yw[s][0] = p.x; yw[s][1] = p.y; yw[s][2] = p.z; yw[s][3] = p.w;
-                    if constexpr (kStoreY) st_vec(static_cast<uint4*>(a.y) + row_off + i, p);
+                    for (int k = 0; k < 4; ++k) {   // y = (h * rrms) * g, two elements per instruction
+                        const float2 t = mul2_rn(make_float2(h[s][2 * k], h[s][2 * k + 1]), splat2(rrms));
+                        const float2 yf = mul2_rn(t, bf2_to_f2(gws[k]));
+                        yw[s][k] = pack_bf16x2(yf.x, yf.y);
+                    }
+                    if constexpr (kStoreY)
+                        st_vec(static_cast<uint4*>(a.y) + row_off + i, make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]));
                 }
             }
         } else {
@@ -157,15 +166,15 @@ __global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
                     }
                 }
             }
-            amax = group_max<32>(amax);
+            amax = warp_max_nonneg(amax);
             if (lane == 0) s_mx[parity][warp] = amax;
             __syncthreads();
-            amax = group_max<kRowWarps>(s_mx[parity][lane & (kRowWarps - 1)]);
+            amax = warp_max_nonneg(s_mx[parity][lane & (kRowWarps - 1)]);
 
-            constexpr float kQMax = kInt8 ? 127.0f : 448.0f;
-            const float inv = (amax > 0.0f) ? (kQMax / amax) : 0.0f;
+            constexpr int kQMax = kInt8 ? 127 : 448;
+            const float inv = quant_inv_scale<kQMax>(amax);
             const long long dst_row = row + slot_base;
-            if (tid == 0) a.scale[dst_row] = amax / kQMax;
+            if (tid == 0) a.scale[dst_row] = quant_scale<kQMax>(amax);
             uint2* c_row = static_cast<uint2*>(a.codes) + static_cast<size_t>(dst_row) * n_vecs;
 #pragma unroll
             for (int s = 0; s < VPT; ++s) {

@@ -12,18 +12,37 @@ namespace rh {
 
 namespace {
 
-__device__ __forceinline__ float silu_mul(float g, float u) {
-    const float s = 1.0f / (1.0f + __expf(-g));
-    return g * s * u;
-}
-
+// Eight products y = bf16((g * s) * u).  kSteps = 0 evaluates the reference's expression verbatim;
+// kSteps = 1, 2 use the refined reciprocal on register pairs, and drop to the verbatim expression
+// for a vector holding a gate below kGateExactBelow (never the case for real activations).
+template <int kSteps>
 __device__ __forceinline__ uint4 swiglu8(const uint4& gv, const uint4& uv) {
-    float g[8], u[8], y[8];
-    unpack8(gv, g);
-    unpack8(uv, u);
+    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t out[4];
+    bool exact = (kSteps == 0);
+    if (kSteps != 0) {
+        const __nv_bfloat162 m = __hmin2(__hmin2(*reinterpret_cast<const __nv_bfloat162*>(&gw[0]),
+                                                 *reinterpret_cast<const __nv_bfloat162*>(&gw[1])),
+                                         __hmin2(*reinterpret_cast<const __nv_bfloat162*>(&gw[2]),
+                                                 *reinterpret_cast<const __nv_bfloat162*>(&gw[3])));
+        const uint32_t mw = *reinterpret_cast<const uint32_t*>(&m);
+        exact = fminf(bf_lo(mw), bf_hi(mw)) < kGateExactBelow;
+    }
+    if (exact) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) y[j] = silu_mul(g[j], u[j]);
-    return pack8(y);
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = bf2_to_f2(gw[k]), u = bf2_to_f2(uw[k]);
+            out[k] = pack_bf16x2(g.x * sigmoid_reference(g.x) * u.x, g.y * sigmoid_reference(g.y) * u.y);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = bf2_to_f2(gw[k]), u = bf2_to_f2(uw[k]);
+            const float2 y = mul2_rn(mul2_rn(g, sigmoid2<(kSteps == 0 ? 2 : kSteps)>(g)), u);
+            out[k] = pack_bf16x2(y.x, y.y);
+        }
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
 constexpr int kElemThreads = 256;
@@ -31,6 +50,7 @@ constexpr int kElemUnroll = 4;
 
 // Flat elementwise kernel: each CTA covers kElemThreads*kElemUnroll consecutive vectors,
 // all loads of a thread issued before its first store.
+template <int kSteps>
 __global__ void __launch_bounds__(kElemThreads) swiglu_kernel(uint4* __restrict__ y, const uint4* gate,
                                                               const uint4* up, long long n_vec) {
     const long long base = static_cast<long long>(blockIdx.x) * (kElemThreads * kElemUnroll) + threadIdx.x;
@@ -46,11 +66,11 @@ __global__ void __launch_bounds__(kElemThreads) swiglu_kernel(uint4* __restrict_
 #pragma unroll
     for (int k = 0; k < kElemUnroll; ++k) {
         const long long i = base + k * kElemThreads;
-        if (i < n_vec) st_vec(y + i, swiglu8(gv[k], uv[k]));
+        if (i < n_vec) st_vec(y + i, swiglu8<kSteps>(gv[k], uv[k]));
     }
 }
 
-template <int kThreads, int VPT, bool kStoreY>
+template <int kThreads, int VPT, bool kStoreY, int kSteps>
 __global__ void __launch_bounds__(kThreads, (kThreads == 512 ? 2 : 4))
 swiglu_quant_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y, const void* gate,
                     const void* up, long long num_tokens, int inter_dim) {
@@ -85,7 +105,7 @@ swiglu_quant_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y
                 const int s = s0 + k;
                 const int i = tid + s * kThreads;
                 if (s < VPT && i < n_vecs) {
-                    yw[s] = swiglu8(gv[k], uv[k]);
+                    yw[s] = swiglu8<kSteps>(gv[k], uv[k]);
                     if constexpr (kStoreY) st_vec(static_cast<uint4*>(y) + row_off + i, yw[s]);
                     m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s].x));
                     m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s].y));
@@ -113,13 +133,13 @@ swiglu_quant_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y
                 }
             }
         }
-        amax = group_max<32>(amax);
+        amax = warp_max_nonneg(amax);
         if (lane == 0) s_mx[parity][warp] = amax;
         __syncthreads();
-        amax = group_max<kWarps>(s_mx[parity][lane & (kWarps - 1)]);
+        amax = warp_max_nonneg(s_mx[parity][lane & (kWarps - 1)]);
 
-        const float inv = (amax > 0.0f) ? (127.0f / amax) : 0.0f;
-        if (tid == 0) x_scale[row] = amax / 127.0f;
+        const float inv = quant_inv_scale<127>(amax);
+        if (tid == 0) x_scale[row] = quant_scale<127>(amax);
         const bool fast = finite && inv <= 3.0e38f;
         uint2* q_row = reinterpret_cast<uint2*>(q) + row_off;
 #pragma unroll
@@ -138,20 +158,37 @@ swiglu_quant_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y
     }
 }
 
-template <int kThreads, int VPT>
-int launch_swiglu_quant(int8_t* q, float* x_scale, void* y, const void* gate, const void* up,
-                        long long num_tokens, int inter_dim, cudaStream_t stream) {
+template <int kThreads, int VPT, int kSteps>
+int launch_swiglu_quant_steps(int8_t* q, float* x_scale, void* y, const void* gate, const void* up,
+                              long long num_tokens, int inter_dim, cudaStream_t stream) {
     static const int resident_y = host::resident_ctas(
-        reinterpret_cast<const void*>(&swiglu_quant_kernel<kThreads, VPT, true>), kThreads);
+        reinterpret_cast<const void*>(&swiglu_quant_kernel<kThreads, VPT, true, kSteps>), kThreads);
     static const int resident_n = host::resident_ctas(
-        reinterpret_cast<const void*>(&swiglu_quant_kernel<kThreads, VPT, false>), kThreads);
+        reinterpret_cast<const void*>(&swiglu_quant_kernel<kThreads, VPT, false, kSteps>), kThreads);
     const int tuned = host::tuning(host::kSwigluCtasPerSm);
     const long long cap =
         static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : (y ? resident_y : resident_n));
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
-    if (y) swiglu_quant_kernel<kThreads, VPT, true><<<grid, kThreads, 0, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
-    else swiglu_quant_kernel<kThreads, VPT, false><<<grid, kThreads, 0, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
+    if (y) swiglu_quant_kernel<kThreads, VPT, true, kSteps><<<grid, kThreads, 0, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
+    else swiglu_quant_kernel<kThreads, VPT, false, kSteps><<<grid, kThreads, 0, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
     return host::check_launch("swiglu_quant_kernel");
+}
+
+// Reciprocal refinement steps: 1 by default (exhaustively exact, see rh_selftest);
+// rh_tune("swiglu_rcp_steps", 2) adds a second step, 3 selects the IEEE division.
+int rcp_steps() {
+    const int t = host::tuning(host::kSwigluRcpSteps);
+    return t == 2 ? 2 : (t >= 3 ? 0 : 1);
+}
+
+template <int kThreads, int VPT>
+int launch_swiglu_quant(int8_t* q, float* x_scale, void* y, const void* gate, const void* up,
+                        long long num_tokens, int inter_dim, cudaStream_t stream) {
+    switch (rcp_steps()) {
+        case 0: return launch_swiglu_quant_steps<kThreads, VPT, 0>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream);
+        case 1: return launch_swiglu_quant_steps<kThreads, VPT, 1>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream);
+        default: return launch_swiglu_quant_steps<kThreads, VPT, 2>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream);
+    }
 }
 
 }  // namespace
@@ -170,8 +207,15 @@ extern "C" int rh_swiglu_bf16(void* y, const void* gate, const void* up, long lo
     const long long per_cta = kElemThreads * kElemUnroll;
     const long long grid = (n_vec + per_cta - 1) / per_cta;
     RH_REQUIRE(grid <= 0x7fffffffLL, RH_ERR_UNSUPPORTED_DIM, "rh_swiglu_bf16: n too large");
-    swiglu_kernel<<<static_cast<unsigned>(grid), kElemThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<uint4*>(y), static_cast<const uint4*>(gate), static_cast<const uint4*>(up), n_vec);
+    const unsigned g = static_cast<unsigned>(grid);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint4* yp = static_cast<uint4*>(y);
+    const uint4 *gp = static_cast<const uint4*>(gate), *up_ = static_cast<const uint4*>(up);
+    switch (rcp_steps()) {
+        case 0: swiglu_kernel<0><<<g, kElemThreads, 0, s>>>(yp, gp, up_, n_vec); break;
+        case 1: swiglu_kernel<1><<<g, kElemThreads, 0, s>>>(yp, gp, up_, n_vec); break;
+        default: swiglu_kernel<2><<<g, kElemThreads, 0, s>>>(yp, gp, up_, n_vec); break;
+    }
     return host::check_launch("swiglu_kernel");
 }
 
@@ -188,9 +232,23 @@ extern "C" int rh_swiglu_quant_int8(int8_t* q, float* x_scale, void* y_or_null, 
                RH_ERR_MISALIGNED, "rh_swiglu_quant_int8: pointers must be 16-byte aligned (q: 8)");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n_vecs = inter_dim / kVec;
-    if (n_vecs <= 256) return launch_swiglu_quant<256, 1>(q, x_scale, y_or_null, gate, up, num_tokens, inter_dim, s);
-    if (n_vecs <= 512) return launch_swiglu_quant<256, 2>(q, x_scale, y_or_null, gate, up, num_tokens, inter_dim, s);
-    if (n_vecs <= 1024) return launch_swiglu_quant<512, 2>(q, x_scale, y_or_null, gate, up, num_tokens, inter_dim, s);
-    if (n_vecs <= 1536) return launch_swiglu_quant<512, 3>(q, x_scale, y_or_null, gate, up, num_tokens, inter_dim, s);
-    return launch_swiglu_quant<512, 4>(q, x_scale, y_or_null, gate, up, num_tokens, inter_dim, s);
+    // 256 threads x up to 8 vectors each (7 x 256 = 14336/8 exactly), or 512 x up to 4 on request.
+    const bool wide = host::tuning(host::kSwigluThreads) == 512 && n_vecs > 512;
+#define RH_SWIGLU(T, V) return launch_swiglu_quant<T, V>(q, x_scale, y_or_null, gate, up, num_tokens, inter_dim, s)
+    if (wide) {
+        if (n_vecs <= 1024) RH_SWIGLU(512, 2);
+        if (n_vecs <= 1536) RH_SWIGLU(512, 3);
+        RH_SWIGLU(512, 4);
+    }
+    switch ((n_vecs + 255) / 256) {
+        case 1: RH_SWIGLU(256, 1);
+        case 2: RH_SWIGLU(256, 2);
+        case 3: RH_SWIGLU(256, 3);
+        case 4: RH_SWIGLU(256, 4);
+        case 5: RH_SWIGLU(256, 5);
+        case 6: RH_SWIGLU(256, 6);
+        case 7: RH_SWIGLU(256, 7);
+        default: RH_SWIGLU(256, 8);
+    }
+#undef RH_SWIGLU
 }
