@@ -158,10 +158,17 @@ int rh_synth_ids_i32(int32_t* out, size_t count, uint64_t seed, uint64_t tensor_
  * Everything the library uses by default must read 0.  Diagnostic: allocates, synchronises. */
 int rh_selftest(unsigned int* mismatches_host);
 
+/* The staged kernels wait on shared-memory barriers with a poll limit instead of spinning forever.
+ * A wait that ran out records (source line << 8 | 1) in a sticky per-device word and the kernel
+ * returns early; this reads that word into *error_host (HOST pointer; 0 = no error so far).
+ * Synchronises the device. */
+int rh_device_error(int* error_host);
+
 /* ---- Tuning knobs (process-wide; for experiments, defaults are the tuned values) --------- */
 
 /* key: "rows_ctas_per_sm", "swiglu_ctas_per_sm", "rope_warps_per_cta", "embed_ctas_per_sm",
- * "swiglu_threads" (256|512), "swiglu_rcp_steps" (1|2|3 = IEEE division); value <= 0 restores
+ * "swiglu_threads" (256|512), "swiglu_rcp_steps" (1|2|3 = IEEE division), "rows_stages" /
+ * "swiglu_stages" (depth of the bulk-copy staging ring, 1 = direct loads); value <= 0 restores
  * the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
 int rh_tune(const char* key, int value);
 

@@ -41,6 +41,7 @@ SIGNATURES = {
     "rh_synth_ids_i32": [_p, _sz, _u64, _u64, _u64, _i32, _p],
     "rh_tune": [C.c_char_p, _i],
     "rh_selftest": [_p],
+    "rh_device_error": [_p],
 }
 _RESTYPES = {"rh_status_string": C.c_char_p, "rh_last_error_string": C.c_char_p}
 

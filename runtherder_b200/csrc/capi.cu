@@ -9,6 +9,10 @@
 
 #include "rh_common.cuh"
 
+namespace rh {
+__device__ int g_rh_device_error = 0;
+}
+
 namespace rh::host {
 
 namespace {
@@ -96,6 +100,13 @@ extern "C" int rh_selftest(unsigned int* mismatches_host) {
     return RH_OK;
 }
 
+extern "C" int rh_device_error(int* error_host) {
+    RH_REQUIRE(error_host != nullptr, RH_ERR_INVALID_ARG, "rh_device_error: null pointer");
+    const cudaError_t err = cudaMemcpyFromSymbol(error_host, g_rh_device_error, sizeof(int));
+    if (err != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_device_error: %s", cudaGetErrorString(err));
+    return RH_OK;
+}
+
 extern "C" int rh_version(void) { return 100; }
 
 extern "C" const char* rh_status_string(int status) {
@@ -116,7 +127,7 @@ extern "C" int rh_tune(const char* key, int value) {
     static const char* const kNames[host::kTuneSlots] = {"rows_ctas_per_sm", "swiglu_ctas_per_sm",
                                                          "rope_warps_per_cta", "embed_ctas_per_sm",
                                                          "elem_ctas_per_sm", "swiglu_threads",
-                                                         "swiglu_rcp_steps"};
+                                                         "swiglu_rcp_steps", "rows_stages", "swiglu_stages"};
     RH_REQUIRE(key != nullptr, RH_ERR_INVALID_ARG, "rh_tune: null key");
     for (int i = 0; i < host::kTuneSlots; ++i) {
         if (std::strcmp(key, kNames[i]) == 0) {

@@ -97,7 +97,7 @@ extern "C" int rh_embedding_lookup_bf16(void* out, const void* table, const int*
     RH_REQUIRE(host::aligned16(out) && host::aligned16(table), RH_ERR_MISALIGNED,
                "rh_embedding_lookup_bf16: pointers must be 16-byte aligned");
     int per_sm = host::tuning(host::kEmbedCtasPerSm);
-    if (per_sm <= 0) per_sm = 16;
+    if (per_sm <= 0) per_sm = 64;   // pure copy: resident CTAs = bytes in flight
     const long long cap = static_cast<long long>(host::num_sms()) * per_sm;
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
     embedding_kernel<<<grid, kEmbThreads, 0, static_cast<cudaStream_t>(stream)>>>(

@@ -1,0 +1,75 @@
+// Bulk-copy (TMA) staging ring: one producer thread streams fixed-size slots of global memory into
+// shared memory with cp.async.bulk; consumer warps wait on a slot's "full" mbarrier, read it with
+// ordinary shared loads and hand it back through its "empty" mbarrier.  The bytes in flight are then
+// set by the ring depth instead of by registers and occupancy, and memory latency never sits in a
+// consumer warp's dependency chain.
+//
+// Rules kept here:
+//  * plain (non-multicast) bulk copies of this GPU's own memory, no cluster launch;
+//  * source address, destination address and size are multiples of 16 bytes;
+//  * every wait is bounded: after kSpinLimit failed polls the waiter records an error in
+//    g_rh_device_error and gives up, so a kernel can never spin forever.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace rh {
+
+// Sticky per-device error word: 0 = none; otherwise (line << 8) | code of the first failure.
+// Read it with rh_device_error().
+extern __device__ int g_rh_device_error;
+
+namespace pipe {
+
+constexpr int kSpinLimit = 1 << 22;  // polls; each try_wait already blocks for a while in hardware
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (after recording the error) when the barrier never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int where) {
+    for (int i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
+    atomicCAS(&g_rh_device_error, 0, (where << 8) | 1);
+    return false;
+}
+// global -> shared bulk copy that reports its bytes to `bar`.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// Barrier among the first `count` threads of the CTA only (the producer warp does not take part).
+__device__ __forceinline__ void consumer_sync(int count) {
+    asm volatile("bar.sync 1, %0;" ::"r"(count) : "memory");
+}
+
+}  // namespace pipe
+}  // namespace rh

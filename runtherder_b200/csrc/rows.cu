@@ -15,6 +15,7 @@
 // bit-identical to the reference's CUDA kernel.  amax reductions are exact in any
 // order.
 #include "rh_common.cuh"
+#include "rh_pipeline.cuh"
 
 namespace rh {
 
@@ -46,150 +47,260 @@ struct RowArgs {
     float eps;
 };
 
-template <int VPT, unsigned F>
-__global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
+template <bool kStaged>
+__device__ __forceinline__ void row_sync() {
+    if constexpr (kStaged) pipe::consumer_sync(kRowThreads);  // the producer warp is not part of it
+    else __syncthreads();
+}
+
+// Per-CTA constants of a launch.
+struct RowCtx {
+    int tid, lane, warp, n_vecs;
+    float dim_f, inv_dim;
+    bool dim_pow2;
+    long long slot_base;
+};
+
+template <unsigned F>
+__device__ __forceinline__ RowCtx make_ctx(const RowArgs& a) {
+    RowCtx c;
+    c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5;
+    c.n_vecs = a.dim / kVec;
+    c.dim_f = static_cast<float>(a.dim);
+    c.dim_pow2 = (a.dim & (a.dim - 1)) == 0;  // then ss/dim is an exact scaling
+    c.inv_dim = 1.0f / c.dim_f;
+    c.slot_base = 0;
+    if constexpr ((F & kFFp8) != 0) c.slot_base = static_cast<long long>(*a.at_pos) * a.rows_per_pos;
+    return c;
+}
+
+// Everything that happens to one row once its vectors sit in registers (xv, rv): h, h_out, the
+// sum of squares and rrms, y, amax, codes and scale.  Shared by the direct-load and the staged kernel.
+template <int VPT, unsigned F, bool kStaged>
+__device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, long long row, int parity,
+                                            const uint4 (&xv)[VPT], const uint4 (&rv)[VPT], const uint4 (&gw)[VPT],
+                                            float (&s_ss)[2][kRowWarps], float (&s_mx)[2][kRowWarps]) {
     constexpr bool kNorm = (F & kFNorm) != 0, kAdd = (F & kFAdd) != 0, kStoreY = (F & kFStoreY) != 0;
     constexpr bool kInt8 = (F & kFInt8) != 0, kFp8 = (F & kFFp8) != 0, kQuant = kInt8 || kFp8;
+    const int tid = c.tid, lane = c.lane, warp = c.warp, n_vecs = c.n_vecs;
+    const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(n_vecs);
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n_vecs = a.dim / kVec;
+    uint32_t yw[VPT][4];  // the row as the next kernel would read it back: packed bf16
 
-    __shared__ float s_ss[2][kRowWarps];
-    __shared__ float s_mx[2][kRowWarps];
-
-    uint4 gw[VPT];
     if constexpr (kNorm) {
-#pragma unroll
-        for (int s = 0; s < VPT; ++s) {
-            const int i = tid + s * kRowThreads;
-            if (i < n_vecs) gw[s] = ld_weight(static_cast<const uint4*>(a.g) + i);
-        }
-    }
-    const float dim_f = static_cast<float>(a.dim);
-    const bool dim_pow2 = (a.dim & (a.dim - 1)) == 0;  // then ss/dim is an exact scaling
-    const float inv_dim = 1.0f / dim_f;
-    long long slot_base = 0;
-    if constexpr (kFp8) slot_base = static_cast<long long>(*a.at_pos) * a.rows_per_pos;
-
-    int parity = 0;
-    for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
-        const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(n_vecs);
-        const uint4* x_row = static_cast<const uint4*>(a.x) + row_off;
-
-        uint4 xv[VPT], rv[VPT];
+        float h[VPT][8];
+        float ss = 0.0f;
 #pragma unroll
         for (int s = 0; s < VPT; ++s) {
             const int i = tid + s * kRowThreads;
             if (i < n_vecs) {
-                xv[s] = ld_stream(x_row + i);
+                if constexpr (kAdd) {
+                    const uint32_t xw[4] = {xv[s].x, xv[s].y, xv[s].z, xv[s].w};
+                    const uint32_t rw[4] = {rv[s].x, rv[s].y, rv[s].z, rv[s].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 hh = add2_rn(bf2_to_f2(xw[k]), bf2_to_f2(rw[k]));
+                        h[s][2 * k] = hh.x;
+                        h[s][2 * k + 1] = hh.y;
+                    }
+                    st_vec(static_cast<uint4*>(a.h_out) + row_off + i, pack8(h[s]));
+                } else {
+                    unpack8(xv[s], h[s]);
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss = __fmaf_rn(h[s][j], h[s][j], ss);
+            }
+        }
+        ss = group_sum<32>(ss);
+        if (lane == 0) s_ss[parity][warp] = ss;
+        row_sync<kStaged>();
+        const float total = group_sum<kRowWarps>(s_ss[parity][lane & (kRowWarps - 1)]);
+        const float rrms = rsqrtf((c.dim_pow2 ? total * c.inv_dim : total / c.dim_f) + a.eps);
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            const int i = tid + s * kRowThreads;
+            if (i < n_vecs) {
+                const uint32_t gws[4] = {gw[s].x, gw[s].y, gw[s].z, gw[s].w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {   // y = (h * rrms) * g, two elements per instruction
+                    const float2 t = mul2_rn(make_float2(h[s][2 * k], h[s][2 * k + 1]), splat2(rrms));
+                    const float2 yf = mul2_rn(t, bf2_to_f2(gws[k]));
+                    yw[s][k] = pack_bf16x2(yf.x, yf.y);
+                }
+                if constexpr (kStoreY)
+                    st_vec(static_cast<uint4*>(a.y) + row_off + i, make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            yw[s][0] = xv[s].x; yw[s][1] = xv[s].y; yw[s][2] = xv[s].z; yw[s][3] = xv[s].w;
+        }
+    }
+
+    if constexpr (kQuant) {
+        // Row amax of the bf16 values.  The packed NaN-propagating max tells, for free,
+        // whether this thread holds a non-finite value; the reference's fmaxf skips NaN.
+        uint32_t m2 = 0u;
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            const int i = tid + s * kRowThreads;
+            if (i < n_vecs) {
+#pragma unroll
+                for (int w = 0; w < 4; ++w) m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s][w]));
+            }
+        }
+        const float m_lo = bf_lo(m2), m_hi = bf_hi(m2);
+        const bool finite = (m_lo <= 3.0e38f) && (m_hi <= 3.0e38f);  // false for Inf and NaN
+        float amax = fmaxf(m_lo, m_hi);
+        if (!finite) {
+            amax = 0.0f;
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                const int i = tid + s * kRowThreads;
+                if (i < n_vecs) {
+#pragma unroll
+                    for (int w = 0; w < 4; ++w)
+                        amax = fmaxf(amax, fmaxf(fabsf(bf_lo(yw[s][w])), fabsf(bf_hi(yw[s][w]))));
+                }
+            }
+        }
+        amax = warp_max_nonneg(amax);
+        if (lane == 0) s_mx[parity][warp] = amax;
+        row_sync<kStaged>();
+        amax = warp_max_nonneg(s_mx[parity][lane & (kRowWarps - 1)]);
+
+        constexpr int kQMax = kInt8 ? 127 : 448;
+        const float inv = quant_inv_scale<kQMax>(amax);
+        const long long dst_row = row + c.slot_base;
+        if (tid == 0) a.scale[dst_row] = quant_scale<kQMax>(amax);
+        uint2* c_row = static_cast<uint2*>(a.codes) + static_cast<size_t>(dst_row) * n_vecs;
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            const int i = tid + s * kRowThreads;
+            if (i < n_vecs) {
+                if (kInt8 && finite && inv <= 3.0e38f) {  // an overflowed inverse (subnormal amax) takes the exact path
+                    st_vec8(c_row + i, pack_int8x8_fast(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), inv));
+                } else {
+                    float yf[8];
+                    unpack8(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), yf);
+                    st_vec8(c_row + i, kInt8 ? pack_int8x8(yf, inv) : pack_e4m3x8(yf, inv));
+                }
+            }
+        }
+    }
+}
+
+template <int VPT, unsigned F>
+__device__ __forceinline__ void load_gains(const RowArgs& a, int n_vecs, uint4 (&gw)[VPT]) {
+    if constexpr ((F & kFNorm) != 0) {
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            const int i = static_cast<int>(threadIdx.x) + s * kRowThreads;
+            if (i < n_vecs) gw[s] = ld_weight(static_cast<const uint4*>(a.g) + i);
+        }
+    }
+}
+
+// Direct-load kernel: each thread loads its vectors of the row straight into registers.
+template <int VPT, unsigned F>
+__global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
+    constexpr bool kAdd = (F & kFAdd) != 0;
+    __shared__ float s_ss[2][kRowWarps];
+    __shared__ float s_mx[2][kRowWarps];
+    const RowCtx c = make_ctx<F>(a);
+    uint4 gw[VPT];
+    load_gains<VPT, F>(a, c.n_vecs, gw);
+
+    int parity = 0;
+    for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
+        const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(c.n_vecs);
+        uint4 xv[VPT], rv[VPT];
+#pragma unroll
+        for (int s = 0; s < VPT; ++s) {
+            const int i = c.tid + s * kRowThreads;
+            if (i < c.n_vecs) {
+                xv[s] = ld_stream(static_cast<const uint4*>(a.x) + row_off + i);
                 if constexpr (kAdd) rv[s] = ld_stream(static_cast<const uint4*>(a.residual) + row_off + i);
             }
         }
+        process_row<VPT, F, false>(a, c, row, parity, xv, rv, gw, s_ss, s_mx);
+    }
+}
 
-        uint32_t yw[VPT][4];  // the row as the next kernel would read it back: packed bf16
+// Staged kernel: a producer thread streams the rows through a shared-memory ring with bulk copies
+// (one slot = the 256 vectors, 4 KB per operand, that the 256 consumer threads read together), so
+// several rows per CTA are always in flight and the consumers only ever wait on shared memory.
+// Thread t still owns vectors t, t+256, ...: the arithmetic, and every bit of the output, is that
+// of the direct-load kernel.
+constexpr int kSlotBytes = kRowThreads * 16;
 
-        if constexpr (kNorm) {
-            float h[VPT][8];
-            float ss = 0.0f;
-#pragma unroll
-            for (int s = 0; s < VPT; ++s) {
-                const int i = tid + s * kRowThreads;
-                if (i < n_vecs) {
-                    if constexpr (kAdd) {
-                        const uint32_t xw[4] = {xv[s].x, xv[s].y, xv[s].z, xv[s].w};
-                        const uint32_t rw[4] = {rv[s].x, rv[s].y, rv[s].z, rv[s].w};
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const float2 hh = add2_rn(bf2_to_f2(xw[k]), bf2_to_f2(rw[k]));
-                            h[s][2 * k] = hh.x;
-                            h[s][2 * k + 1] = hh.y;
-                        }
-                        st_vec(static_cast<uint4*>(a.h_out) + row_off + i, pack8(h[s]));
-                    } else {
-                        unpack8(xv[s], h[s]);
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) ss = __fmaf_rn(h[s][j], h[s][j], ss);
-                }
-            }
-            ss = group_sum<32>(ss);
-            if (lane == 0) s_ss[parity][warp] = ss;
-            __syncthreads();
-            const float total = group_sum<kRowWarps>(s_ss[parity][lane & (kRowWarps - 1)]);
-            const float rrms = rsqrtf((dim_pow2 ? total * inv_dim : total / dim_f) + a.eps);
-#pragma unroll
-            for (int s = 0; s < VPT; ++s) {
-                const int i = tid + s * kRowThreads;
-                if (i < n_vecs) {
-                    const uint32_t gws[4] = {gw[s].x, gw[s].y, gw[s].z, gw[s].w};
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {   // y = (h * rrms) * g, two elements per instruction
-                        const float2 t = mul2_rn(make_float2(h[s][2 * k], h[s][2 * k + 1]), splat2(rrms));
-                        const float2 yf = mul2_rn(t, bf2_to_f2(gws[k]));
-                        yw[s][k] = pack_bf16x2(yf.x, yf.y);
-                    }
-                    if constexpr (kStoreY)
-                        st_vec(static_cast<uint4*>(a.y) + row_off + i, make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]));
-                }
-            }
-        } else {
-#pragma unroll
-            for (int s = 0; s < VPT; ++s) {
-                yw[s][0] = xv[s].x; yw[s][1] = xv[s].y; yw[s][2] = xv[s].z; yw[s][3] = xv[s].w;
-            }
+template <int VPT, unsigned F>
+__global__ void __launch_bounds__(kRowThreads + 32) rows_staged_kernel(const RowArgs a, const int stages) {
+    constexpr bool kAdd = (F & kFAdd) != 0;
+    constexpr int kOps = kAdd ? 2 : 1;
+    extern __shared__ __align__(128) unsigned char ring[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(stages) * kOps * kSlotBytes);
+    uint64_t* empty = full + stages;
+    __shared__ float s_ss[2][kRowWarps];
+    __shared__ float s_mx[2][kRowWarps];
+
+    const int n_vecs = a.dim / kVec;
+    const int slots_per_row = (n_vecs + kRowThreads - 1) / kRowThreads;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            pipe::mbar_init(full + s, 1);
+            pipe::mbar_init(empty + s, kRowWarps);
         }
+        pipe::mbar_init_fence();
+    }
+    __syncthreads();
 
-        if constexpr (kQuant) {
-            // Row amax of the bf16 values.  The packed NaN-propagating max tells, for free,
-            // whether this thread holds a non-finite value; the reference's fmaxf skips NaN.
-            uint32_t m2 = 0u;
-#pragma unroll
-            for (int s = 0; s < VPT; ++s) {
-                const int i = tid + s * kRowThreads;
-                if (i < n_vecs) {
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s][w]));
-                }
-            }
-            const float m_lo = bf_lo(m2), m_hi = bf_hi(m2);
-            const bool finite = (m_lo <= 3.0e38f) && (m_hi <= 3.0e38f);  // false for Inf and NaN
-            float amax = fmaxf(m_lo, m_hi);
-            if (!finite) {
-                amax = 0.0f;
-#pragma unroll
-                for (int s = 0; s < VPT; ++s) {
-                    const int i = tid + s * kRowThreads;
-                    if (i < n_vecs) {
-#pragma unroll
-                        for (int w = 0; w < 4; ++w)
-                            amax = fmaxf(amax, fmaxf(fabsf(bf_lo(yw[s][w])), fabsf(bf_hi(yw[s][w]))));
-                    }
-                }
-            }
-            amax = warp_max_nonneg(amax);
-            if (lane == 0) s_mx[parity][warp] = amax;
-            __syncthreads();
-            amax = warp_max_nonneg(s_mx[parity][lane & (kRowWarps - 1)]);
-
-            constexpr int kQMax = kInt8 ? 127 : 448;
-            const float inv = quant_inv_scale<kQMax>(amax);
-            const long long dst_row = row + slot_base;
-            if (tid == 0) a.scale[dst_row] = quant_scale<kQMax>(amax);
-            uint2* c_row = static_cast<uint2*>(a.codes) + static_cast<size_t>(dst_row) * n_vecs;
-#pragma unroll
-            for (int s = 0; s < VPT; ++s) {
-                const int i = tid + s * kRowThreads;
-                if (i < n_vecs) {
-                    if (kInt8 && finite && inv <= 3.0e38f) {  // an overflowed inverse (subnormal amax) takes the exact path
-                        st_vec8(c_row + i, pack_int8x8_fast(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), inv));
-                    } else {
-                        float yf[8];
-                        unpack8(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), yf);
-                        st_vec8(c_row + i, kInt8 ? pack_int8x8(yf, inv) : pack_e4m3x8(yf, inv));
-                    }
+    if (threadIdx.x >= kRowThreads) {   // producer warp: one thread issues every copy of this CTA
+        if (threadIdx.x == kRowThreads) {
+            int s = 0;
+            uint32_t round = 0;   // how many times the ring has wrapped
+            for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x) {
+                const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(n_vecs);
+                for (int sl = 0; sl < slots_per_row; ++sl) {
+                    if (round > 0 && !pipe::mbar_wait(empty + s, (round - 1) & 1, __LINE__)) return;
+                    const int vec0 = sl * kRowThreads;
+                    const uint32_t bytes = static_cast<uint32_t>(min(kRowThreads, n_vecs - vec0)) * 16u;
+                    unsigned char* dst = ring + static_cast<size_t>(s) * kOps * kSlotBytes;
+                    pipe::mbar_expect_tx(full + s, bytes * kOps);
+                    pipe::bulk_load(dst, static_cast<const uint4*>(a.x) + row_off + vec0, bytes, full + s);
+                    if constexpr (kAdd)
+                        pipe::bulk_load(dst + kSlotBytes, static_cast<const uint4*>(a.residual) + row_off + vec0, bytes, full + s);
+                    if (++s == stages) { s = 0; ++round; }
                 }
             }
         }
+        return;
+    }
+
+    const RowCtx c = make_ctx<F>(a);
+    uint4 gw[VPT];
+    load_gains<VPT, F>(a, c.n_vecs, gw);
+
+    int parity = 0, s = 0;
+    uint32_t phase = 0;
+    for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
+        uint4 xv[VPT], rv[VPT];
+#pragma unroll
+        for (int sl = 0; sl < VPT; ++sl) {
+            if (sl < slots_per_row) {
+                if (!pipe::mbar_wait(full + s, phase, __LINE__)) return;
+                const unsigned char* src = ring + static_cast<size_t>(s) * kOps * kSlotBytes + c.tid * 16;
+                if (c.tid + sl * kRowThreads < c.n_vecs) {
+                    xv[sl] = *reinterpret_cast<const uint4*>(src);
+                    if constexpr (kAdd) rv[sl] = *reinterpret_cast<const uint4*>(src + kSlotBytes);
+                }
+                __syncwarp();
+                if (c.lane == 0) pipe::mbar_arrive(empty + s);   // this warp is done with the slot
+                if (++s == stages) { s = 0; phase ^= 1; }
+            }
+        }
+        process_row<VPT, F, true>(a, c, row, parity, xv, rv, gw, s_ss, s_mx);
     }
 }
 
@@ -272,6 +383,29 @@ __global__ void __launch_bounds__(kRowThreads) short_rows_kernel(const RowArgs a
 // CTA keeps its gains in registers and walks its share of the rows.
 template <int VPT, unsigned F>
 void launch_long(const RowArgs& a, cudaStream_t stream) {
+    constexpr int kOps = (F & kFAdd) ? 2 : 1;
+    // The direct-load kernel is the default: measured on B200 the row kernels are bound by their
+    // per-row dependency chain (two block reductions), not by load latency, and the ring's extra warp
+    // costs a resident CTA.  rh_tune("rows_stages", n >= 2) selects the staged kernel with n slots.
+    const int stages = host::tuning(host::kRowsStages);
+    // Rows up to 4096 wide (two slots per row); wider rows keep too much in registers to add a ring.
+    const bool staged = VPT <= 2 && stages >= 2 && a.num_rows >= 4LL * host::num_sms();
+    if constexpr (VPT <= 2) if (staged) {
+        const size_t smem = static_cast<size_t>(stages) * kOps * kSlotBytes + 2 * stages * sizeof(uint64_t);
+        static int configured_stages = 0;
+        static int resident = 1;
+        if (configured_stages != stages) {   // first use (or a changed ring depth): opt in to the shared memory
+            cudaFuncSetAttribute(reinterpret_cast<const void*>(&rows_staged_kernel<VPT, F>),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_staged_kernel<VPT, F>), kRowThreads + 32, smem);
+            configured_stages = stages;
+        }
+        const int tuned = host::tuning(host::kRowsCtasPerSm);
+        const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
+        const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
+        rows_staged_kernel<VPT, F><<<grid, kRowThreads + 32, smem, stream>>>(a, stages);
+        return;
+    }
     static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F>), kRowThreads);
     const int tuned = host::tuning(host::kRowsCtasPerSm);
     const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);

@@ -211,6 +211,36 @@ def test_fused_chain_equals_reference_sequence(env, name, rows, offset):
         assert env.eq(fused[key], ref[key]), f"{name}: {key}: {env.mm(fused[key], ref[key])} of {fused[key].numel()} differ"
 
 
+@pytest.mark.parametrize("T,H", [(2048, 4096), (1000, 3072), (777, 264)])
+def test_staged_rows_kernel_matches_direct(env, T, H):
+    """The bulk-copy (TMA ring) variant of the row kernels, selected with rh_tune("rows_stages", n), must
+    produce the bytes of the direct-load kernel, and no bounded wait may have run out."""
+    import ctypes as C
+    from runtherder_b200 import _lib
+    x = env.synth.normal_bf16(T * H, 3, 1).view(T, H)
+    r = env.synth.normal_bf16(T * H, 3, 2).view(T, H)
+    g = env.synth.uniform_bf16(H, 3, 3, 0.5, 1.5)
+    res = {}
+    for stages in (1, 2, 5):
+        _lib.call("rh_tune", b"rows_stages", stages)
+        q = torch.empty(T, H, dtype=torch.int8, device="cuda"); s = torch.empty(T, dtype=torch.float32, device="cuda")
+        h, y = torch.empty_like(x), torch.empty_like(x)
+        env.K.rmsnorm_add_quant_int8(q, s, h, y, x, r, g, T, H, 1e-5)
+        q2 = torch.empty_like(q); s2 = torch.empty_like(s)
+        env.K.quantize_per_token_int8(q2, s2, x, T, H)
+        y2 = torch.empty_like(x)
+        env.K.rmsnorm_bf16_forward(y2, x, g, T, H, 1e-5)
+        torch.cuda.synchronize()
+        res[stages] = (q, s, h, y, q2, s2, y2)
+    _lib.call("rh_tune", b"rows_stages", 0)
+    for stages in (2, 5):
+        for a, b in zip(res[1], res[stages]):
+            assert env.eq(a, b)
+    err = C.c_int(-1)
+    _lib.call("rh_device_error", C.byref(err))
+    assert err.value == 0
+
+
 def test_division_free_sequences_are_exact(env):
     """rh_selftest: the refined-reciprocal replacements of the reference's IEEE divisions, exhaustively."""
     import ctypes as C
