@@ -158,6 +158,20 @@ int rh_synth_ids_i32(int32_t* out, size_t count, uint64_t seed, uint64_t tensor_
  * Everything the library uses by default must read 0.  Diagnostic: allocates, synchronises. */
 int rh_selftest(unsigned int* mismatches_host);
 
+/* rh_selftest without any allocation.  This entry point has no counterpart in the reference; it exists
+ * for hosts that cannot call cudaMalloc once they are running — an engine that, like the reference's,
+ * hands all device memory to its weight slab, scratch arena and KV cache at start-up, where a later
+ * cudaMalloc may fail and in any case stalls the device.  The mismatch counters live in a fixed
+ * array inside the library image (RH_SELFTEST_MAX_COUNTERS counters, held on every GPU that loads
+ * the library until the process exits).  Writes the first `num_counters` counts of rh_selftest's
+ * layout to mismatches_host (HOST pointer); num_counters > RH_SELFTEST_MAX_COUNTERS is rejected with
+ * RH_ERR_UNSUPPORTED_DIM.  Work is enqueued on `stream` and the call returns after the stream has
+ * drained.  The array is shared by all calls on a device: it is zeroed at the start of each call, and
+ * calls whose GPU work overlaps race on it — serialise them.  The first call on a device resolves the
+ * array's device address; make it before any stream capture starts. */
+#define RH_SELFTEST_MAX_COUNTERS 8
+int rh_selftest_static(unsigned int* mismatches_host, int num_counters, void* stream);
+
 /* The staged kernels wait on shared-memory barriers with a poll limit instead of spinning forever.
  * A wait that ran out records (source line << 8 | 1) in a sticky per-device word and the kernel
  * returns early; this reads that word into *error_host (HOST pointer; 0 = no error so far).
