@@ -178,6 +178,12 @@ int rh_selftest_static(unsigned int* mismatches_host, int num_counters, void* st
  * Synchronises the device. */
 int rh_device_error(int* error_host);
 
+/* Failure-detection self-check: one warp waits, with a limit of `polls` (1..65536) polls, on a
+ * barrier that nothing completes.  The wait must run out: *gave_up_host becomes 1, *error_host the
+ * recorded error word (non-zero), the kernel returns normally and the context stays usable.  The
+ * sticky device error word is restored afterwards.  Diagnostic: allocates, synchronises. */
+int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host);
+
 /* ---- Tuning knobs (process-wide; for experiments, defaults are the tuned values) --------- */
 
 /* key: "rows_ctas_per_sm", "swiglu_ctas_per_sm", "rope_warps_per_cta", "embed_ctas_per_sm",

@@ -42,6 +42,7 @@ SIGNATURES = {
     "rh_tune": [C.c_char_p, _i],
     "rh_selftest": [_p],
     "rh_device_error": [_p],
+    "rh_selfcheck_bounded_wait": [_i, _p, _p],
     "rh_selftest_static": [_p, _i, _p],
 }
 _RESTYPES = {"rh_status_string": C.c_char_p, "rh_last_error_string": C.c_char_p}

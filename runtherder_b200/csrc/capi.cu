@@ -9,9 +9,13 @@
 
 #include "rh_common.cuh"
 
+#include "rh_pipeline.cuh"
+
 namespace rh {
+namespace {
 __device__ int g_rh_device_error = 0;
 }
+}  // namespace rh
 
 namespace rh::host {
 
@@ -57,6 +61,18 @@ int resident_ctas(const void* kernel, int threads, size_t dyn_smem) {
 
 int tuning(int slot) { return g_tuning[slot].load(std::memory_order_relaxed); }
 
+int* device_error_word() {
+    static std::atomic<int*> cache[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    int* p = cache[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rh_device_error) != cudaSuccess) return nullptr;
+        cache[dev].store(p, std::memory_order_release);
+    }
+    return p;
+}
+
 }  // namespace rh::host
 
 namespace rh {
@@ -100,9 +116,48 @@ extern "C" int rh_selftest(unsigned int* mismatches_host) {
     return RH_OK;
 }
 
+namespace rh {
+namespace {
+// One warp waits on a barrier that nothing will ever complete; the bounded wait must give up, record
+// the error and let the kernel return normally.
+__global__ void bounded_wait_probe_kernel(int polls, int* error_word, int* gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        pipe::mbar_init(&bar, 1);
+        pipe::mbar_init_fence();
+    }
+    __syncthreads();
+    const bool ok = pipe::mbar_wait(&bar, 0, __LINE__, error_word, polls);
+    if (threadIdx.x == 0) *gave_up = ok ? 0 : 1;
+}
+}  // namespace
+}  // namespace rh
+
+extern "C" int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host) {
+    RH_REQUIRE(gave_up_host && error_host, RH_ERR_INVALID_ARG, "rh_selfcheck_bounded_wait: null pointer");
+    RH_REQUIRE(polls >= 1 && polls <= (1 << 16), RH_ERR_INVALID_ARG, "rh_selfcheck_bounded_wait: polls must be in 1..65536");
+    int* word = host::device_error_word();
+    RH_REQUIRE(word != nullptr, RH_ERR_CUDA, "rh_selfcheck_bounded_wait: error word unavailable");
+    int* flag = nullptr;
+    if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selfcheck_bounded_wait: cudaMalloc failed");
+    int saved = 0;
+    cudaMemcpy(&saved, word, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaMemset(word, 0, sizeof(int));
+    cudaMemset(flag, 0, sizeof(int));
+    bounded_wait_probe_kernel<<<1, 32>>>(polls, word, flag);
+    cudaError_t err = cudaMemcpy(gave_up_host, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    if (err == cudaSuccess) err = cudaMemcpy(error_host, word, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaMemcpy(word, &saved, sizeof(int), cudaMemcpyHostToDevice);   // the probe leaves the sticky word as it found it
+    cudaFree(flag);
+    if (err != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selfcheck_bounded_wait: %s", cudaGetErrorString(err));
+    return RH_OK;
+}
+
 extern "C" int rh_device_error(int* error_host) {
     RH_REQUIRE(error_host != nullptr, RH_ERR_INVALID_ARG, "rh_device_error: null pointer");
-    const cudaError_t err = cudaMemcpyFromSymbol(error_host, g_rh_device_error, sizeof(int));
+    int* word = host::device_error_word();
+    RH_REQUIRE(word != nullptr, RH_ERR_CUDA, "rh_device_error: error word unavailable");
+    const cudaError_t err = cudaMemcpy(error_host, word, sizeof(int), cudaMemcpyDeviceToHost);
     if (err != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_device_error: %s", cudaGetErrorString(err));
     return RH_OK;
 }
@@ -127,7 +182,8 @@ extern "C" int rh_tune(const char* key, int value) {
     static const char* const kNames[host::kTuneSlots] = {"rows_ctas_per_sm", "swiglu_ctas_per_sm",
                                                          "rope_warps_per_cta", "embed_ctas_per_sm",
                                                          "elem_ctas_per_sm", "swiglu_threads",
-                                                         "swiglu_rcp_steps", "rows_stages", "swiglu_stages"};
+                                                         "swiglu_rcp_steps", "rows_stages", "swiglu_stages",
+                                                         "rows_smem_h"};
     RH_REQUIRE(key != nullptr, RH_ERR_INVALID_ARG, "rh_tune: null key");
     for (int i = 0; i < host::kTuneSlots; ++i) {
         if (std::strcmp(key, kNames[i]) == 0) {

@@ -252,7 +252,7 @@ int resident_ctas(const void* kernel, int threads, size_t dyn_smem = 0);  // CTA
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kSwigluThreads,
-                kSwigluRcpSteps, kRowsStages, kSwigluStages, kTuneSlots };
+                kSwigluRcpSteps, kRowsStages, kSwigluStages, kRowsSmemH, kTuneSlots };
 
 }  // namespace rh::host
 

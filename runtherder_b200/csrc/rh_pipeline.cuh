@@ -7,8 +7,9 @@
 // Rules kept here:
 //  * plain (non-multicast) bulk copies of this GPU's own memory, no cluster launch;
 //  * source address, destination address and size are multiples of 16 bytes;
-//  * every wait is bounded: after kSpinLimit failed polls the waiter records an error in
-//    g_rh_device_error and gives up, so a kernel can never spin forever.
+//  * every wait is bounded: after kSpinLimit failed polls the waiter records an error in the
+//    library's per-device error word (passed to the kernel) and gives up, so a kernel can never spin
+//    forever.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -17,9 +18,11 @@
 
 namespace rh {
 
-// Sticky per-device error word: 0 = none; otherwise (line << 8) | code of the first failure.
-// Read it with rh_device_error().
-extern __device__ int g_rh_device_error;
+namespace host {
+// Device address of the sticky per-device error word (0 = none; otherwise (line << 8) | code of the
+// first failure), resolved once per device.  rh_device_error() reads it.
+int* device_error_word();
+}  // namespace host
 
 namespace pipe {
 
@@ -52,11 +55,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false (after recording the error) when the barrier never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int where) {
-    for (int i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int where, int* error_word,
+                                          int limit = kSpinLimit) {
+    for (int i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }
-    atomicCAS(&g_rh_device_error, 0, (where << 8) | 1);
+    if (error_word != nullptr) atomicCAS(error_word, 0, (where << 8) | 1);
     return false;
 }
 // global -> shared bulk copy that reports its bytes to `bar`.

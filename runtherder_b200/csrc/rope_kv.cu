@@ -60,7 +60,7 @@ __device__ __forceinline__ void rotate(float a, float b, float c, float s, float
 }
 
 template <int D, bool kNorm, bool kKV>
-__global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
+__global__ void __launch_bounds__(256) rope_kv_generic_kernel(const RopeArgs p) {
     constexpr int kLanesPerHead = D / 16;
     constexpr int kHeadsPerGroup = 32 / kLanesPerHead;
     constexpr int kVecsPerRow = D / 8;
@@ -197,6 +197,174 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
     }
 }
 
+// Fast path for head counts that are multiples of the heads a warp carries (4 at D = 128): every
+// group of a warp is then all-Q, all-K or all-V, so the three roles become three straight loops with
+// no per-row role logic, row pointers advance by a constant, and the rotation works on the register
+// pairs a packed bf16 word unpacks into:
+//   lo2 = fma2(a2, c2, b2 * (-s2)),  hi2 = fma2(a2, s2, b2 * c2)
+// — the same two roundings per output as fma(a, c, -(b*s)) and fma(a, s, b*c).
+template <int D, bool kNorm, bool kKV>
+__global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
+    constexpr int kLanesPerHead = D / 16;
+    constexpr int kHeadsPerGroup = 32 / kLanesPerHead;
+    constexpr int kVecsPerRow = D / 8;
+
+    const int lane = threadIdx.x & 31;
+    const int sub = lane % kLanesPerHead;
+    const int hslot = lane / kLanesPerHead;
+    const int warps_per_cta = blockDim.x >> 5;
+    const long long item = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
+    const long long num_items = static_cast<long long>(p.seq_len) * p.items_per_token;
+    if (item >= num_items) return;  // whole warps only
+
+    const int token = static_cast<int>(item / p.items_per_token);
+    const int chunk = static_cast<int>(item % p.items_per_token);
+    const int Hq = p.num_q_heads, Hkv = p.num_kv_heads;
+    const int gq = Hq / kHeadsPerGroup, gk = Hkv / kHeadsPerGroup;
+    const int groups = gq + gk + (kKV ? gk : 0);
+    const int g_begin = chunk * p.groups_per_item;
+    const int g_end = min(groups, g_begin + p.groups_per_item);
+
+    float2 c2[4], s2[4], ns2[4];   // cos, sin, -sin of this lane's eight angles, as pairs
+    if (g_begin < gq + gk) {
+        const float pos = static_cast<float>(p.positions[token]);
+        const float4 f0 = __ldg(reinterpret_cast<const float4*>(p.inv_freq) + 2 * sub);
+        const float4 f1 = __ldg(reinterpret_cast<const float4*>(p.inv_freq) + 2 * sub + 1);
+        const float fr[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            __sincosf(pos * fr[2 * k], &s2[k].x, &c2[k].x);
+            __sincosf(pos * fr[2 * k + 1], &s2[k].y, &c2[k].y);
+            ns2[k] = neg2(s2[k]);
+        }
+    }
+    long long slot_base = 0;
+    if constexpr (kKV) slot_base = static_cast<long long>(*p.at_pos) * Hkv;
+
+    // [per-head RMSNorm +] rotation of one head row held as (lo, hi) vectors; returns the rotated words.
+    auto norm_rotate = [&](const uint4& lo_v, const uint4& hi_v, const void* norm_w, uint4& out_lo, uint4& out_hi) {
+        const uint32_t lw[4] = {lo_v.x, lo_v.y, lo_v.z, lo_v.w}, hw[4] = {hi_v.x, hi_v.y, hi_v.z, hi_v.w};
+        float2 a2[4], b2[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            a2[k] = bf2_to_f2(lw[k]);
+            b2[k] = bf2_to_f2(hw[k]);
+        }
+        if constexpr (kNorm) {
+            float ss_lo = 0.0f, ss_hi = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                ss_lo = __fmaf_rn(a2[k].x, a2[k].x, ss_lo);
+                ss_lo = __fmaf_rn(a2[k].y, a2[k].y, ss_lo);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                ss_hi = __fmaf_rn(b2[k].x, b2[k].x, ss_hi);
+                ss_hi = __fmaf_rn(b2[k].y, b2[k].y, ss_hi);
+            }
+            const float total = group_sum<kLanesPerHead>(ss_lo + ss_hi);
+            const float2 rrms = splat2(rsqrtf(total / static_cast<float>(D) + p.eps));
+            const uint4 gl = ld_weight(static_cast<const uint4*>(norm_w) + sub);
+            const uint4 gh = ld_weight(static_cast<const uint4*>(norm_w) + sub + kLanesPerHead);
+            const uint32_t glw[4] = {gl.x, gl.y, gl.z, gl.w}, ghw[4] = {gh.x, gh.y, gh.z, gh.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {   // bf16((h * rrms) * g), as the stored tensor the rotation reads
+                const float2 ya = mul2_rn(mul2_rn(a2[k], rrms), bf2_to_f2(glw[k]));
+                const float2 yb = mul2_rn(mul2_rn(b2[k], rrms), bf2_to_f2(ghw[k]));
+                a2[k] = bf2_to_f2(pack_bf16x2(ya.x, ya.y));
+                b2[k] = bf2_to_f2(pack_bf16x2(yb.x, yb.y));
+            }
+        }
+        uint32_t ol[4], oh[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 lo2 = fma2_rn(a2[k], c2[k], mul2_rn(b2[k], ns2[k]));
+            const float2 hi2 = fma2_rn(a2[k], s2[k], mul2_rn(b2[k], c2[k]));
+            ol[k] = pack_bf16x2(lo2.x, lo2.y);
+            oh[k] = pack_bf16x2(hi2.x, hi2.y);
+        }
+        out_lo = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+        out_hi = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+    };
+
+    // FP8 append of one head row (packed bf16 words) at destination row dst_row.
+    auto append_fp8 = [&](const uint4& lo_v, const uint4& hi_v, uint8_t* cache, float* scale, long long dst_row) {
+        const uint32_t w[8] = {lo_v.x, lo_v.y, lo_v.z, lo_v.w, hi_v.x, hi_v.y, hi_v.z, hi_v.w};
+        __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[0]));
+#pragma unroll
+        for (int k = 1; k < 8; ++k) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[k])));   // skips NaN like fmaxf
+        const uint32_t mw = *reinterpret_cast<const uint32_t*>(&m);
+        float amax = fmaxf(fmaxf(bf_lo(mw), bf_hi(mw)), 0.0f);
+        amax = group_max<kLanesPerHead>(amax);
+        const float2 inv2 = splat2(quant_inv_scale<448>(amax));
+        if (sub == 0) scale[dst_row] = quant_scale<448>(amax);
+        uint32_t c[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 p0 = mul2_rn(bf2_to_f2(w[2 * k]), inv2), p1 = mul2_rn(bf2_to_f2(w[2 * k + 1]), inv2);
+            c[k] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(p0, __NV_SATFINITE, __NV_E4M3)) |
+                   (static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(p1, __NV_SATFINITE, __NV_E4M3)) << 16);
+        }
+        uint2* dst = reinterpret_cast<uint2*>(cache + static_cast<size_t>(dst_row) * D);
+        st_vec8(dst + sub, make_uint2(c[0], c[1]));
+        st_vec8(dst + sub + kLanesPerHead, make_uint2(c[2], c[3]));
+    };
+
+    // One loop over the chunk's groups; the role of a group is warp-uniform.  Loads run kAhead groups
+    // ahead of the arithmetic so that a warp keeps (kAhead + 1) KB in flight.
+    constexpr int kAhead = 2;
+    auto group_src = [&](int g) -> const uint4* {
+        const int h = hslot;
+        if (g < gq) return static_cast<const uint4*>(p.q) + (static_cast<size_t>(token) * Hq + g * kHeadsPerGroup + h) * kVecsPerRow;
+        if (g < gq + gk)
+            return static_cast<const uint4*>(p.k_in) + (static_cast<size_t>(token) * Hkv + (g - gq) * kHeadsPerGroup + h) * kVecsPerRow;
+        return static_cast<const uint4*>(p.v_in) + (static_cast<size_t>(token) * Hkv + (g - gq - gk) * kHeadsPerGroup + h) * kVecsPerRow;
+    };
+    uint4 lo_q[kAhead + 1], hi_q[kAhead + 1];
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) {
+        if (g_begin + k < g_end) {
+            const uint4* src = group_src(g_begin + k);
+            lo_q[k] = ld_stream(src + sub);
+            hi_q[k] = ld_stream(src + sub + kLanesPerHead);
+        }
+    }
+    for (int g0 = g_begin; g0 < g_end; g0 += kAhead + 1) {
+#pragma unroll
+        for (int k = 0; k <= kAhead; ++k) {          // register ring: slot k holds group g0 + k
+            const int g = g0 + k;
+            if (g < g_end) {
+                if (g + kAhead < g_end) {
+                    const uint4* src = group_src(g + kAhead);
+                    lo_q[(k + kAhead) % (kAhead + 1)] = ld_stream(src + sub);
+                    hi_q[(k + kAhead) % (kAhead + 1)] = ld_stream(src + sub + kLanesPerHead);
+                }
+                const uint4 lo_v = lo_q[k], hi_v = hi_q[k];
+                if (g < gq) {                            // Q: rotate in place
+                    uint4* rowp = static_cast<uint4*>(p.q) + (static_cast<size_t>(token) * Hq + g * kHeadsPerGroup + hslot) * kVecsPerRow;
+                    uint4 out_lo, out_hi;
+                    norm_rotate(lo_v, hi_v, p.q_norm, out_lo, out_hi);
+                    st_vec(rowp + sub, out_lo);
+                    st_vec(rowp + sub + kLanesPerHead, out_hi);
+                } else if (g < gq + gk) {                // K: rotate, optional bf16 write-back, FP8 append
+                    const size_t row = static_cast<size_t>(token) * Hkv + (g - gq) * kHeadsPerGroup + hslot;
+                    uint4 out_lo, out_hi;
+                    norm_rotate(lo_v, hi_v, p.k_norm, out_lo, out_hi);
+                    if (p.k_out != nullptr) {
+                        uint4* dst = static_cast<uint4*>(p.k_out) + row * kVecsPerRow;
+                        st_vec(dst + sub, out_lo);
+                        st_vec(dst + sub + kLanesPerHead, out_hi);
+                    }
+                    if constexpr (kKV) append_fp8(out_lo, out_hi, p.k_cache, p.k_scale, static_cast<long long>(row) + slot_base);
+                } else if constexpr (kKV) {              // V: FP8 append only
+                    const size_t row = static_cast<size_t>(token) * Hkv + (g - gq - gk) * kHeadsPerGroup + hslot;
+                    append_fp8(lo_v, hi_v, p.v_cache, p.v_scale, static_cast<long long>(row) + slot_base);
+                }
+            }
+        }
+    }
+}
+
 // Any even head_dim <= 256 that is not a multiple of 16: one thread per rotation pair.
 __global__ void rope_generic_kernel(__nv_bfloat16* q, __nv_bfloat16* k, const int* positions,
                                     const float* inv_freq, long long total_pairs, int num_q_heads,
@@ -243,12 +411,23 @@ int launch_rope(RopeArgs p, bool norm, bool kv, cudaStream_t stream) {
     const long long grid = (items + warps - 1) / warps;
     RH_REQUIRE(grid <= 0x7fffffffLL, RH_ERR_UNSUPPORTED_DIM, "rope: too many rows for one launch");
     const unsigned g = static_cast<unsigned>(grid), b = static_cast<unsigned>(warps * 32);
-    if (kv) {
-        if (norm) rope_kv_kernel<D, true, true><<<g, b, 0, stream>>>(p);
-        else rope_kv_kernel<D, false, true><<<g, b, 0, stream>>>(p);
+    const bool aligned = p.num_q_heads % kHeadsPerGroup == 0 && p.num_kv_heads % kHeadsPerGroup == 0;
+    if (aligned) {
+        if (kv) {
+            if (norm) rope_kv_kernel<D, true, true><<<g, b, 0, stream>>>(p);
+            else rope_kv_kernel<D, false, true><<<g, b, 0, stream>>>(p);
+        } else {
+            if (norm) rope_kv_kernel<D, true, false><<<g, b, 0, stream>>>(p);
+            else rope_kv_kernel<D, false, false><<<g, b, 0, stream>>>(p);
+        }
     } else {
-        if (norm) rope_kv_kernel<D, true, false><<<g, b, 0, stream>>>(p);
-        else rope_kv_kernel<D, false, false><<<g, b, 0, stream>>>(p);
+        if (kv) {
+            if (norm) rope_kv_generic_kernel<D, true, true><<<g, b, 0, stream>>>(p);
+            else rope_kv_generic_kernel<D, false, true><<<g, b, 0, stream>>>(p);
+        } else {
+            if (norm) rope_kv_generic_kernel<D, true, false><<<g, b, 0, stream>>>(p);
+            else rope_kv_generic_kernel<D, false, false><<<g, b, 0, stream>>>(p);
+        }
     }
     return host::check_launch("rope_kv_kernel");
 }

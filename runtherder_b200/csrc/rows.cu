@@ -76,10 +76,13 @@ __device__ __forceinline__ RowCtx make_ctx(const RowArgs& a) {
 
 // Everything that happens to one row once its vectors sit in registers (xv, rv): h, h_out, the
 // sum of squares and rrms, y, amax, codes and scale.  Shared by the direct-load and the staged kernel.
-template <int VPT, unsigned F, bool kStaged>
+// kSmemH: the fp32 row h is parked in shared memory between the two passes instead of in 8*VPT
+// registers per thread (layout [slot][half][thread] float4: conflict-free), which buys a resident CTA.
+template <int VPT, unsigned F, bool kStaged, bool kSmemH = false>
 __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, long long row, int parity,
                                             const uint4 (&xv)[VPT], const uint4 (&rv)[VPT], const uint4 (&gw)[VPT],
-                                            float (&s_ss)[2][kRowWarps], float (&s_mx)[2][kRowWarps]) {
+                                            float (&s_ss)[2][kRowWarps], float (&s_mx)[2][kRowWarps],
+                                            float4* s_h = nullptr) {
     constexpr bool kNorm = (F & kFNorm) != 0, kAdd = (F & kFAdd) != 0, kStoreY = (F & kFStoreY) != 0;
     constexpr bool kInt8 = (F & kFInt8) != 0, kFp8 = (F & kFFp8) != 0, kQuant = kInt8 || kFp8;
     const int tid = c.tid, lane = c.lane, warp = c.warp, n_vecs = c.n_vecs;
@@ -88,15 +91,16 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
     uint32_t yw[VPT][4];  // the row as the next kernel would read it back: packed bf16
 
     if constexpr (kNorm) {
-        float h[VPT][8];
+        float h[kSmemH ? 1 : VPT][8];
         float ss = 0.0f;
 #pragma unroll
-        for (int s = 0; s < VPT; ++s) {
-            const int i = tid + s * kRowThreads;
+        for (int s0 = 0; s0 < VPT; ++s0) {
+            const int s = kSmemH ? 0 : s0;           // register slot
+            const int i = tid + s0 * kRowThreads;
             if (i < n_vecs) {
                 if constexpr (kAdd) {
-                    const uint32_t xw[4] = {xv[s].x, xv[s].y, xv[s].z, xv[s].w};
-                    const uint32_t rw[4] = {rv[s].x, rv[s].y, rv[s].z, rv[s].w};
+                    const uint32_t xw[4] = {xv[s0].x, xv[s0].y, xv[s0].z, xv[s0].w};
+                    const uint32_t rw[4] = {rv[s0].x, rv[s0].y, rv[s0].z, rv[s0].w};
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const float2 hh = add2_rn(bf2_to_f2(xw[k]), bf2_to_f2(rw[k]));
@@ -105,10 +109,14 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
                     }
                     st_vec(static_cast<uint4*>(a.h_out) + row_off + i, pack8(h[s]));
                 } else {
-                    unpack8(xv[s], h[s]);
+                    unpack8(xv[s0], h[s]);
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) ss = __fmaf_rn(h[s][j], h[s][j], ss);
+                if constexpr (kSmemH) {
+                    s_h[(s0 * 2 + 0) * kRowThreads + tid] = make_float4(h[0][0], h[0][1], h[0][2], h[0][3]);
+                    s_h[(s0 * 2 + 1) * kRowThreads + tid] = make_float4(h[0][4], h[0][5], h[0][6], h[0][7]);
+                }
             }
         }
         ss = group_sum<32>(ss);
@@ -121,9 +129,18 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
             const int i = tid + s * kRowThreads;
             if (i < n_vecs) {
                 const uint32_t gws[4] = {gw[s].x, gw[s].y, gw[s].z, gw[s].w};
+                float hv[8];
+                if constexpr (kSmemH) {   // each thread reads back exactly what it wrote: no barrier needed
+                    const float4 lo = s_h[(s * 2 + 0) * kRowThreads + tid], hi = s_h[(s * 2 + 1) * kRowThreads + tid];
+                    hv[0] = lo.x; hv[1] = lo.y; hv[2] = lo.z; hv[3] = lo.w;
+                    hv[4] = hi.x; hv[5] = hi.y; hv[6] = hi.z; hv[7] = hi.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) hv[j] = h[s][j];
+                }
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {   // y = (h * rrms) * g, two elements per instruction
-                    const float2 t = mul2_rn(make_float2(h[s][2 * k], h[s][2 * k + 1]), splat2(rrms));
+                    const float2 t = mul2_rn(make_float2(hv[2 * k], hv[2 * k + 1]), splat2(rrms));
                     const float2 yf = mul2_rn(t, bf2_to_f2(gws[k]));
                     yw[s][k] = pack_bf16x2(yf.x, yf.y);
                 }
@@ -203,11 +220,12 @@ __device__ __forceinline__ void load_gains(const RowArgs& a, int n_vecs, uint4 (
 }
 
 // Direct-load kernel: each thread loads its vectors of the row straight into registers.
-template <int VPT, unsigned F>
-__global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
+template <int VPT, unsigned F, bool kSmemH = false>
+__global__ void __launch_bounds__(kRowThreads, (kSmemH ? 4 : ((F & kFNorm) == 0 ? (VPT <= 2 ? 6 : 2) : (VPT <= 2 ? 3 : 1)))) rows_kernel(const RowArgs a) {
     constexpr bool kAdd = (F & kFAdd) != 0;
     __shared__ float s_ss[2][kRowWarps];
     __shared__ float s_mx[2][kRowWarps];
+    __shared__ float4 s_h[kSmemH ? VPT * 2 * kRowThreads : 1];
     const RowCtx c = make_ctx<F>(a);
     uint4 gw[VPT];
     load_gains<VPT, F>(a, c.n_vecs, gw);
@@ -224,7 +242,7 @@ __global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
                 if constexpr (kAdd) rv[s] = ld_stream(static_cast<const uint4*>(a.residual) + row_off + i);
             }
         }
-        process_row<VPT, F, false>(a, c, row, parity, xv, rv, gw, s_ss, s_mx);
+        process_row<VPT, F, false, kSmemH>(a, c, row, parity, xv, rv, gw, s_ss, s_mx, s_h);
     }
 }
 
@@ -236,7 +254,7 @@ __global__ void __launch_bounds__(kRowThreads) rows_kernel(const RowArgs a) {
 constexpr int kSlotBytes = kRowThreads * 16;
 
 template <int VPT, unsigned F>
-__global__ void __launch_bounds__(kRowThreads + 32) rows_staged_kernel(const RowArgs a, const int stages) {
+__global__ void __launch_bounds__(kRowThreads + 32) rows_staged_kernel(const RowArgs a, const int stages, int* error_word) {
     constexpr bool kAdd = (F & kFAdd) != 0;
     constexpr int kOps = kAdd ? 2 : 1;
     extern __shared__ __align__(128) unsigned char ring[];
@@ -263,7 +281,7 @@ __global__ void __launch_bounds__(kRowThreads + 32) rows_staged_kernel(const Row
             for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x) {
                 const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(n_vecs);
                 for (int sl = 0; sl < slots_per_row; ++sl) {
-                    if (round > 0 && !pipe::mbar_wait(empty + s, (round - 1) & 1, __LINE__)) return;
+                    if (round > 0 && !pipe::mbar_wait(empty + s, (round - 1) & 1, __LINE__, error_word)) return;
                     const int vec0 = sl * kRowThreads;
                     const uint32_t bytes = static_cast<uint32_t>(min(kRowThreads, n_vecs - vec0)) * 16u;
                     unsigned char* dst = ring + static_cast<size_t>(s) * kOps * kSlotBytes;
@@ -289,7 +307,7 @@ __global__ void __launch_bounds__(kRowThreads + 32) rows_staged_kernel(const Row
 #pragma unroll
         for (int sl = 0; sl < VPT; ++sl) {
             if (sl < slots_per_row) {
-                if (!pipe::mbar_wait(full + s, phase, __LINE__)) return;
+                if (!pipe::mbar_wait(full + s, phase, __LINE__, error_word)) return;
                 const unsigned char* src = ring + static_cast<size_t>(s) * kOps * kSlotBytes + c.tid * 16;
                 if (c.tid + sl * kRowThreads < c.n_vecs) {
                     xv[sl] = *reinterpret_cast<const uint4*>(src);
@@ -403,11 +421,20 @@ void launch_long(const RowArgs& a, cudaStream_t stream) {
         const int tuned = host::tuning(host::kRowsCtasPerSm);
         const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
         const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-        rows_staged_kernel<VPT, F><<<grid, kRowThreads + 32, smem, stream>>>(a, stages);
+        rows_staged_kernel<VPT, F><<<grid, kRowThreads + 32, smem, stream>>>(a, stages, host::device_error_word());
         return;
     }
-    static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F>), kRowThreads);
     const int tuned = host::tuning(host::kRowsCtasPerSm);
+    if constexpr ((F & kFNorm) != 0 && VPT <= 4) {   // 8 KB of shared memory per slot: up to 32 KB static
+        if (host::tuning(host::kRowsSmemH) != 1) {   // rh_tune("rows_smem_h", 1) keeps h in registers
+            static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F, true>), kRowThreads);
+            const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
+            const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
+            rows_kernel<VPT, F, true><<<grid, kRowThreads, 0, stream>>>(a);
+            return;
+        }
+    }
+    static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F>), kRowThreads);
     const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
     const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
     rows_kernel<VPT, F><<<grid, kRowThreads, 0, stream>>>(a);

@@ -69,3 +69,19 @@ def test_decode_chain_in_cuda_graph_tracks_position():
             assert bits_equal(kc, o["k_cache"][pos]) and bits_equal(ks, o["k_scale"][pos])
             assert bits_equal(q, i["q"]) and bits_equal(qm, o["q_mlp"])
             assert bool(o["k_scale"][pos].abs().sum() > 0)
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """Failure detection without a fault: a wait on a barrier nothing completes runs out after its poll
+    limit, the kernel returns normally, the error word says where, and the context keeps working."""
+    import ctypes as C
+    from runtherder_b200 import _lib
+    gave_up, err = C.c_int(-1), C.c_int(-1)
+    _lib.call("rh_selfcheck_bounded_wait", 64, C.byref(gave_up), C.byref(err))
+    assert gave_up.value == 1
+    assert err.value != 0 and (err.value & 0xff) == 1 and (err.value >> 8) > 0    # (source line << 8) | code
+    after = C.c_int(-1)
+    _lib.call("rh_device_error", C.byref(after))
+    assert after.value == 0                                                        # sticky word restored
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum()) == 16.0                                            # context still usable
