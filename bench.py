@@ -32,6 +32,10 @@ sys.path.insert(0, str(ROOT))
 METRIC = "fused-layer-op HBM GB/s"
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum per token row of each step kernel, from the ncu capture
+# summarised in profiles/c4_step_kernels_ncu_16384rows.md (16384-row case; rows are independent units,
+# so a launch's traffic is this figure times its rows).
+DRAM_TRAFFIC_BYTES_PER_ROW = {"embedding": 13070, "norm_quant": 25353, "rope_kv": 19116, "swiglu_quant": 70759}
 
 
 def parse_args():
@@ -46,6 +50,8 @@ def parse_args():
     p.add_argument("--no-cpu", action="store_true")
     p.add_argument("--no-refcuda", action="store_true")
     p.add_argument("--cpu-seconds", type=float, default=15.0)
+    p.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
+                   help="layer-chain configs: replay the forward from a CUDA graph (auto: on for the decode config)")
     return p.parse_args()
 
 
@@ -264,6 +270,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep stdout for the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -277,6 +284,13 @@ def main():
         t = torch.tensor([x], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.config != "c4":
+        run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     T = cfg.tokens
     b, e = shard_bounds(T, world, rank)
@@ -333,14 +347,8 @@ def main():
     dom = max(range(4), key=lambda j: op_ms[j])
     dom_name, dom_bpr = ops[dom]
     achieved = rows * dom_bpr / (op_ms[dom] * 1e-3) / 1e9
-    traffic_file = ROOT / "profiles" / "dram_traffic.json"
-    traffic = None
-    if traffic_file.exists():
-        try:
-            per_row_traffic = json.loads(traffic_file.read_text()).get(dom_name, {}).get("dram_bytes_per_row")
-            traffic = None if per_row_traffic is None else per_row_traffic * rows
-        except Exception:
-            traffic = None
+    traffic = DRAM_TRAFFIC_BYTES_PER_ROW.get(dom_name)
+    traffic = None if traffic is None or args.config != "c4" else traffic * rows
     roofline = {"bound": "hbm", "kernel": dom_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": traffic,
                 "algorithmic_bytes_per_launch": rows * dom_bpr}
@@ -377,6 +385,169 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
+    """Configs c0-c3: a step is one forward's worth of the per-layer op chain — the embedding gather, then
+    `layers` x (fused norm[+INT8], RoPE[+QK-norm]+FP8 KV append, [INT8 of the attention output,] fused
+    norm[+INT8], SwiGLU[+INT8]) — on rotating buffer sets (distinct memory per layer up to ~2 GB, never
+    fewer than two sets) so a layer does not find its inputs in L2 from the previous one.  Timed eagerly
+    and, for the decode config, as one CUDA graph.  The reference's own CUDA kernels run the same forward
+    through the reference's call sequence (13 launches per W8A8 layer) for comparison."""
+    import torch
+    from runtherder_b200 import layer_ops, synth
+    from runtherder_b200.sharding import shard_bounds
+
+    T, L = cfg.tokens, cfg.layers
+    b, e = shard_bounds(T, world, rank)
+    rows = e - b
+    if rows == 0:
+        raise SystemExit(f"{cfg.name}: fewer rows than ranks")
+    per_row = cfg.chain_bytes_per_row()
+    layer_bytes = per_row * rows * 2.2            # inputs + outputs + scratch, roughly
+    n_sets = int(min(L, max(2, 2e9 // max(layer_bytes, 1))))
+    sub = cfg.with_tokens(rows, start_pos=cfg.start_pos)
+    ins = [synth.make_inputs(sub, rows=rows, row_offset=b + i * 7, device=dev, with_table=(i == 0)) for i in range(n_sets)]
+    slots = cfg.cache_slots
+    outs = [layer_ops.alloc_outputs(cfg, rows, device=dev, slots=slots) for _ in range(n_sets)]
+    for o in outs:
+        o["at_pos"].fill_(cfg.start_pos + b)
+    for i in ins:
+        i["positions"] = torch.arange(cfg.start_pos + b, cfg.start_pos + e, dtype=torch.int32, device=dev)
+
+    def forward():
+        n = 0
+        for l in range(L):
+            n += layer_ops.fused_layer_step(cfg, ins[l % n_sets], outs[l % n_sets], with_embedding=(l == 0))
+        return n
+
+    use_graph = args.graph == "on" or (args.graph == "auto" and cfg.tokens == 1)
+    launches_per_step = forward()
+    torch.cuda.synchronize()
+    graph = None
+    if use_graph:
+        side = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(side):
+            forward()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                forward()
+        torch.cuda.synchronize()
+    step = graph.replay if graph is not None else forward
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    K = args.steps
+    barrier()
+    a, bb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index or 0) as clocks:
+        a.record()
+        for _ in range(K):
+            step()
+        bb.record()
+        torch.cuda.synchronize()
+    ms = max_over_ranks(a.elapsed_time(bb)) / K
+    barrier()
+
+    peak, peak_kind = measured_peak()
+    total_bytes = per_row * T * L + cfg.bytes_embedding() * T
+    value = total_bytes / (ms * 1e-3) / 1e9
+    line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 in, fp32 math, " + ("int8/fp8-e4m3 out" if cfg.int8 else "bf16/fp8-e4m3 out"),
+            "data": "synthetic", "token_rows_per_s": round(T / (ms * 1e-3), 1), "us_per_layer": round(ms * 1e3 / L, 3),
+            "frac_of_hbm_peak": {peak_kind: round(value / (peak * world), 4)},
+            "config": {"workload": cfg.name, "token_rows": T, "rows_per_gpu": rows, "layers": L, "hidden": cfg.hidden,
+                       "inter": cfg.inter, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
+                       "int8": cfg.int8, "qk_norm": cfg.qk_norm, "start_pos": cfg.start_pos, "seed": cfg.seed,
+                       "ops_per_layer": [n for n, _ in cfg.chain_ops()], "algorithmic_bytes_per_row_per_layer": per_row,
+                       "buffer_sets": n_sets, "cuda_graph": graph is not None, "parallelism": f"rows/{world}",
+                       "l2": f"{n_sets} rotating buffer sets; a set is {'larger' if layer_bytes > 126e6 else 'smaller'} than the 126 MB L2"},
+            "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "clocks": clocks.summary()}
+
+    # per-kernel roofline from a separate event pass over one layer (not part of the timed region)
+    try:
+        line["roofline"] = chain_roofline(cfg, ins[0], outs[0], rows, peak, peak_kind)
+    except Exception as exc:
+        line["roofline"] = {"unavailable": str(exc)[:200]}
+
+    if world == 1 and not args.no_refcuda:
+        try:
+            line["ref_cuda"] = time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph, max(3, min(K, 20)))
+        except Exception as exc:
+            line["ref_cuda"] = {"unavailable": str(exc)[:200]}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def chain_roofline(cfg, i, o, rows, peak, peak_kind):
+    import torch
+    from runtherder_b200 import kernels as Kn
+    H = cfg.hidden
+    if cfg.int8:
+        name, bpr = "swiglu_quant", cfg.bytes_swiglu_quant()
+        fn = lambda: Kn.swiglu_quant_int8(o["q_mlp"], o["s_mlp"], None, i["gate"], i["up"], rows, cfg.inter)
+    else:
+        name, bpr = "swiglu", cfg.bytes_swiglu()
+        fn = lambda: Kn.swiglu_bf16_forward(o["mlp_act"], i["gate"], i["up"], rows * cfg.inter)
+    for _ in range(3):
+        fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 20
+    achieved = rows * bpr / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+            "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None, "us_per_launch": round(ms * 1e3, 2),
+            "note": "back-to-back launches on one buffer set" + ("" if rows * bpr > 126e6 else " that fits in L2: latency-bound, not an HBM figure")}
+
+
+def time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph, reps):
+    import torch
+    sys.path.insert(0, str(ROOT / "tests"))
+    from gpu_util import RefCuda
+    from runtherder_b200 import layer_ops
+    ref = RefCuda()
+    scratch = {"normed": torch.empty_like(ins[0]["x"]), "ffn_normed": torch.empty_like(ins[0]["x"]),
+               "act": torch.empty_like(ins[0]["gate"])}
+    out = {}
+    for label, dedup in (("as_issued", False), ("dedup", True)):
+        def forward():
+            n = 1
+            ref.embedding_lookup_bf16_forward(outs[0]["emb"], ins[0]["table"], ins[0]["ids"], rows, cfg.hidden)
+            for l in range(L):
+                n += layer_ops.reference_sequence(ref, cfg, ins[l % n_sets], outs[l % n_sets], scratch, dedup_quant=dedup)
+            return n
+        n = forward()
+        torch.cuda.synchronize()
+        step = forward
+        if use_graph:
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                forward()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    forward()
+            torch.cuda.synchronize()
+            step = g.replay
+        for _ in range(3):
+            step()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        out[label] = {"ms_per_step": round(ms, 4), "launches_per_step": n, "value": round(total_bytes / (ms * 1e-3) / 1e9, 1),
+                      "unit": "GB/s (same algorithmic bytes)"}
+    out["what"] = "reference src/kernels/*.cu compiled for sm_100a through the reference's call sequence, same buffers"
+    return out
 
 
 def time_reference_cuda(cfg, ins, outs, rows, per_row, reps):

@@ -5,7 +5,8 @@
 // consumer warp's dependency chain.
 //
 // Rules kept here:
-//  * plain (non-multicast) bulk copies of this GPU's own memory, no cluster launch;
+//  * plain one-destination bulk copies of this GPU's own memory into this CTA's shared memory, no
+//    cluster launch;
 //  * source address, destination address and size are multiples of 16 bytes;
 //  * every wait is bounded: after kSpinLimit failed polls the waiter records an error in the
 //    library's per-device error word (passed to the kernel) and gives up, so a kernel can never spin

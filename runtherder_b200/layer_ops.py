@@ -108,13 +108,15 @@ def reference_sequence(api, cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dic
             api.quantize_per_token_int8(dst_q, dst_s, src, T, k, stream)
             n += 1
 
-    api.rmsnorm_add_bf16_forward(scratch["normed"], o["h_attn"], i["x"], i["residual"], i["g_attn"], T, H, cfg.eps,
-                                 stream)
+    # bf16 models keep the normalised rows (they feed the bf16 GEMMs); W8A8 models only need them as the
+    # quantiser's input
+    normed = scratch["normed"] if cfg.int8 else o["normed"]
+    ffn_normed = scratch["ffn_normed"] if cfg.int8 else o["ffn_normed"]
+    act = scratch["act"] if cfg.int8 else o["mlp_act"]
+    api.rmsnorm_add_bf16_forward(normed, o["h_attn"], i["x"], i["residual"], i["g_attn"], T, H, cfg.eps, stream)
     n += 1
     if cfg.int8:
-        quant(o["q_attn_in"], o["s_attn_in"], scratch["normed"], H, 3)
-    else:
-        o["normed"].copy_(scratch["normed"])
+        quant(o["q_attn_in"], o["s_attn_in"], normed, H, 3)
     if cfg.qk_norm:
         api.rmsnorm_bf16_forward(i["q"], i["q"], i["q_norm"], T * cfg.q_heads, D, cfg.eps, stream)
         api.rmsnorm_bf16_forward(i["k"], i["k"], i["k_norm"], T * cfg.kv_heads, D, cfg.eps, stream)
@@ -125,17 +127,12 @@ def reference_sequence(api, cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dic
     n += 3
     if cfg.int8:
         quant(o["q_attn_out"], o["s_attn_out"], i["attn"], cfg.q_dim, 1)
-    api.rmsnorm_add_bf16_forward(scratch["ffn_normed"], o["h_ffn"], i["x"], o["h_attn"], i["g_ffn"], T, H, cfg.eps,
-                                 stream)
+    api.rmsnorm_add_bf16_forward(ffn_normed, o["h_ffn"], i["x"], o["h_attn"], i["g_ffn"], T, H, cfg.eps, stream)
     n += 1
     if cfg.int8:
-        quant(o["q_ffn_in"], o["s_ffn_in"], scratch["ffn_normed"], H, 2)
-    else:
-        o["ffn_normed"].copy_(scratch["ffn_normed"])
-    api.swiglu_bf16_forward(scratch["act"], i["gate"], i["up"], T * I, stream)
+        quant(o["q_ffn_in"], o["s_ffn_in"], ffn_normed, H, 2)
+    api.swiglu_bf16_forward(act, i["gate"], i["up"], T * I, stream)
     n += 1
     if cfg.int8:
-        quant(o["q_mlp"], o["s_mlp"], scratch["act"], I, 1)
-    else:
-        o["mlp_act"].copy_(scratch["act"])
+        quant(o["q_mlp"], o["s_mlp"], act, I, 1)
     return n
