@@ -121,6 +121,12 @@ __device__ __forceinline__ uint32_t max_nan_bf16x2(uint32_t a, uint32_t b) {
     __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
 }
+// m = max(m, |w|) on both halves, NaN-propagating; written with the intrinsics so the absolute value
+// can ride on the max instruction as an operand modifier.
+__device__ __forceinline__ uint32_t amax_acc_bf16x2(uint32_t m, uint32_t w) {
+    __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&m), __habs2(*reinterpret_cast<__nv_bfloat162*>(&w)));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
 
 // INT8 code of p = y*inv without the conversion unit: adding 1.5*2^23 leaves
 // round_half_even(p) in the low mantissa byte (two's complement).  |p| <= 127.0001 for a
@@ -201,8 +207,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 template <int kSteps>
 __device__ __forceinline__ float2 sigmoid2(float2 g) {
     const float2 t = mul2_rn(g, splat2(-1.4426950408889634f));
-    const float2 d = add2_rn(make_float2(ex2_approx(t.x), ex2_approx(t.y)), splat2(1.0f));
-    const float2 nd = neg2(d);
+    const float2 e = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+    const float2 d = add2_rn(e, splat2(1.0f));
+    const float2 nd = fma2_rn(e, splat2(-1.0f), splat2(-1.0f));   // -(e + 1): one paired op instead of two negations
     float2 r = make_float2(rcp_approx(d.x), rcp_approx(d.y));
     r = fma2_rn(r, fma2_rn(nd, r, splat2(1.0f)), r);
     if (kSteps >= 2) r = fma2_rn(fma2_rn(nd, r, splat2(1.0f)), r, r);

@@ -164,7 +164,7 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
             const int i = tid + s * kRowThreads;
             if (i < n_vecs) {
 #pragma unroll
-                for (int w = 0; w < 4; ++w) m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s][w]));
+                for (int w = 0; w < 4; ++w) m2 = amax_acc_bf16x2(m2, yw[s][w]);
             }
         }
         const float m_lo = bf_lo(m2), m_hi = bf_hi(m2);
@@ -254,14 +254,16 @@ __global__ void __launch_bounds__(kRowThreads, (kSmemH ? 4 : ((F & kFNorm) == 0 
 constexpr int kSlotBytes = kRowThreads * 16;
 
 template <int VPT, unsigned F>
-__global__ void __launch_bounds__(kRowThreads + 32) rows_staged_kernel(const RowArgs a, const int stages, int* error_word) {
-    constexpr bool kAdd = (F & kFAdd) != 0;
+__global__ void __launch_bounds__(kRowThreads + 32, ((F & kFNorm) != 0 ? 4 : 1))
+rows_staged_kernel(const RowArgs a, const int stages, int* error_word) {
+    constexpr bool kAdd = (F & kFAdd) != 0, kSmemH = (F & kFNorm) != 0;
     constexpr int kOps = kAdd ? 2 : 1;
     extern __shared__ __align__(128) unsigned char ring[];
     uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(stages) * kOps * kSlotBytes);
     uint64_t* empty = full + stages;
     __shared__ float s_ss[2][kRowWarps];
     __shared__ float s_mx[2][kRowWarps];
+    __shared__ float4 s_h[kSmemH ? VPT * 2 * kRowThreads : 1];
 
     const int n_vecs = a.dim / kVec;
     const int slots_per_row = (n_vecs + kRowThreads - 1) / kRowThreads;
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(kRowThreads + 32) rows_staged_kernel(const Row
                 if (++s == stages) { s = 0; phase ^= 1; }
             }
         }
-        process_row<VPT, F, true>(a, c, row, parity, xv, rv, gw, s_ss, s_mx);
+        process_row<VPT, F, true, kSmemH>(a, c, row, parity, xv, rv, gw, s_ss, s_mx, s_h);
     }
 }
 

@@ -46,6 +46,35 @@ __device__ __forceinline__ uint4 swiglu8(const uint4& gv, const uint4& uv) {
     return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
+// Fused kernels hoist the range check out of the per-vector path: they always take the refined
+// reciprocal, track the smallest gate a thread has seen (one packed min per word), and only a thread
+// that met a gate below kGateExactBelow recomputes its vectors with the verbatim expression.
+template <int kSteps>
+__device__ __forceinline__ uint4 swiglu8_unchecked(const uint4& gv, const uint4& uv) {
+    if constexpr (kSteps == 0) return swiglu8<0>(gv, uv);
+    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 g = bf2_to_f2(gw[k]), u = bf2_to_f2(uw[k]);
+        const float2 y = mul2_rn(mul2_rn(g, sigmoid2<(kSteps == 0 ? 1 : kSteps)>(g)), u);
+        out[k] = pack_bf16x2(y.x, y.y);
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+}
+constexpr uint32_t kGateMinInit = 0x7f807f80u;   // +Inf, +Inf
+__device__ __forceinline__ uint32_t gate_min_acc(uint32_t m, const uint4& gv) {
+    __nv_bfloat162 r = *reinterpret_cast<__nv_bfloat162*>(&m);
+    r = __hmin2(r, *reinterpret_cast<const __nv_bfloat162*>(&gv.x));
+    r = __hmin2(r, *reinterpret_cast<const __nv_bfloat162*>(&gv.y));
+    r = __hmin2(r, *reinterpret_cast<const __nv_bfloat162*>(&gv.z));
+    r = __hmin2(r, *reinterpret_cast<const __nv_bfloat162*>(&gv.w));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ bool gate_min_needs_exact(uint32_t m) {
+    return fminf(bf_lo(m), bf_hi(m)) < kGateExactBelow;
+}
+
 constexpr int kElemThreads = 256;
 constexpr int kElemUnroll = 4;
 
@@ -89,7 +118,7 @@ swiglu_quant_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y
         // Two slots (four 128-bit loads) are in flight per thread at a time; the products are
         // kept packed, so a 14336-wide row costs 16 registers per thread at 512 threads.
         uint4 yw[VPT];
-        uint32_t m2 = 0u;
+        uint32_t m2 = 0u, gmin = kGateMinInit;
 #pragma unroll
         for (int s0 = 0; s0 < VPT; s0 += 2) {
             uint4 gv[2], uv[2];
@@ -106,15 +135,31 @@ swiglu_quant_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y
                 const int s = s0 + k;
                 const int i = tid + s * kThreads;
                 if (s < VPT && i < n_vecs) {
-                    yw[s] = swiglu8<kSteps>(gv[k], uv[k]);
+                    gmin = gate_min_acc(gmin, gv[k]);
+                    yw[s] = swiglu8_unchecked<kSteps>(gv[k], uv[k]);
                     if constexpr (kStoreY) st_vec(static_cast<uint4*>(y) + row_off + i, yw[s]);
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s].x));
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s].y));
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s].z));
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[s].w));
+                    m2 = amax_acc_bf16x2(m2, yw[s].x);
+                    m2 = amax_acc_bf16x2(m2, yw[s].y);
+                    m2 = amax_acc_bf16x2(m2, yw[s].z);
+                    m2 = amax_acc_bf16x2(m2, yw[s].w);
                 }
             }
             asm volatile("" ::: "memory");  // keep the next pair's loads behind this pair's math
+        }
+        if (kSteps != 0 && gate_min_needs_exact(gmin)) {   // a gate below -85: redo this thread's share verbatim
+            m2 = 0u;
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                const int i = tid + s * kThreads;
+                if (i < n_vecs) {
+                    yw[s] = swiglu8<0>(ld_stream(g_row + i), ld_stream(u_row + i));
+                    if constexpr (kStoreY) st_vec(static_cast<uint4*>(y) + row_off + i, yw[s]);
+                    m2 = amax_acc_bf16x2(m2, yw[s].x);
+                    m2 = amax_acc_bf16x2(m2, yw[s].y);
+                    m2 = amax_acc_bf16x2(m2, yw[s].z);
+                    m2 = amax_acc_bf16x2(m2, yw[s].w);
+                }
+            }
         }
         // The reference's amax (fmaxf) skips NaN; redo this thread's share that way if it holds
         // a non-finite value, and let those elements take the exact conversion path below.
@@ -213,7 +258,7 @@ swiglu_quant_staged_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, 
     for (long long row = blockIdx.x; row < num_tokens; row += gridDim.x, parity ^= 1) {
         const size_t row_off = static_cast<size_t>(row) * n_vecs;
         uint4 yw[VPT];
-        uint32_t m2 = 0u;
+        uint32_t m2 = 0u, gmin = kGateMinInit;
 #pragma unroll
         for (int sl = 0; sl < VPT; ++sl) {
             if (sl < slots_per_row) {
@@ -229,12 +274,29 @@ swiglu_quant_staged_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, 
                 if (lane == 0) pipe::mbar_arrive(empty + s);
                 if (++s == stages) { s = 0; phase ^= 1; }
                 if (i < n_vecs) {
-                    yw[sl] = swiglu8<kSteps>(gv, uv);
+                    gmin = gate_min_acc(gmin, gv);
+                    yw[sl] = swiglu8_unchecked<kSteps>(gv, uv);
                     if constexpr (kStoreY) st_vec(static_cast<uint4*>(y) + row_off + i, yw[sl]);
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[sl].x));
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[sl].y));
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[sl].z));
-                    m2 = max_nan_bf16x2(m2, abs_bf16x2(yw[sl].w));
+                    m2 = amax_acc_bf16x2(m2, yw[sl].x);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].y);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].z);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].w);
+                }
+            }
+        }
+        if (gate_min_needs_exact(gmin)) {   // a gate below -85: redo this thread's share verbatim, from global memory
+            m2 = 0u;
+#pragma unroll
+            for (int sl = 0; sl < VPT; ++sl) {
+                const int i = tid + sl * kThreads;
+                if (i < n_vecs) {
+                    yw[sl] = swiglu8<0>(ld_stream(static_cast<const uint4*>(gate) + row_off + i),
+                                        ld_stream(static_cast<const uint4*>(up) + row_off + i));
+                    if constexpr (kStoreY) st_vec(static_cast<uint4*>(y) + row_off + i, yw[sl]);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].x);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].y);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].z);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].w);
                 }
             }
         }
