@@ -57,4 +57,9 @@ void embedding_lookup_bf16_forward(__nv_bfloat16* out, const __nv_bfloat16* embe
                                    const int* token_ids, int num_tokens, int hidden_dim,
                                    cudaStream_t stream = nullptr);
 
+// include/runtherder/kernels/bias.cuh:20-30
+void qkv_bias_add_bf16_forward(__nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* v, const __nv_bfloat16* q_bias,
+                               const __nv_bfloat16* k_bias, const __nv_bfloat16* v_bias, int n, int q_dim,
+                               int kv_dim, cudaStream_t stream = nullptr);
+
 }  // namespace runtherder::kernels

@@ -94,6 +94,13 @@ int rh_rope_bf16(void* q, void* k, const int* positions, const float* inv_freq, 
 int rh_embedding_lookup_bf16(void* out, const void* table, const int* token_ids, int num_tokens,
                              int hidden_dim, void* stream);
 
+/* q[r,:] += q_bias, k[r,:] += k_bias, v[r,:] += v_bias in place (Qwen2's projection biases); every
+ * output is bf16(float(x) + float(b)).
+ * Replaces qkv_bias_add_bf16_forward (include/runtherder/kernels/bias.cuh:20-30,
+ * src/kernels/bias.cu:64-90 — a file that does not compile as shipped: line 1 carries a stray token). */
+int rh_qkv_bias_add_bf16(void* q, void* k, void* v, const void* q_bias, const void* k_bias,
+                         const void* v_bias, int n, int q_dim, int kv_dim, void* stream);
+
 /* ---- Fused entry points (new; each equals a chain of the reference's calls) --------------- */
 
 /* [residual add +] RMSNorm + per-token INT8 quantisation in one pass over the row.
@@ -124,6 +131,20 @@ int rh_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v
                    const int* positions, const float* inv_freq, uint8_t* k_cache, float* k_scale,
                    uint8_t* v_cache, float* v_scale, const int* at_pos, int seq_len, int num_q_heads,
                    int num_kv_heads, int head_dim, void* stream);
+
+/* ---- Decode-loop glue on the device ------------------------------------------------------- */
+
+/* positions[i] = start_pos + i for i < n, *decode_pos = start_pos: what LlamaModel::stage
+ * (src/model/supported/llama/llama.cu:266-274) and EngineContext::set_decode_pos
+ * (include/runtherder/engine/context.h:41-45) do with a host iota and two synchronous copies.
+ * start_pos is passed by value: inside a captured graph use rh_decode_advance instead. */
+int rh_stage_positions(int* positions, int* decode_pos_or_null, int start_pos, int n, void* stream);
+
+/* End-of-step update for a graph-captured decode loop: *token_slot = *next_token (the sampled id, when
+ * both are given), *position += step, *decode_pos += step — all device-resident, so the next replay
+ * sees the next position without any host copy. */
+int rh_decode_advance(int* token_slot_or_null, int* position_or_null, int* decode_pos_or_null,
+                      const int* next_token_or_null, int step, void* stream);
 
 /* ---- Host-side tables (HOST pointers, no GPU involved) ----------------------------------- */
 

@@ -309,6 +309,19 @@ ORC_API void orc_embedding_lookup(uint16_t* out, const uint16_t* table, const in
 }
 
 /* ------------------------------------------------------------------------ */
+/* Row-broadcast bias add (Qwen2 q/k/v projections):                         */
+/* tests/kernels/test_bias.cpp:33-45 (host reference of src/kernels/bias.cu:15-28). */
+/* out = bf16(float(x) + float(bias[c])); may run in place.                  */
+/* ------------------------------------------------------------------------ */
+ORC_API void orc_add_rows(uint16_t* out, const uint16_t* x, const uint16_t* bias, long n, int dim) {
+    for (long r = 0; r < n; ++r)
+        for (int c = 0; c < dim; ++c) {
+            size_t i = (size_t)r * dim + c;
+            out[i] = orc_f32_to_bf16(orc_bf16_to_f32(x[i]) + orc_bf16_to_f32(bias[c]));
+        }
+}
+
+/* ------------------------------------------------------------------------ */
 /* Chains, as the reference's layer composition issues them.  Each stage     */
 /* rounds to bf16 exactly where the reference stores a bf16 tensor.          */
 /* ------------------------------------------------------------------------ */

@@ -26,3 +26,5 @@ struct Sink {
 #define EXPECT_FALSE(a) RH_NULL_EXPECT(a)
 #define EXPECT_FLOAT_EQ(a, b) RH_NULL_EXPECT(a, b)
 #define EXPECT_NEAR(a, b, tol) RH_NULL_EXPECT(a, b, tol)
+#define ASSERT_EQ(a, b) RH_NULL_EXPECT(a, b)
+#define ASSERT_TRUE(a) RH_NULL_EXPECT(a)

@@ -57,6 +57,12 @@ private:
     std::ostringstream msg_;
 };
 
+// `return Voidify() = Check(...) << msg;` — assignment binds looser than <<, so the message is streamed
+// first and the whole expression has type void.
+struct Voidify {
+    void operator=(const Check&) const {}
+};
+
 // GoogleTest's EXPECT_FLOAT_EQ: equal within 4 units in the last place.
 inline bool almost_equal_4ulp(float a, float b) {
     if (std::isnan(a) || std::isnan(b)) return false;
@@ -99,4 +105,9 @@ inline int run_all() {
 #define EXPECT_TRUE(a) RH_CHECK_(static_cast<bool>(a), #a)
 #define EXPECT_FALSE(a) RH_CHECK_(!static_cast<bool>(a), "!(" #a ")")
 #define EXPECT_FLOAT_EQ(a, b) RH_CHECK_(::rh_gtest_runner::almost_equal_4ulp((a), (b)), #a " ~= " #b)
+// ASSERT_*: record the failure and leave the enclosing (void) function, like GoogleTest does.
+#define ASSERT_EQ(a, b) \
+    if ((a) == (b)) {} else return ::rh_gtest_runner::Voidify() = RH_CHECK_(false, #a " == " #b)
+#define ASSERT_TRUE(a) \
+    if (static_cast<bool>(a)) {} else return ::rh_gtest_runner::Voidify() = RH_CHECK_(false, #a)
 #define EXPECT_NEAR(a, b, tol) RH_CHECK_(std::fabs((a) - (b)) <= (tol), "|" #a " - " #b "| <= " #tol)

@@ -31,9 +31,12 @@ SIGNATURES = {
     "rh_swiglu_bf16": [_p, _p, _p, _ll, _p],
     "rh_rope_bf16": [_p, _p, _p, _p, _i, _i, _i, _i, _p],
     "rh_embedding_lookup_bf16": [_p, _p, _p, _i, _i, _p],
+    "rh_qkv_bias_add_bf16": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p],
     "rh_rmsnorm_add_quant_int8": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p],
     "rh_swiglu_quant_int8": [_p, _p, _p, _p, _p, _i, _i, _p],
     "rh_rope_kv_fp8": [_p, _p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
+    "rh_stage_positions": [_p, _p, _i, _i, _p],
+    "rh_decode_advance": [_p, _p, _p, _p, _i, _p],
     "rh_rope_inv_freq_plain": [_p, _i, _f],
     "rh_rope_inv_freq_llama3": [_p, _i, _f, _f, _f, _f, _i],
     "rh_synth_normal_bf16": [_p, _sz, _u64, _u64, _u64, _f, _p, _i, _p],

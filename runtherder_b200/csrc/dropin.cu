@@ -66,4 +66,11 @@ void embedding_lookup_bf16_forward(__nv_bfloat16* out, const __nv_bfloat16* embe
                  "embedding_lookup_bf16_forward");
 }
 
+void qkv_bias_add_bf16_forward(__nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* v, const __nv_bfloat16* q_bias,
+                               const __nv_bfloat16* k_bias, const __nv_bfloat16* v_bias, int n, int q_dim,
+                               int kv_dim, cudaStream_t stream) {
+    die_on_error(rh_qkv_bias_add_bf16(q, k, v, q_bias, k_bias, v_bias, n, q_dim, kv_dim, stream),
+                 "qkv_bias_add_bf16_forward");
+}
+
 }  // namespace runtherder::kernels

@@ -82,11 +82,101 @@ __global__ void __launch_bounds__(256) dequant_w8a8_kernel(__nv_bfloat16* __rest
     }
 }
 
+// q[r,:] += q_bias, k[r,:] += k_bias, v[r,:] += v_bias in place, each output bf16(float(x) + float(b))
+// (reference: src/kernels/bias.cu:15-60, Qwen2's projections).  One 128-bit vector per thread over the
+// concatenated [n, q_vecs + 2*kv_vecs] index space; the fp32 adds are issued in pairs.
+__global__ void __launch_bounds__(256) qkv_bias_add_kernel(uint4* __restrict__ q, uint4* __restrict__ k,
+                                                           uint4* __restrict__ v, const uint4* __restrict__ qb,
+                                                           const uint4* __restrict__ kb, const uint4* __restrict__ vb,
+                                                           long long total, int q_vecs, int kv_vecs) {
+    const int row_vecs = q_vecs + 2 * kv_vecs;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const long long row = idx / row_vecs;
+        int col = static_cast<int>(idx - row * row_vecs);
+        uint4* x;
+        const uint4* b;
+        if (col < q_vecs) {
+            x = q + row * q_vecs + col; b = qb + col;
+        } else if ((col -= q_vecs) < kv_vecs) {
+            x = k + row * kv_vecs + col; b = kb + col;
+        } else {
+            col -= kv_vecs;
+            x = v + row * kv_vecs + col; b = vb + col;
+        }
+        const uint4 xv = ld_stream(x), bv = ld_weight(b);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 r = add2_rn(bf2_to_f2(xw[j]), bf2_to_f2(bw[j]));
+            o[j] = pack_bf16x2(r.x, r.y);
+        }
+        st_vec(x, make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
+
+// Device-side replacements for the per-step host work of the decode loop (reference:
+// LlamaModel::stage, src/model/supported/llama/llama.cu:266-274, and EngineContext::set_decode_pos,
+// include/runtherder/engine/context.h:41-45 — three synchronous cudaMemcpy per generated token).
+__global__ void stage_positions_kernel(int* __restrict__ positions, int* __restrict__ decode_pos, int start_pos, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) positions[i] = start_pos + i;            // std::iota(positions, start_pos)
+    if (i == 0 && decode_pos != nullptr) *decode_pos = start_pos;
+}
+__global__ void decode_advance_kernel(int* __restrict__ token_slot, int* __restrict__ position, int* __restrict__ decode_pos,
+                                      const int* __restrict__ next_token, int step) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        if (token_slot != nullptr && next_token != nullptr) *token_slot = *next_token;
+        if (position != nullptr) *position += step;
+        if (decode_pos != nullptr) *decode_pos += step;
+    }
+}
+
 }  // namespace
 
 }  // namespace rh
 
 using namespace rh;
+
+extern "C" int rh_stage_positions(int* positions, int* decode_pos_or_null, int start_pos, int n, void* stream) {
+    RH_REQUIRE(positions != nullptr, RH_ERR_INVALID_ARG, "rh_stage_positions: null pointer");
+    RH_REQUIRE(n >= 1, RH_ERR_INVALID_ARG, "rh_stage_positions: stage needs at least one token");
+    RH_REQUIRE(start_pos >= 0, RH_ERR_INVALID_ARG, "rh_stage_positions: start_pos must be >= 0");
+    stage_positions_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(positions, decode_pos_or_null, start_pos, n);
+    return host::check_launch("stage_positions_kernel");
+}
+
+extern "C" int rh_decode_advance(int* token_slot_or_null, int* position_or_null, int* decode_pos_or_null,
+                                 const int* next_token_or_null, int step, void* stream) {
+    RH_REQUIRE(position_or_null || decode_pos_or_null || token_slot_or_null, RH_ERR_INVALID_ARG,
+               "rh_decode_advance: nothing to advance");
+    RH_REQUIRE(step >= 0, RH_ERR_INVALID_ARG, "rh_decode_advance: step must be >= 0");
+    decode_advance_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(token_slot_or_null, position_or_null,
+                                                                         decode_pos_or_null, next_token_or_null, step);
+    return host::check_launch("decode_advance_kernel");
+}
+
+extern "C" int rh_qkv_bias_add_bf16(void* q, void* k, void* v, const void* q_bias, const void* k_bias,
+                                    const void* v_bias, int n, int q_dim, int kv_dim, void* stream) {
+    RH_REQUIRE(q && k && v && q_bias && k_bias && v_bias, RH_ERR_INVALID_ARG, "rh_qkv_bias_add_bf16: null pointer");
+    RH_REQUIRE(n >= 1, RH_ERR_INVALID_ARG, "rh_qkv_bias_add_bf16: n must be >= 1");
+    RH_REQUIRE(q_dim >= kVec && kv_dim >= kVec, RH_ERR_UNSUPPORTED_DIM, "rh_qkv_bias_add_bf16: q_dim and kv_dim must be >= 8");
+    RH_REQUIRE(q_dim % kVec == 0 && kv_dim % kVec == 0, RH_ERR_UNSUPPORTED_DIM,
+               "rh_qkv_bias_add_bf16: q_dim and kv_dim must be multiples of 8");
+    RH_REQUIRE(host::aligned16(q) && host::aligned16(k) && host::aligned16(v) && host::aligned16(q_bias) &&
+                   host::aligned16(k_bias) && host::aligned16(v_bias),
+               RH_ERR_MISALIGNED, "rh_qkv_bias_add_bf16: pointers must be 16-byte aligned");
+    const int q_vecs = q_dim / kVec, kv_vecs = kv_dim / kVec;
+    const long long total = static_cast<long long>(n) * (q_vecs + 2 * kv_vecs);
+    long long grid = (total + 255) / 256;
+    const long long cap = static_cast<long long>(host::num_sms()) * 16;
+    if (grid > cap) grid = cap;
+    qkv_bias_add_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint4*>(q), static_cast<uint4*>(k), static_cast<uint4*>(v), static_cast<const uint4*>(q_bias),
+        static_cast<const uint4*>(k_bias), static_cast<const uint4*>(v_bias), total, q_vecs, kv_vecs);
+    return host::check_launch("qkv_bias_add_kernel");
+}
 
 extern "C" int rh_embedding_lookup_bf16(void* out, const void* table, const int* token_ids,
                                         int num_tokens, int hidden_dim, void* stream) {

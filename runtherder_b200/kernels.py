@@ -19,7 +19,7 @@ TensorOrPtr = Union[torch.Tensor, int, None]
 __all__ = [
     "RhError", "rmsnorm_bf16_forward", "rmsnorm_add_bf16_forward", "quantize_per_token_int8",
     "dequantize_w8a8", "quantize_kv_fp8", "dequantize_kv_fp8", "swiglu_bf16_forward", "rope_bf16",
-    "embedding_lookup_bf16_forward", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
+    "embedding_lookup_bf16_forward", "qkv_bias_add_bf16_forward", "stage_positions", "decode_advance", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
 ]
 
 
@@ -122,6 +122,25 @@ def embedding_lookup_bf16_forward(out, embedding_table, token_ids, num_tokens: i
     call("rh_embedding_lookup_bf16", _ptr(out, _BF, num_tokens * hidden_dim, "out"),
          _ptr(embedding_table, _BF, hidden_dim, "embedding_table"), _ptr(token_ids, _I32, num_tokens, "token_ids"),
          num_tokens, hidden_dim, _stream(stream))
+
+
+def qkv_bias_add_bf16_forward(q, k, v, q_bias, k_bias, v_bias, n: int, q_dim: int, kv_dim: int, stream=None) -> None:
+    """q[r] += q_bias, k[r] += k_bias, v[r] += v_bias for every row, in place.  (bias.cuh:20-30)"""
+    call("rh_qkv_bias_add_bf16", _ptr(q, _BF, n * q_dim, "q"), _ptr(k, _BF, n * kv_dim, "k"), _ptr(v, _BF, n * kv_dim, "v"),
+         _ptr(q_bias, _BF, q_dim, "q_bias"), _ptr(k_bias, _BF, kv_dim, "k_bias"), _ptr(v_bias, _BF, kv_dim, "v_bias"),
+         n, q_dim, kv_dim, _stream(stream))
+
+
+def stage_positions(positions, decode_pos, start_pos: int, n: int, stream=None) -> None:
+    """positions[:n] = start_pos + arange(n), decode_pos[0] = start_pos, on the device (llama.cu:266-274)."""
+    call("rh_stage_positions", _ptr(positions, _I32, n, "positions"), _ptr(decode_pos, _I32, 1, "decode_pos"), start_pos, n,
+         _stream(stream))
+
+
+def decode_advance(token_slot, position, decode_pos, next_token, step: int = 1, stream=None) -> None:
+    """token_slot[0] = next_token[0]; position[0] += step; decode_pos[0] += step — graph-capturable step update."""
+    call("rh_decode_advance", _ptr(token_slot, _I32, 1, "token_slot"), _ptr(position, _I32, 1, "position"),
+         _ptr(decode_pos, _I32, 1, "decode_pos"), _ptr(next_token, _I32, 1, "next_token"), step, _stream(stream))
 
 
 # ---- fused entry points ---------------------------------------------------------------------

@@ -98,6 +98,13 @@ def main() -> None:
         ref.refhost_swiglu(ptr(y), ptr(g), ptr(u), n)
         put(f"swiglu_n{n}_seed{sg:x}", gate=g, up=u, y=y)
 
+    for n, q_dim, kv_dim in [(3, 64, 16), (1, 1536, 256), (511, 2048, 256)]:             # test_bias.cpp:103-116
+        for name, dim, sx, sb in (("q", q_dim, 0x1111, 0x4444), ("k", kv_dim, 0x2222, 0x5555), ("v", kv_dim, 0x3333, 0x6666)):
+            x, b = rnd(n * dim, 4.0, sx), rnd(dim, 2.0, sb)
+            out = np.empty_like(x)
+            ref.refhost_add_rows(ptr(out), ptr(x), ptr(b), n, dim)
+            put(f"bias_{name}_n{n}_dim{dim}", x=x, bias=b, out=out)
+
     np.savez_compressed(HERE / "reference_host.npz", **arrays)
     (HERE / "reference_host_digests.json").write_text(json.dumps(digests, indent=1, sort_keys=True) + "\n")
     print(f"{len(arrays)} arrays, {len(digests)} cases")

@@ -37,6 +37,7 @@ def load_oracle() -> C.CDLL:
         "orc_dequantize_w8a8": ([_p, _p, _p, _p, _l, _i], None),
         "orc_quantize_kv_fp8": ([_p, _p, _p, _i, _i, _l, _i], None),
         "orc_swiglu": ([_p, _p, _p, _sz], None),
+        "orc_add_rows": ([_p, _p, _p, _l, _i], None),
         "orc_rope_theta": ([_p, _i, _l, _i, _i, _f], None),
         "orc_rope_table": ([_p, _p, _p, _l, _i, _i], None),
         "orc_rope_inv_freq_plain": ([_p, _i, _f], None),
@@ -81,6 +82,7 @@ def load_ref_host():
         "refhost_dequantize_kv_fp8": ([_u8, _f], _f),
         "refhost_rope": ([_p, _i, _i, _i, _i, _f], C.c_double),
         "refhost_swiglu": ([_p, _p, _p, _sz], C.c_double),
+        "refhost_add_rows": ([_p, _p, _p, _i, _i], None),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)
@@ -154,6 +156,12 @@ class Oracle:
         q, s = np.zeros((total, D), np.uint8), np.zeros(total, np.float32)
         self.lib.orc_quantize_kv_fp8(ptr(q), ptr(s), ptr(x), at_pos, rows_per_pos, R, D)
         return q, s
+
+    def add_rows(self, x, bias):
+        n, dim = x.shape
+        out = np.empty_like(x)
+        self.lib.orc_add_rows(ptr(out), ptr(x), ptr(bias), n, dim)
+        return out
 
     def swiglu(self, gate, up):
         y = np.empty_like(gate)

@@ -22,6 +22,8 @@ REFERENCE_CXX_SYMBOLS = [
     "_ZN10runtherder7kernels9rope_bf16EP13__nv_bfloat16S2_PKiPKfiiiiP11CUstream_st",
     "_ZN10runtherder7kernels29embedding_lookup_bf16_forwardEP13__nv_bfloat16PKS1_PKiiiP11CUstream_st",
 ]
+# bias.cu does not compile in the reference as shipped, so no reference object defines this one
+BIAS_CXX_SYMBOL = "_ZN10runtherder7kernels25qkv_bias_add_bf16_forwardEP13__nv_bfloat16S2_S2_PKS1_S4_S4_iiiP11CUstream_st"
 
 
 def declared_entry_points():
@@ -43,7 +45,7 @@ def test_library_loads_and_exports_every_declared_symbol():
 
 def test_library_exports_reference_cxx_signatures():
     from runtherder_b200 import _lib
-    for sym in REFERENCE_CXX_SYMBOLS:
+    for sym in REFERENCE_CXX_SYMBOLS + [BIAS_CXX_SYMBOL]:
         getattr(_lib.lib, sym)  # raises AttributeError when missing
 
 

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-@pytest.mark.parametrize("suite", ["rmsnorm", "quantization", "rope", "activation"])
+@pytest.mark.parametrize("suite", ["rmsnorm", "quantization", "rope", "activation", "bias"])
 def test_reference_kernel_tests_pass_against_this_library(suite):
     exe = ROOT / "oracle" / "_ref" / f"dropin_test_{suite}"
     if not exe.exists():
@@ -85,3 +85,34 @@ def test_bounded_wait_gives_up_and_reports():
     assert after.value == 0                                                        # sticky word restored
     x = torch.ones(8, device="cuda")
     assert float((x * 2).sum()) == 16.0                                            # context still usable
+
+
+def test_decode_glue_advances_positions_inside_a_graph():
+    """rh_stage_positions == iota + decode_pos copy; rh_decode_advance captured at the end of a step makes
+    every replay of the graph see the next position and the previously sampled token, with no host copy."""
+    from runtherder_b200 import kernels as K
+    positions = torch.full((40,), -1, dtype=torch.int32, device="cuda")
+    decode_pos = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    K.stage_positions(positions, decode_pos, 17, 35)
+    assert positions[:35].tolist() == list(range(17, 52)) and positions[35:].tolist() == [-1] * 5
+    assert decode_pos.item() == 17
+    token = torch.tensor([5], dtype=torch.int32, device="cuda")
+    sampled = torch.tensor([0], dtype=torch.int32, device="cuda")
+    pos1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    K.stage_positions(pos1, decode_pos, 100, 1)
+    seen = torch.zeros(4, 3, dtype=torch.int32, device="cuda")
+    step_idx = torch.zeros(1, dtype=torch.int64, device="cuda")
+    side = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=side):
+            row = torch.stack([token[0], pos1[0], decode_pos[0]])      # what a forward would read this step
+            seen.index_copy_(0, step_idx, row.unsqueeze(0))
+            sampled.copy_(token + 7)                                   # stand-in for the sampler
+            K.decode_advance(token, pos1, decode_pos, sampled, 1)
+            step_idx.add_(1)
+    for _ in range(4):
+        g.replay()
+    torch.cuda.synchronize()
+    assert seen.tolist() == [[5, 100, 100], [12, 101, 101], [19, 102, 102], [26, 103, 103]]

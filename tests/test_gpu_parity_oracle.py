@@ -153,6 +153,19 @@ def test_embedding_gather():
         assert np.array_equal(to_np(out), table[ids])
 
 
+@pytest.mark.parametrize("n,q_dim,kv_dim", [(3, 64, 16), (1, 1536, 256), (511, 2048, 256), (35, 3072, 1024), (2, 8, 8)])
+def test_qkv_bias_add(n, q_dim, kv_dim):
+    """Bit-identical to bf16(float(x) + float(b)) (tests/kernels/test_bias.cpp:46-57), shapes and seeds of that test."""
+    K = _k(); to_dev, to_np = _gpu()
+    q, k, v = (make_bf16_random(n * d, 4.0, s).reshape(n, d) for d, s in ((q_dim, 0x1111), (kv_dim, 0x2222), (kv_dim, 0x3333)))
+    qb, kb, vb = (make_bf16_random(d, 2.0, s) for d, s in ((q_dim, 0x4444), (kv_dim, 0x5555), (kv_dim, 0x6666)))
+    qd, kd, vd = to_dev(q), to_dev(k), to_dev(v)
+    K.qkv_bias_add_bf16_forward(qd, kd, vd, to_dev(qb), to_dev(kb), to_dev(vb), n, q_dim, kv_dim)
+    assert np.array_equal(to_np(qd), ORC.add_rows(q, qb))
+    assert np.array_equal(to_np(kd), ORC.add_rows(k, kb))
+    assert np.array_equal(to_np(vd), ORC.add_rows(v, vb))
+
+
 def test_dequantize_w8a8():
     K = _k(); to_dev, to_np = _gpu()
     rng = np.random.default_rng(2)

@@ -114,6 +114,14 @@ def test_swiglu_matches_reference_host(n, sg, su):
     assert sha(ORC.swiglu(g, u)) == DIG[case]["y"]
 
 
+@pytest.mark.parametrize("n,q_dim,kv_dim", [(3, 64, 16), (1, 1536, 256), (511, 2048, 256)])
+def test_bias_add_matches_reference_host(n, q_dim, kv_dim):
+    for name, dim, sx, sb in (("q", q_dim, 0x1111, 0x4444), ("k", kv_dim, 0x2222, 0x5555), ("v", kv_dim, 0x3333, 0x6666)):
+        case = f"bias_{name}_n{n}_dim{dim}"
+        x, b = _inputs(case, ["x", "bias"], [(n * dim, 4.0, sx), (dim, 2.0, sb)])
+        assert sha(ORC.add_rows(x.reshape(n, dim), b)) == DIG[case]["out"]
+
+
 def test_inv_freq_known_answers():
     """Values of theta^(-2i/D) and of the Llama-3 rescaling computed independently from the formula
     (src/model/supported/llama/llama.cu:128-143, llama3.cu:26-60) for the benchmark configurations."""
