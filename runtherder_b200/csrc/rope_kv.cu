@@ -197,6 +197,21 @@ __global__ void __launch_bounds__(256) rope_kv_generic_kernel(const RopeArgs p) 
     }
 }
 
+constexpr int kRopeDepth = 4;   // groups in flight per warp in the fast kernel (1 KB each at D = 128)
+
+// 16-byte asynchronous global -> shared copy (L2 only).  `after` is an unused input that orders the
+// copy behind the instruction that produced it.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, uint32_t after) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+                 "l"(gmem_src), "r"(after)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
 // Fast path for head counts that are multiples of the heads a warp carries (4 at D = 128): every
 // group of a warp is then all-Q, all-K or all-V, so the three roles become three straight loops with
 // no per-row role logic, row pointers advance by a constant, and the rotation works on the register
@@ -310,9 +325,10 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
         st_vec8(dst + sub + kLanesPerHead, make_uint2(c[2], c[3]));
     };
 
-    // One loop over the chunk's groups; the role of a group is warp-uniform.  Loads run kAhead groups
-    // ahead of the arithmetic so that a warp keeps (kAhead + 1) KB in flight.
-    constexpr int kAhead = 2;
+    // One loop over the chunk's groups; the role of a group is warp-uniform.  The rows of the next
+    // kDepth groups are always on their way into this warp's slice of shared memory (cp.async, 16 bytes
+    // per lane and vector, L2 only), so a warp keeps kDepth KB in flight without holding them in
+    // registers; every lane reads back only what it copied itself, so no barrier is involved.
     auto group_src = [&](int g) -> const uint4* {
         const int h = hslot;
         if (g < gq) return static_cast<const uint4*>(p.q) + (static_cast<size_t>(token) * Hq + g * kHeadsPerGroup + h) * kVecsPerRow;
@@ -320,49 +336,50 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
             return static_cast<const uint4*>(p.k_in) + (static_cast<size_t>(token) * Hkv + (g - gq) * kHeadsPerGroup + h) * kVecsPerRow;
         return static_cast<const uint4*>(p.v_in) + (static_cast<size_t>(token) * Hkv + (g - gq - gk) * kHeadsPerGroup + h) * kVecsPerRow;
     };
-    uint4 lo_q[kAhead + 1], hi_q[kAhead + 1];
+    extern __shared__ uint4 rope_stage[];                    // [warps][kDepth][lo|hi][32 lanes]
+    uint4* mine = rope_stage + static_cast<size_t>(threadIdx.x >> 5) * (kRopeDepth * 64) + lane;
+    auto fetch = [&](int g, int slot, uint32_t after) {      // `after`: a value the copy must wait for
+        const uint4* src = group_src(g);
+        cp_async16(mine + slot * 64, src + sub, after);
+        cp_async16(mine + slot * 64 + 32, src + sub + kLanesPerHead, after);
+    };
 #pragma unroll
-    for (int k = 0; k < kAhead; ++k) {
-        if (g_begin + k < g_end) {
-            const uint4* src = group_src(g_begin + k);
-            lo_q[k] = ld_stream(src + sub);
-            hi_q[k] = ld_stream(src + sub + kLanesPerHead);
-        }
+    for (int d = 0; d < kRopeDepth; ++d) {
+        if (g_begin + d < g_end) fetch(g_begin + d, d, 0u);
+        cp_async_commit();
     }
-    for (int g0 = g_begin; g0 < g_end; g0 += kAhead + 1) {
-#pragma unroll
-        for (int k = 0; k <= kAhead; ++k) {          // register ring: slot k holds group g0 + k
-            const int g = g0 + k;
-            if (g < g_end) {
-                if (g + kAhead < g_end) {
-                    const uint4* src = group_src(g + kAhead);
-                    lo_q[(k + kAhead) % (kAhead + 1)] = ld_stream(src + sub);
-                    hi_q[(k + kAhead) % (kAhead + 1)] = ld_stream(src + sub + kLanesPerHead);
-                }
-                const uint4 lo_v = lo_q[k], hi_v = hi_q[k];
-                if (g < gq) {                            // Q: rotate in place
-                    uint4* rowp = static_cast<uint4*>(p.q) + (static_cast<size_t>(token) * Hq + g * kHeadsPerGroup + hslot) * kVecsPerRow;
-                    uint4 out_lo, out_hi;
-                    norm_rotate(lo_v, hi_v, p.q_norm, out_lo, out_hi);
-                    st_vec(rowp + sub, out_lo);
-                    st_vec(rowp + sub + kLanesPerHead, out_hi);
-                } else if (g < gq + gk) {                // K: rotate, optional bf16 write-back, FP8 append
-                    const size_t row = static_cast<size_t>(token) * Hkv + (g - gq) * kHeadsPerGroup + hslot;
-                    uint4 out_lo, out_hi;
-                    norm_rotate(lo_v, hi_v, p.k_norm, out_lo, out_hi);
-                    if (p.k_out != nullptr) {
-                        uint4* dst = static_cast<uint4*>(p.k_out) + row * kVecsPerRow;
-                        st_vec(dst + sub, out_lo);
-                        st_vec(dst + sub + kLanesPerHead, out_hi);
-                    }
-                    if constexpr (kKV) append_fp8(out_lo, out_hi, p.k_cache, p.k_scale, static_cast<long long>(row) + slot_base);
-                } else if constexpr (kKV) {              // V: FP8 append only
-                    const size_t row = static_cast<size_t>(token) * Hkv + (g - gq - gk) * kHeadsPerGroup + hslot;
-                    append_fp8(lo_v, hi_v, p.v_cache, p.v_scale, static_cast<long long>(row) + slot_base);
-                }
+    int slot = 0;
+    for (int g = g_begin; g < g_end; ++g) {
+        cp_async_wait<kRopeDepth - 1>();
+        const uint4 lo_v = mine[slot * 64], hi_v = mine[slot * 64 + 32];
+        // refill this slot with the group kDepth ahead; the copy is tied to the values just read so it
+        // cannot be issued before they have left shared memory
+        if (g + kRopeDepth < g_end) fetch(g + kRopeDepth, slot, lo_v.x ^ hi_v.w);
+        cp_async_commit();
+        slot = (slot + 1 == kRopeDepth) ? 0 : slot + 1;
+
+        if (g < gq) {                            // Q: rotate in place
+            uint4* rowp = static_cast<uint4*>(p.q) + (static_cast<size_t>(token) * Hq + g * kHeadsPerGroup + hslot) * kVecsPerRow;
+            uint4 out_lo, out_hi;
+            norm_rotate(lo_v, hi_v, p.q_norm, out_lo, out_hi);
+            st_vec(rowp + sub, out_lo);
+            st_vec(rowp + sub + kLanesPerHead, out_hi);
+        } else if (g < gq + gk) {                // K: rotate, optional bf16 write-back, FP8 append
+            const size_t row = static_cast<size_t>(token) * Hkv + (g - gq) * kHeadsPerGroup + hslot;
+            uint4 out_lo, out_hi;
+            norm_rotate(lo_v, hi_v, p.k_norm, out_lo, out_hi);
+            if (p.k_out != nullptr) {
+                uint4* dst = static_cast<uint4*>(p.k_out) + row * kVecsPerRow;
+                st_vec(dst + sub, out_lo);
+                st_vec(dst + sub + kLanesPerHead, out_hi);
             }
+            if constexpr (kKV) append_fp8(out_lo, out_hi, p.k_cache, p.k_scale, static_cast<long long>(row) + slot_base);
+        } else if constexpr (kKV) {              // V: FP8 append only
+            const size_t row = static_cast<size_t>(token) * Hkv + (g - gq - gk) * kHeadsPerGroup + hslot;
+            append_fp8(lo_v, hi_v, p.v_cache, p.v_scale, static_cast<long long>(row) + slot_base);
         }
     }
+    cp_async_wait<0>();
 }
 
 // Any even head_dim <= 256 that is not a multiple of 16: one thread per rotation pair.
@@ -413,12 +430,13 @@ int launch_rope(RopeArgs p, bool norm, bool kv, cudaStream_t stream) {
     const unsigned g = static_cast<unsigned>(grid), b = static_cast<unsigned>(warps * 32);
     const bool aligned = p.num_q_heads % kHeadsPerGroup == 0 && p.num_kv_heads % kHeadsPerGroup == 0;
     if (aligned) {
+        const size_t smem = static_cast<size_t>(warps) * kRopeDepth * 64 * sizeof(uint4);   // <= 32 KB
         if (kv) {
-            if (norm) rope_kv_kernel<D, true, true><<<g, b, 0, stream>>>(p);
-            else rope_kv_kernel<D, false, true><<<g, b, 0, stream>>>(p);
+            if (norm) rope_kv_kernel<D, true, true><<<g, b, smem, stream>>>(p);
+            else rope_kv_kernel<D, false, true><<<g, b, smem, stream>>>(p);
         } else {
-            if (norm) rope_kv_kernel<D, true, false><<<g, b, 0, stream>>>(p);
-            else rope_kv_kernel<D, false, false><<<g, b, 0, stream>>>(p);
+            if (norm) rope_kv_kernel<D, true, false><<<g, b, smem, stream>>>(p);
+            else rope_kv_kernel<D, false, false><<<g, b, smem, stream>>>(p);
         }
     } else {
         if (kv) {
