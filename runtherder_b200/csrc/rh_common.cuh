@@ -41,6 +41,22 @@ __device__ __forceinline__ uint4 ld_weight(const void* p) {
 __device__ __forceinline__ void st_vec(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 __device__ __forceinline__ void st_vec8(void* p, uint2 v) { *reinterpret_cast<uint2*>(p) = v; }
 
+// Prefetch rings: each thread streams the vectors it will need into its own shared-memory slots with
+// cp.async and reads back only what it copied itself, so no barrier is involved and the bytes in
+// flight are set by the ring depth, not by registers.
+// 16-byte asynchronous global -> shared copy (L2 only).  `after` is an unused input that orders the
+// copy behind the instruction that produced it.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, uint32_t after) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+                 "l"(gmem_src), "r"(after)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
 // ---- bf16 <-> fp32 -------------------------------------------------------------------------
 
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -259,7 +275,8 @@ int resident_ctas(const void* kernel, int threads, size_t dyn_smem = 0);  // CTA
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kSwigluThreads,
-                kSwigluRcpSteps, kRowsStages, kSwigluStages, kRowsSmemH, kTuneSlots };
+                kSwigluRcpSteps, kRowsStages, kSwigluStages, kRowsSmemH, kRowsPrefetch,
+                kSwigluPrefetch, kTuneSlots };
 
 }  // namespace rh::host
 

@@ -199,19 +199,6 @@ __global__ void __launch_bounds__(256) rope_kv_generic_kernel(const RopeArgs p) 
 
 constexpr int kRopeDepth = 4;   // groups in flight per warp in the fast kernel (1 KB each at D = 128)
 
-// 16-byte asynchronous global -> shared copy (L2 only).  `after` is an unused input that orders the
-// copy behind the instruction that produced it.
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, uint32_t after) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-                 "l"(gmem_src), "r"(after)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int kPending>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory");
-}
-
 // Fast path for head counts that are multiples of the heads a warp carries (4 at D = 128): every
 // group of a warp is then all-Q, all-K or all-V, so the three roles become three straight loops with
 // no per-row role logic, row pointers advance by a constant, and the rotation works on the register

@@ -14,6 +14,8 @@
 // partials), so rrms — and with it every bf16 output and every INT8 code — is
 // bit-identical to the reference's CUDA kernel.  amax reductions are exact in any
 // order.
+#include <type_traits>
+
 #include "rh_common.cuh"
 #include "rh_pipeline.cuh"
 
@@ -219,31 +221,80 @@ __device__ __forceinline__ void load_gains(const RowArgs& a, int n_vecs, uint4 (
     }
 }
 
-// Direct-load kernel: each thread loads its vectors of the row straight into registers.
-template <int VPT, unsigned F, bool kSmemH = false>
-__global__ void __launch_bounds__(kRowThreads, (kSmemH ? 4 : ((F & kFNorm) == 0 ? (VPT <= 2 ? 6 : 2) : (VPT <= 2 ? 3 : 1)))) rows_kernel(const RowArgs a) {
+// Direct-load kernel.  kDepth = 0: each thread loads its vectors of the row straight into registers.
+// kDepth >= 1: each thread keeps the vectors of its next kDepth rows on their way into private
+// shared-memory slots (cp.async), so the global-load latency of a row is paid while the previous rows
+// are being reduced and quantised.
+template <int VPT, unsigned F, bool kSmemH = false, int kDepth = 0>
+__global__ void __launch_bounds__(kRowThreads, (kSmemH ? 4 : ((F & kFNorm) == 0 ? (VPT <= 2 ? 6 : 2) : (VPT <= 2 ? 3 : 1))))
+rows_kernel(const RowArgs a) {
     constexpr bool kAdd = (F & kFAdd) != 0;
+    constexpr int kOps = kAdd ? 2 : 1;
     __shared__ float s_ss[2][kRowWarps];
     __shared__ float s_mx[2][kRowWarps];
     __shared__ float4 s_h[kSmemH ? VPT * 2 * kRowThreads : 1];
+    extern __shared__ uint4 pre[];   // [kDepth][kOps][VPT][256], thread-private columns
     const RowCtx c = make_ctx<F>(a);
     uint4 gw[VPT];
     load_gains<VPT, F>(a, c.n_vecs, gw);
 
-    int parity = 0;
-    for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
+    auto fetch = [&](long long row, int slot, uint32_t after) {
         const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(c.n_vecs);
-        uint4 xv[VPT], rv[VPT];
 #pragma unroll
         for (int s = 0; s < VPT; ++s) {
             const int i = c.tid + s * kRowThreads;
             if (i < c.n_vecs) {
-                xv[s] = ld_stream(static_cast<const uint4*>(a.x) + row_off + i);
-                if constexpr (kAdd) rv[s] = ld_stream(static_cast<const uint4*>(a.residual) + row_off + i);
+                cp_async16(pre + ((slot * kOps + 0) * VPT + s) * kRowThreads + c.tid, static_cast<const uint4*>(a.x) + row_off + i, after);
+                if constexpr (kAdd)
+                    cp_async16(pre + ((slot * kOps + 1) * VPT + s) * kRowThreads + c.tid,
+                               static_cast<const uint4*>(a.residual) + row_off + i, after);
+            }
+        }
+    };
+    if constexpr (kDepth > 0) {
+#pragma unroll
+        for (int d = 0; d < kDepth; ++d) {
+            const long long row = blockIdx.x + static_cast<long long>(d) * gridDim.x;
+            if (row < a.num_rows) fetch(row, d, 0u);
+            cp_async_commit();
+        }
+    }
+
+    int parity = 0, slot = 0;
+    for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
+        uint4 xv[VPT], rv[VPT];
+        if constexpr (kDepth > 0) {
+            cp_async_wait<kDepth - 1>();
+            uint32_t tie = 0u;
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                if (c.tid + s * kRowThreads < c.n_vecs) {
+                    xv[s] = pre[((slot * kOps + 0) * VPT + s) * kRowThreads + c.tid];
+                    tie ^= xv[s].x;
+                    if constexpr (kAdd) {
+                        rv[s] = pre[((slot * kOps + 1) * VPT + s) * kRowThreads + c.tid];
+                        tie ^= rv[s].w;
+                    }
+                }
+            }
+            const long long ahead = row + static_cast<long long>(kDepth) * gridDim.x;
+            if (ahead < a.num_rows) fetch(ahead, slot, tie);   // refill the slot just drained
+            cp_async_commit();
+            slot = (slot + 1 == kDepth) ? 0 : slot + 1;
+        } else {
+            const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(c.n_vecs);
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                const int i = c.tid + s * kRowThreads;
+                if (i < c.n_vecs) {
+                    xv[s] = ld_stream(static_cast<const uint4*>(a.x) + row_off + i);
+                    if constexpr (kAdd) rv[s] = ld_stream(static_cast<const uint4*>(a.residual) + row_off + i);
+                }
             }
         }
         process_row<VPT, F, false, kSmemH>(a, c, row, parity, xv, rv, gw, s_ss, s_mx, s_h);
     }
+    if constexpr (kDepth > 0) cp_async_wait<0>();
 }
 
 // Staged kernel: a producer thread streams the rows through a shared-memory ring with bulk copies
@@ -427,6 +478,37 @@ void launch_long(const RowArgs& a, cudaStream_t stream) {
         return;
     }
     const int tuned = host::tuning(host::kRowsCtasPerSm);
+    if constexpr (VPT <= 2) {
+        // Plenty of rows: cp.async prefetch ring, rh_tune("rows_prefetch", depth 1..3; 4 = off).  Defaults
+        // from measurements at 65536 x 4096 on B200: norm + INT8 one row ahead (295 us vs 322 us), plain
+        // quantisation two rows ahead (120 us vs 131 us), both with three CTAs per SM; the bf16-output norm
+        // is store-bound and loses with a ring (370 us vs 332 us), so it keeps the plain loads.
+        constexpr bool kQuantOut = (F & (kFInt8 | kFFp8)) != 0;
+        int depth = host::tuning(host::kRowsPrefetch);
+        if (depth == 0) depth = !kQuantOut ? 4 : ((F & kFNorm) != 0 ? 1 : 2);
+        if (depth <= 3 && a.num_rows >= 4LL * host::num_sms() && host::tuning(host::kRowsSmemH) != 1) {
+            constexpr bool kSm = (F & kFNorm) != 0;
+            constexpr int kOps = (F & kFAdd) ? 2 : 1;
+            auto go = [&](auto depth_tag) {
+                constexpr int kD = decltype(depth_tag)::value;
+                const size_t smem = static_cast<size_t>(kD) * kOps * VPT * kRowThreads * sizeof(uint4);
+                static int resident = 0;
+                const void* fn = reinterpret_cast<const void*>(&rows_kernel<VPT, F, kSm, kD>);
+                if (resident == 0) {
+                    cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+                    resident = host::resident_ctas(fn, kRowThreads, smem);
+                }
+                const int per_sm = tuned > 0 ? tuned : (resident < 3 ? resident : 3);
+                const long long cap = static_cast<long long>(host::num_sms()) * per_sm;
+                const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
+                rows_kernel<VPT, F, kSm, kD><<<grid, kRowThreads, smem, stream>>>(a);
+            };
+            if (depth == 1) go(std::integral_constant<int, 1>{});
+            else if (depth == 2) go(std::integral_constant<int, 2>{});
+            else go(std::integral_constant<int, 3>{});
+            return;
+        }
+    }
     if constexpr ((F & kFNorm) != 0 && VPT <= 4) {   // 8 KB of shared memory per slot: up to 32 KB static
         if (host::tuning(host::kRowsSmemH) != 1) {   // rh_tune("rows_smem_h", 1) keeps h in registers
             static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F, true>), kRowThreads);

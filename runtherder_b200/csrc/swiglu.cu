@@ -360,6 +360,140 @@ int launch_swiglu_quant_staged(int8_t* q, float* x_scale, void* y, const void* g
     return host::check_launch("swiglu_quant_staged_kernel");
 }
 
+// Prefetch-ring variant (256 threads, no producer warp, no barriers for the data): each thread keeps
+// the gate/up vectors of its next kDepth slots on their way into private shared-memory slots with
+// cp.async and reads back only what it copied itself.  Same mapping and arithmetic as the kernels above.
+template <int VPT, bool kStoreY, int kSteps, int kDepth>
+__global__ void __launch_bounds__(256, 4)
+swiglu_quant_prefetch_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y, const void* gate,
+                             const void* up, long long num_tokens, int inter_dim) {
+    constexpr int kThreads = 256, kWarps = 8;
+    extern __shared__ uint4 pre[];   // [kDepth][gate|up][256]
+    __shared__ float s_mx[2][kWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n_vecs = inter_dim / kVec;
+    const int slots_per_row = (n_vecs + kThreads - 1) / kThreads;
+
+    // producer cursor: the next (row, slot-in-row) to fetch
+    long long p_row = blockIdx.x;
+    int p_sl = 0;
+    auto fetch_next = [&](int ring_slot, uint32_t after) {
+        if (p_row < num_tokens) {
+            const int i = tid + p_sl * kThreads;
+            if (i < n_vecs) {
+                const size_t off = static_cast<size_t>(p_row) * n_vecs + i;
+                cp_async16(pre + (ring_slot * 2 + 0) * kThreads + tid, static_cast<const uint4*>(gate) + off, after);
+                cp_async16(pre + (ring_slot * 2 + 1) * kThreads + tid, static_cast<const uint4*>(up) + off, after);
+            }
+            if (++p_sl == slots_per_row) { p_sl = 0; p_row += gridDim.x; }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) fetch_next(d, 0u);
+
+    int parity = 0, ring = 0;
+    for (long long row = blockIdx.x; row < num_tokens; row += gridDim.x, parity ^= 1) {
+        const size_t row_off = static_cast<size_t>(row) * n_vecs;
+        uint4 yw[VPT];
+        uint32_t m2 = 0u, gmin = kGateMinInit;
+#pragma unroll
+        for (int sl = 0; sl < VPT; ++sl) {
+            if (sl < slots_per_row) {
+                cp_async_wait<kDepth - 1>();
+                const int i = tid + sl * kThreads;
+                uint4 gv = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
+                if (i < n_vecs) {
+                    gv = pre[(ring * 2 + 0) * kThreads + tid];
+                    uv = pre[(ring * 2 + 1) * kThreads + tid];
+                }
+                fetch_next(ring, gv.x ^ uv.w);     // refill the slot just drained, behind the reads above
+                ring = (ring + 1 == kDepth) ? 0 : ring + 1;
+                if (i < n_vecs) {
+                    gmin = gate_min_acc(gmin, gv);
+                    yw[sl] = swiglu8_unchecked<kSteps>(gv, uv);
+                    if constexpr (kStoreY) st_vec(static_cast<uint4*>(y) + row_off + i, yw[sl]);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].x);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].y);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].z);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].w);
+                }
+            }
+        }
+        if (kSteps != 0 && gate_min_needs_exact(gmin)) {   // a gate below -85: redo this thread's share verbatim
+            m2 = 0u;
+#pragma unroll
+            for (int sl = 0; sl < VPT; ++sl) {
+                const int i = tid + sl * kThreads;
+                if (i < n_vecs) {
+                    yw[sl] = swiglu8<0>(ld_stream(static_cast<const uint4*>(gate) + row_off + i),
+                                        ld_stream(static_cast<const uint4*>(up) + row_off + i));
+                    if constexpr (kStoreY) st_vec(static_cast<uint4*>(y) + row_off + i, yw[sl]);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].x);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].y);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].z);
+                    m2 = amax_acc_bf16x2(m2, yw[sl].w);
+                }
+            }
+        }
+        const float m_lo = bf_lo(m2), m_hi = bf_hi(m2);
+        const bool finite = (m_lo <= 3.0e38f) && (m_hi <= 3.0e38f);
+        float amax = fmaxf(m_lo, m_hi);
+        if (!finite) {
+            amax = 0.0f;
+#pragma unroll
+            for (int sl = 0; sl < VPT; ++sl) {
+                if (tid + sl * kThreads < n_vecs) {
+                    float f[8];
+                    unpack8(yw[sl], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+                }
+            }
+        }
+        amax = warp_max_nonneg(amax);
+        if (lane == 0) s_mx[parity][warp] = amax;
+        __syncthreads();
+        amax = warp_max_nonneg(s_mx[parity][lane & (kWarps - 1)]);
+
+        const float inv = quant_inv_scale<127>(amax);
+        if (tid == 0) x_scale[row] = quant_scale<127>(amax);
+        const bool fast = finite && inv <= 3.0e38f;
+        uint2* q_row = reinterpret_cast<uint2*>(q) + row_off;
+#pragma unroll
+        for (int sl = 0; sl < VPT; ++sl) {
+            const int i = tid + sl * kThreads;
+            if (i < n_vecs) {
+                if (fast) {
+                    st_vec8(q_row + i, pack_int8x8_fast(yw[sl], inv));
+                } else {
+                    float f[8];
+                    unpack8(yw[sl], f);
+                    st_vec8(q_row + i, pack_int8x8(f, inv));
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+}
+
+template <int VPT, bool kStoreY, int kDepth>
+int launch_swiglu_quant_prefetch(int8_t* q, float* x_scale, void* y, const void* gate, const void* up,
+                                 long long num_tokens, int inter_dim, cudaStream_t stream) {
+    constexpr size_t smem = static_cast<size_t>(kDepth) * 2 * 256 * sizeof(uint4);
+    static int resident = 0;
+    const void* fn = reinterpret_cast<const void*>(&swiglu_quant_prefetch_kernel<VPT, kStoreY, 1, kDepth>);
+    if (resident == 0) {
+        cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        resident = host::resident_ctas(fn, 256, smem);
+    }
+    const int tuned = host::tuning(host::kSwigluCtasPerSm);
+    const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
+    const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
+    swiglu_quant_prefetch_kernel<VPT, kStoreY, 1, kDepth><<<grid, 256, smem, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
+    return host::check_launch("swiglu_quant_prefetch_kernel");
+}
+
 template <int kThreads, int VPT, int kSteps>
 int launch_swiglu_quant_steps(int8_t* q, float* x_scale, void* y, const void* gate, const void* up,
                               long long num_tokens, int inter_dim, cudaStream_t stream) {
@@ -387,6 +521,16 @@ template <int kThreads, int VPT>
 int launch_swiglu_quant(int8_t* q, float* x_scale, void* y, const void* gate, const void* up,
                         long long num_tokens, int inter_dim, cudaStream_t stream) {
     if constexpr (kThreads == 256 && VPT >= 2) {
+        // rh_tune("swiglu_prefetch", d): cp.async prefetch ring of d slots (2, 4 or 6) instead of the bulk-copy ring.
+        const int pf = host::tuning(host::kSwigluPrefetch);
+        if (pf >= 2 && rcp_steps() == 1 && num_tokens >= 4LL * host::num_sms()) {
+            if (pf >= 6) return y ? launch_swiglu_quant_prefetch<VPT, true, 6>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream)
+                                  : launch_swiglu_quant_prefetch<VPT, false, 6>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream);
+            if (pf >= 4) return y ? launch_swiglu_quant_prefetch<VPT, true, 4>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream)
+                                  : launch_swiglu_quant_prefetch<VPT, false, 4>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream);
+            return y ? launch_swiglu_quant_prefetch<VPT, true, 2>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream)
+                     : launch_swiglu_quant_prefetch<VPT, false, 2>(q, x_scale, y, gate, up, num_tokens, inter_dim, stream);
+        }
         // With plenty of rows the bulk-copy staging ring wins (measured on B200 at I = 14336: 0.80 ms vs
         // 0.85 ms for 65536 rows): three slots by default, rh_tune("swiglu_stages", n) sets the depth
         // and n = 1 selects the direct-load kernel.  Few rows are latency-bound: direct loads.
