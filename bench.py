@@ -35,7 +35,7 @@ NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per token row of each step kernel, from the ncu capture
 # summarised in profiles/c4_step_kernels_ncu_16384rows.md (16384-row case; rows are independent units,
 # so a launch's traffic is this figure times its rows).
-DRAM_TRAFFIC_BYTES_PER_ROW = {"embedding": 13070, "norm_quant": 25353, "rope_kv": 19116, "swiglu_quant": 70759}
+DRAM_TRAFFIC_BYTES_PER_ROW = {"embedding": 12878, "norm_quant": 26223, "rope_kv": 19303, "swiglu_quant": 70921}
 
 
 def parse_args():
@@ -309,25 +309,38 @@ def main():
     K = args.steps
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
     launches = 0
-    from runtherder_b200 import kernels as Kn
+    # The timed loop calls the C ABI directly with pre-resolved device pointers (the Python mirror in
+    # runtherder_b200.kernels adds ~10 us of argument checking per call, which matters once a GPU's share
+    # of a step shrinks to ~200 us at 8 GPUs).
+    from runtherder_b200 import _lib
+    L = _lib.lib
+    sp = torch.cuda.current_stream().cuda_stream or None
     H = cfg.hidden
+    P = lambda t: t.data_ptr()
+    calls = [
+        (L.rh_embedding_lookup_bf16, (P(outs["emb"]), P(ins["table"]), P(ins["ids"]), rows, H, sp)),
+        (L.rh_rmsnorm_add_quant_int8, (P(outs["q_attn_in"]), P(outs["s_attn_in"]), P(outs["h_attn"]), None, P(ins["x"]),
+                                       P(ins["residual"]), P(ins["g_attn"]), rows, H, cfg.eps, sp)),
+        (L.rh_rope_kv_fp8, (P(ins["q"]), None, P(ins["k"]), P(ins["v"]), None, None, cfg.eps, P(ins["positions"]),
+                            P(ins["inv_freq"]), P(outs["k_cache"]), P(outs["k_scale"]), P(outs["v_cache"]),
+                            P(outs["v_scale"]), P(outs["at_pos"]), rows, cfg.q_heads, cfg.kv_heads, cfg.head_dim, sp)),
+        (L.rh_swiglu_quant_int8, (P(outs["q_mlp"]), P(outs["s_mlp"]), None, P(ins["gate"]), P(ins["up"]), rows, cfg.inter, sp)),
+    ]
+    status = 0
     barrier()
     with ClockSampler(local_rank) as clocks:
+        t_enqueue = time.perf_counter()
         for s in range(K):
-            ev[s][0].record()
-            Kn.embedding_lookup_bf16_forward(outs["emb"], ins["table"], ins["ids"], rows, H)
-            ev[s][1].record()
-            Kn.rmsnorm_add_quant_int8(outs["q_attn_in"], outs["s_attn_in"], outs["h_attn"], None, ins["x"],
-                                      ins["residual"], ins["g_attn"], rows, H, cfg.eps)
-            ev[s][2].record()
-            Kn.rope_kv_fp8(ins["q"], None, ins["k"], ins["v"], None, None, cfg.eps, ins["positions"], ins["inv_freq"],
-                           outs["k_cache"], outs["k_scale"], outs["v_cache"], outs["v_scale"], outs["at_pos"], rows,
-                           cfg.q_heads, cfg.kv_heads, cfg.head_dim)
-            ev[s][3].record()
-            Kn.swiglu_quant_int8(outs["q_mlp"], outs["s_mlp"], None, ins["gate"], ins["up"], rows, cfg.inter)
-            ev[s][4].record()
+            e = ev[s]
+            e[0].record()
+            for j, (fn, fargs) in enumerate(calls):
+                status |= fn(*fargs)
+                e[j + 1].record()
             launches += 4
+        t_enqueue = time.perf_counter() - t_enqueue
         torch.cuda.synchronize()
+    if status != 0:
+        raise SystemExit("a kernel call failed: " + L.rh_last_error_string().decode())
     elapsed_ms = ev[0][0].elapsed_time(ev[K - 1][4])
     barrier()
     elapsed_ms = max_over_ranks(elapsed_ms)
@@ -364,7 +377,8 @@ def main():
                        "vocab": cfg.vocab, "seed": cfg.seed, "ops_per_step": [n for n, _ in ops],
                        "algorithmic_bytes_per_row": per_row, "parallelism": f"rows/{world}",
                        "l2": "every op streams more than the 126 MB L2 per launch (inputs larger than L2)"},
-            "ops": op_table, "roofline": roofline, "gpu_launches": launches, "clocks": clocks.summary()}
+            "ops": op_table, "roofline": roofline, "gpu_launches": launches, "clocks": clocks.summary(),
+            "host_enqueue_us_per_step": round(t_enqueue / K * 1e6, 1)}
 
     # ---- the reference's own CUDA kernels on the same buffers (rank 0, N=1) ----
     if world == 1 and not args.no_refcuda:
