@@ -211,6 +211,54 @@ def test_fused_chain_equals_reference_sequence(env, name, rows, offset):
         assert env.eq(fused[key], ref[key]), f"{name}: {key}: {env.mm(fused[key], ref[key])} of {fused[key].numel()} differ"
 
 
+def test_full_size_sweep_is_bit_exact(env):
+    """The benchmark's own workload at full size (T=65536, H=4096, I=14336, 32/8 heads x 128, seed 1): the four
+    fused launches against the reference's kernels in the reference's order, every output byte.  At this
+    size the large-batch code paths are the ones under test (bulk-copy ring, cp.async rings)."""
+    cfg = env.cfg["c4"]
+    T, H, I = cfg.tokens, cfg.hidden, cfg.inter
+    ins = env.synth.make_inputs(cfg, rows=T)
+    o = env.ops.alloc_outputs(cfg, T, slots=T)
+    from runtherder_b200 import host_path
+    q_orig, k_orig = ins["q"].clone(), ins["k"].clone()
+    assert host_path.sweep_step(cfg, ins, o) == 4
+    torch.cuda.synchronize()
+    # reference: gather; rmsnorm_add -> quantize; rope -> 2x quantize_kv; swiglu -> quantize
+    emb = torch.empty_like(o["emb"])
+    env.ref.embedding_lookup_bf16_forward(emb, ins["table"], ins["ids"], T, H)
+    assert env.eq(emb, o["emb"])
+    del emb
+    normed, h = torch.empty_like(ins["x"]), torch.empty_like(ins["x"])
+    env.ref.rmsnorm_add_bf16_forward(normed, h, ins["x"], ins["residual"], ins["g_attn"], T, H, cfg.eps)
+    q8 = torch.empty(T, H, dtype=torch.int8, device="cuda"); s8 = torch.empty(T, dtype=torch.float32, device="cuda")
+    env.ref.quantize_per_token_int8(q8, s8, normed, T, H)
+    assert env.eq(h, o["h_attn"]) and env.eq(q8, o["q_attn_in"]) and env.eq(s8, o["s_attn_in"])
+    del normed, h, q8
+    env.ref.rope_bf16(q_orig, k_orig, ins["positions"], ins["inv_freq"], T, cfg.q_heads, cfg.kv_heads, cfg.head_dim)
+    assert env.eq(q_orig, ins["q"]), f"{env.mm(q_orig, ins['q'])} rotated q values differ"
+    for src, cache, scale in ((k_orig, "k_cache", "k_scale"), (ins["v"], "v_cache", "v_scale")):
+        c = torch.zeros_like(o[cache]); sc = torch.zeros_like(o[scale])
+        env.ref.quantize_kv_fp8(c, sc, src, o["at_pos"], cfg.kv_heads, T * cfg.kv_heads, cfg.head_dim)
+        assert env.eq(c, o[cache]) and env.eq(sc, o[scale])
+    del q_orig, k_orig
+    act = torch.empty_like(ins["gate"])
+    env.ref.swiglu_bf16_forward(act, ins["gate"], ins["up"], T * I)
+    qm = torch.empty(T, I, dtype=torch.int8, device="cuda")
+    env.ref.quantize_per_token_int8(qm, s8, act, T, I)
+    assert env.eq(qm, o["q_mlp"]), f"{env.mm(qm, o['q_mlp'])} of {qm.numel()} codes differ"
+    assert env.eq(s8, o["s_mlp"])
+
+
+def test_full_size_qwen3_layer_is_bit_exact(env):
+    """One full Qwen3-8B layer (T=8192, QK-norm, bf16 outputs): fused chain vs the reference's sequence."""
+    cfg = env.cfg["c3"]
+    fused, ref = _run_both(env, cfg, cfg.tokens, 0)
+    for key in fused:
+        if key in ("launches", "emb", "at_pos"):
+            continue
+        assert env.eq(fused[key], ref[key]), f"{key}: {env.mm(fused[key], ref[key])} of {fused[key].numel()} differ"
+
+
 @pytest.mark.parametrize("T,H", [(2048, 4096), (1000, 3072), (777, 264)])
 def test_staged_rows_kernel_matches_direct(env, T, H):
     """The bulk-copy (TMA ring) variant of the row kernels, selected with rh_tune("rows_stages", n), must
