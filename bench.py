@@ -65,6 +65,16 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def sweep_config(cfg, world, rows_per_gpu):
+    """The `config` object of the throughput-sweep line; both arms print the same one."""
+    ops, per_row = step_bytes_per_row(cfg)
+    return {"workload": cfg.name, "token_rows": cfg.tokens, "rows_per_gpu": rows_per_gpu, "hidden": cfg.hidden,
+            "inter": cfg.inter, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
+            "vocab": cfg.vocab, "seed": cfg.seed, "ops_per_step": [n for n, _ in ops],
+            "algorithmic_bytes_per_row": per_row, "parallelism": f"rows/{world}",
+            "l2": "every op streams more than the 126 MB L2 per launch (inputs larger than L2)"}
+
+
 def step_bytes_per_row(cfg):
     ops = [("embedding", cfg.bytes_embedding()), ("norm_quant", cfg.bytes_norm_quant()),
            ("rope_kv", cfg.bytes_rope_kv()), ("swiglu_quant", cfg.bytes_swiglu_quant())]
@@ -205,8 +215,12 @@ def cpu_baseline(cfg, seconds: float):
     rows -= rows % threads
     t, kind, _ = cpu_rows_per_second(cfg, rows, threads)
     _, per_row = step_bytes_per_row(cfg)
+    one_rows = max(16, min(512, int(rate / threads * 3.0)))        # ~3 s of the scalar code as the reference has it
+    t1, _, _ = cpu_rows_per_second(cfg, one_rows, 1)
     return {"value": rows * per_row / t / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
             "rows_per_s": rows / t,
+            "single_thread": {"value": one_rows * per_row / t1 / 1e9, "unit": "GB/s", "rows_per_s": one_rows / t1,
+                              "sample": f"{one_rows} rows on one thread"},
             "sample": f"{rows} of {cfg.tokens} token rows of the same four ops, row-parallel over {threads} host "
                       f"threads; {'reference test helpers (double precision) for norm, RoPE, FP8 KV, SwiGLU; ' if kind == 'reference' else ''}"
                       f"oracle port for INT8 quantisation and the gather (the reference has no host code for them)"}
@@ -237,9 +251,10 @@ def run_reference_arm(args, cfg):
               f"(reference test helpers where the reference has host code, oracle port for INT8 quantisation and gather)")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in / int8+fp8 out (fp64 host arithmetic)",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f64",
+            "io_dtypes": "bf16 in; int8 / fp8-e4m3 / bf16 out (the reference's host helpers compute in double)",
             "data": "synthetic", "token_rows_per_s": rows / (total / args.steps),
-            "config": {"workload": cfg.name, "rows_per_step": rows},
+            "config": sweep_config(cfg, args.gpus, -(-cfg.tokens // max(args.gpus, 1))), "sample_rows_per_step": rows,
             "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -368,15 +383,11 @@ def main():
 
     line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 in, fp32 math, int8/fp8-e4m3 out",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "io_dtypes": "bf16 in; int8 codes, fp8-e4m3 cache bytes, fp32 scales, bf16 out",
             "data": "synthetic", "token_rows_per_s": round(T / (ms_per_step * 1e-3), 1),
             "frac_of_hbm_peak": {peak_kind: round(value / (peak * world), 4),
                                  "nominal_8TBs": round(value / (NOMINAL_HBM_GBS * world), 4)},
-            "config": {"workload": cfg.name, "token_rows": T, "rows_per_gpu": rows, "hidden": cfg.hidden,
-                       "inter": cfg.inter, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
-                       "vocab": cfg.vocab, "seed": cfg.seed, "ops_per_step": [n for n, _ in ops],
-                       "algorithmic_bytes_per_row": per_row, "parallelism": f"rows/{world}",
-                       "l2": "every op streams more than the 126 MB L2 per launch (inputs larger than L2)"},
+            "config": sweep_config(cfg, world, rows),
             "ops": op_table, "roofline": roofline, "gpu_launches": launches, "clocks": clocks.summary(),
             "host_enqueue_us_per_step": round(t_enqueue / K * 1e6, 1)}
 
@@ -469,7 +480,8 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
     value = total_bytes / (ms * 1e-3) / 1e9
     line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16 in, fp32 math, " + ("int8/fp8-e4m3 out" if cfg.int8 else "bf16/fp8-e4m3 out"),
+            "vs_baseline": None, "dtype": "f32",
+            "io_dtypes": "bf16 in; " + ("int8 codes, " if cfg.int8 else "") + "fp8-e4m3 cache bytes, fp32 scales, bf16 out",
             "data": "synthetic", "token_rows_per_s": round(T / (ms * 1e-3), 1), "us_per_layer": round(ms * 1e3 / L, 3),
             "frac_of_hbm_peak": {peak_kind: round(value / (peak * world), 4)},
             "config": {"workload": cfg.name, "token_rows": T, "rows_per_gpu": rows, "layers": L, "hidden": cfg.hidden,
