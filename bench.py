@@ -52,6 +52,8 @@ def parse_args():
     p.add_argument("--cpu-seconds", type=float, default=15.0)
     p.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                    help="layer-chain configs: replay the forward from a CUDA graph (auto: on for the decode config)")
+    p.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
+                   help="set a library tuning knob (rh_tune) before measuring, e.g. no_pdl=1; repeatable")
     return p.parse_args()
 
 
@@ -274,7 +276,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from runtherder_b200 import host_path, layer_ops, synth
+    from runtherder_b200 import host_path, kernels, layer_ops, synth
     from runtherder_b200.sharding import shard_bounds
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -284,6 +286,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    for item in args.tune:
+        key, _, value = item.partition("=")
+        kernels.tune(key, int(value))
     if world > 1:
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep stdout for the one JSON line
         dist.init_process_group("nccl", device_id=dev)

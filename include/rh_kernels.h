@@ -209,8 +209,10 @@ int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host);
 
 /* key: "rows_ctas_per_sm", "swiglu_ctas_per_sm", "rope_warps_per_cta", "embed_ctas_per_sm",
  * "swiglu_threads" (256|512), "swiglu_rcp_steps" (1|2|3 = IEEE division), "rows_stages" /
- * "swiglu_stages" (depth of the bulk-copy staging ring, 1 = direct loads); value <= 0 restores
- * the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
+ * "swiglu_stages" (depth of the bulk-copy staging ring, 1 = direct loads), "no_pdl" (1 = launch
+ * without the programmatic-dependent-launch attribute; by default each kernel may be scheduled
+ * while the previous kernel of its stream drains and orders itself on the device before its first
+ * memory access, so stream semantics are unchanged); value <= 0 restores the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
 int rh_tune(const char* key, int value);
 
 #ifdef __cplusplus

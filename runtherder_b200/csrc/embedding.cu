@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(kEmbThreads) embedding_kernel(uint4* __restric
                                                                 const int* __restrict__ ids,
                                                                 long long num_tokens, int n_vecs) {
     long long row = blockIdx.x;
+    pdl_enter();
     if (row >= num_tokens) return;
     int id = __ldg(ids + row);
     while (row < num_tokens) {
@@ -56,6 +57,7 @@ __global__ void __launch_bounds__(256) dequant_w8a8_kernel(__nv_bfloat16* __rest
                                                            const __nv_bfloat16* __restrict__ w_scale,
                                                            long long m, int n) {
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    pdl_enter();
     if constexpr (kVec4) {
         const int n4 = n >> 2;
         const long long total = m * n4;
@@ -91,6 +93,7 @@ __global__ void __launch_bounds__(256) qkv_bias_add_kernel(uint4* __restrict__ q
                                                            long long total, int q_vecs, int kv_vecs) {
     const int row_vecs = q_vecs + 2 * kv_vecs;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    pdl_enter();
     for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const long long row = idx / row_vecs;
         int col = static_cast<int>(idx - row * row_vecs);
@@ -121,11 +124,13 @@ __global__ void __launch_bounds__(256) qkv_bias_add_kernel(uint4* __restrict__ q
 // include/runtherder/engine/context.h:41-45 — three synchronous cudaMemcpy per generated token).
 __global__ void stage_positions_kernel(int* __restrict__ positions, int* __restrict__ decode_pos, int start_pos, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_enter();
     if (i < n) positions[i] = start_pos + i;            // std::iota(positions, start_pos)
     if (i == 0 && decode_pos != nullptr) *decode_pos = start_pos;
 }
 __global__ void decode_advance_kernel(int* __restrict__ token_slot, int* __restrict__ position, int* __restrict__ decode_pos,
                                       const int* __restrict__ next_token, int step) {
+    pdl_enter();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         if (token_slot != nullptr && next_token != nullptr) *token_slot = *next_token;
         if (position != nullptr) *position += step;
@@ -143,7 +148,7 @@ extern "C" int rh_stage_positions(int* positions, int* decode_pos_or_null, int s
     RH_REQUIRE(positions != nullptr, RH_ERR_INVALID_ARG, "rh_stage_positions: null pointer");
     RH_REQUIRE(n >= 1, RH_ERR_INVALID_ARG, "rh_stage_positions: stage needs at least one token");
     RH_REQUIRE(start_pos >= 0, RH_ERR_INVALID_ARG, "rh_stage_positions: start_pos must be >= 0");
-    stage_positions_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(positions, decode_pos_or_null, start_pos, n);
+    host::launch(stage_positions_kernel, dim3((n + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), positions, decode_pos_or_null, start_pos, n);
     return host::check_launch("stage_positions_kernel");
 }
 
@@ -152,7 +157,7 @@ extern "C" int rh_decode_advance(int* token_slot_or_null, int* position_or_null,
     RH_REQUIRE(position_or_null || decode_pos_or_null || token_slot_or_null, RH_ERR_INVALID_ARG,
                "rh_decode_advance: nothing to advance");
     RH_REQUIRE(step >= 0, RH_ERR_INVALID_ARG, "rh_decode_advance: step must be >= 0");
-    decode_advance_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(token_slot_or_null, position_or_null,
+    host::launch(decode_advance_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), token_slot_or_null, position_or_null,
                                                                          decode_pos_or_null, next_token_or_null, step);
     return host::check_launch("decode_advance_kernel");
 }
@@ -172,7 +177,7 @@ extern "C" int rh_qkv_bias_add_bf16(void* q, void* k, void* v, const void* q_bia
     long long grid = (total + 255) / 256;
     const long long cap = static_cast<long long>(host::num_sms()) * 16;
     if (grid > cap) grid = cap;
-    qkv_bias_add_kernel<<<static_cast<unsigned>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+    host::launch(qkv_bias_add_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, static_cast<cudaStream_t>(stream), 
         static_cast<uint4*>(q), static_cast<uint4*>(k), static_cast<uint4*>(v), static_cast<const uint4*>(q_bias),
         static_cast<const uint4*>(k_bias), static_cast<const uint4*>(v_bias), total, q_vecs, kv_vecs);
     return host::check_launch("qkv_bias_add_kernel");
@@ -190,7 +195,7 @@ extern "C" int rh_embedding_lookup_bf16(void* out, const void* table, const int*
     if (per_sm <= 0) per_sm = 64;   // pure copy: resident CTAs = bytes in flight
     const long long cap = static_cast<long long>(host::num_sms()) * per_sm;
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
-    embedding_kernel<<<grid, kEmbThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    host::launch(embedding_kernel, dim3(grid), dim3(kEmbThreads), 0, static_cast<cudaStream_t>(stream), 
         static_cast<uint4*>(out), static_cast<const uint4*>(table), token_ids, num_tokens, hidden_dim / kVec);
     return host::check_launch("embedding_kernel");
 }
@@ -208,10 +213,10 @@ extern "C" int rh_dequantize_w8a8(void* y, const int32_t* acc, const float* x_sc
     if (grid > cap) grid = cap;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (vec4)
-        dequant_w8a8_kernel<true><<<static_cast<unsigned>(grid), 256, 0, s>>>(
+        host::launch(dequant_w8a8_kernel<true>, dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
             static_cast<__nv_bfloat16*>(y), acc, x_scale, static_cast<const __nv_bfloat16*>(w_scale), m, n);
     else
-        dequant_w8a8_kernel<false><<<static_cast<unsigned>(grid), 256, 0, s>>>(
+        host::launch(dequant_w8a8_kernel<false>, dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
             static_cast<__nv_bfloat16*>(y), acc, x_scale, static_cast<const __nv_bfloat16*>(w_scale), m, n);
     return host::check_launch("dequant_w8a8_kernel");
 }

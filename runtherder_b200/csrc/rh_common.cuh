@@ -260,6 +260,20 @@ __device__ __forceinline__ float group_max(float v) {
     return v;
 }
 
+// Programmatic dependent launch.  Every kernel of this library calls pdl_wait() before its first
+// access to global memory: it returns once the preceding kernel of the stream has completed and its
+// writes are visible (at once when the launch carried no programmatic attribute).  pdl_trigger()
+// lets the following kernel's CTAs be placed on SMs as soon as every CTA of this grid has called it
+// or exited; those CTAs then block in their own pdl_wait().  Row-persistent kernels trigger when a
+// CTA starts its last row, so that dependents arrive while the tail drains and do not sit on the
+// SMs for the whole kernel; one-shot kernels trigger straight after the wait (pdl_enter).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() {
+    pdl_wait();
+    pdl_trigger();
+}
+
 }  // namespace rh
 
 // ---- host side -----------------------------------------------------------------------------
@@ -276,7 +290,26 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kSwigluThreads,
                 kSwigluRcpSteps, kRowsStages, kSwigluStages, kRowsSmemH, kRowsPrefetch,
-                kSwigluPrefetch, kTuneSlots };
+                kSwigluPrefetch, kNoPdl, kTuneSlots };
+
+// Launches `kernel` with the programmatic-stream-serialization attribute (unless rh_tune("no_pdl", 1)):
+// the kernel may be scheduled while the previous kernel of `stream` drains; it orders itself with
+// pdl_enter().  Inside stream capture the edge becomes a programmatic dependency of the graph.
+// A failure is left in the runtime's last-error slot for check_launch().
+template <typename... P, typename... A>
+inline void launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = tuning(kNoPdl) != 0 ? 0 : 1;
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
 
 }  // namespace rh::host
 

@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(256) rope_kv_generic_kernel(const RopeArgs p) 
     const int warps_per_cta = blockDim.x >> 5;
     const long long item = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
     const long long num_items = static_cast<long long>(p.seq_len) * p.items_per_token;
+    pdl_enter();
     if (item >= num_items) return;  // whole warps only: shuffles below stay convergent
 
     const int token = static_cast<int>(item / p.items_per_token);
@@ -217,6 +218,7 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
     const int warps_per_cta = blockDim.x >> 5;
     const long long item = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
     const long long num_items = static_cast<long long>(p.seq_len) * p.items_per_token;
+    pdl_enter();
     if (item >= num_items) return;  // whole warps only
 
     const int token = static_cast<int>(item / p.items_per_token);
@@ -375,6 +377,7 @@ __global__ void rope_generic_kernel(__nv_bfloat16* q, __nv_bfloat16* k, const in
                                     int num_kv_heads, int head_dim) {
     const int half = head_dim >> 1;
     const int heads = num_q_heads + num_kv_heads;
+    pdl_enter();
     for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total_pairs;
          idx += static_cast<long long>(gridDim.x) * blockDim.x) {
         const int i = static_cast<int>(idx % half);
@@ -419,19 +422,19 @@ int launch_rope(RopeArgs p, bool norm, bool kv, cudaStream_t stream) {
     if (aligned) {
         const size_t smem = static_cast<size_t>(warps) * kRopeDepth * 64 * sizeof(uint4);   // <= 32 KB
         if (kv) {
-            if (norm) rope_kv_kernel<D, true, true><<<g, b, smem, stream>>>(p);
-            else rope_kv_kernel<D, false, true><<<g, b, smem, stream>>>(p);
+            if (norm) host::launch(rope_kv_kernel<D, true, true>, dim3(g), dim3(b), smem, stream, p);
+            else host::launch(rope_kv_kernel<D, false, true>, dim3(g), dim3(b), smem, stream, p);
         } else {
-            if (norm) rope_kv_kernel<D, true, false><<<g, b, smem, stream>>>(p);
-            else rope_kv_kernel<D, false, false><<<g, b, smem, stream>>>(p);
+            if (norm) host::launch(rope_kv_kernel<D, true, false>, dim3(g), dim3(b), smem, stream, p);
+            else host::launch(rope_kv_kernel<D, false, false>, dim3(g), dim3(b), smem, stream, p);
         }
     } else {
         if (kv) {
-            if (norm) rope_kv_generic_kernel<D, true, true><<<g, b, 0, stream>>>(p);
-            else rope_kv_generic_kernel<D, false, true><<<g, b, 0, stream>>>(p);
+            if (norm) host::launch(rope_kv_generic_kernel<D, true, true>, dim3(g), dim3(b), 0, stream, p);
+            else host::launch(rope_kv_generic_kernel<D, false, true>, dim3(g), dim3(b), 0, stream, p);
         } else {
-            if (norm) rope_kv_generic_kernel<D, true, false><<<g, b, 0, stream>>>(p);
-            else rope_kv_generic_kernel<D, false, false><<<g, b, 0, stream>>>(p);
+            if (norm) host::launch(rope_kv_generic_kernel<D, true, false>, dim3(g), dim3(b), 0, stream, p);
+            else host::launch(rope_kv_generic_kernel<D, false, false>, dim3(g), dim3(b), 0, stream, p);
         }
     }
     return host::check_launch("rope_kv_kernel");
@@ -481,7 +484,7 @@ extern "C" int rh_rope_bf16(void* q, void* k, const int* positions, const float*
     long long grid = (pairs + 255) / 256;
     const long long cap = static_cast<long long>(host::num_sms()) * 16;
     if (grid > cap) grid = cap;
-    rope_generic_kernel<<<static_cast<unsigned>(grid), 256, 0, s>>>(
+    host::launch(rope_generic_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
         static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), positions, inv_freq, pairs,
         num_q_heads, num_kv_heads, head_dim);
     return host::check_launch("rope_generic_kernel");

@@ -234,6 +234,7 @@ rows_kernel(const RowArgs a) {
     __shared__ float s_mx[2][kRowWarps];
     __shared__ float4 s_h[kSmemH ? VPT * 2 * kRowThreads : 1];
     extern __shared__ uint4 pre[];   // [kDepth][kOps][VPT][256], thread-private columns
+    pdl_wait();
     const RowCtx c = make_ctx<F>(a);
     uint4 gw[VPT];
     load_gains<VPT, F>(a, c.n_vecs, gw);
@@ -262,6 +263,7 @@ rows_kernel(const RowArgs a) {
 
     int parity = 0, slot = 0;
     for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
+        if (row + gridDim.x >= a.num_rows) pdl_trigger();   // last row of this CTA
         uint4 xv[VPT], rv[VPT];
         if constexpr (kDepth > 0) {
             cp_async_wait<kDepth - 1>();
@@ -326,6 +328,7 @@ rows_staged_kernel(const RowArgs a, const int stages, int* error_word) {
         pipe::mbar_init_fence();
     }
     __syncthreads();
+    pdl_wait();
 
     if (threadIdx.x >= kRowThreads) {   // producer warp: one thread issues every copy of this CTA
         if (threadIdx.x == kRowThreads) {
@@ -356,6 +359,7 @@ rows_staged_kernel(const RowArgs a, const int stages, int* error_word) {
     int parity = 0, s = 0;
     uint32_t phase = 0;
     for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
+        if (row + gridDim.x >= a.num_rows) pdl_trigger();   // last row of this CTA
         uint4 xv[VPT], rv[VPT];
 #pragma unroll
         for (int sl = 0; sl < VPT; ++sl) {
@@ -390,6 +394,7 @@ __global__ void __launch_bounds__(kRowThreads) short_rows_kernel(const RowArgs a
     const bool active = sub < n_vecs;
     const float dim_f = static_cast<float>(a.dim);
 
+    pdl_enter();
     uint4 gw = make_uint4(0, 0, 0, 0);
     if (kNorm && active) gw = ld_weight(static_cast<const uint4*>(a.g) + sub);
     long long slot_base = 0;
@@ -474,7 +479,7 @@ void launch_long(const RowArgs& a, cudaStream_t stream) {
         const int tuned = host::tuning(host::kRowsCtasPerSm);
         const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
         const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-        rows_staged_kernel<VPT, F><<<grid, kRowThreads + 32, smem, stream>>>(a, stages, host::device_error_word());
+        host::launch(rows_staged_kernel<VPT, F>, dim3(grid), dim3(kRowThreads + 32), smem, stream, a, stages, host::device_error_word());
         return;
     }
     const int tuned = host::tuning(host::kRowsCtasPerSm);
@@ -501,7 +506,7 @@ void launch_long(const RowArgs& a, cudaStream_t stream) {
                 const int per_sm = tuned > 0 ? tuned : (resident < 3 ? resident : 3);
                 const long long cap = static_cast<long long>(host::num_sms()) * per_sm;
                 const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-                rows_kernel<VPT, F, kSm, kD><<<grid, kRowThreads, smem, stream>>>(a);
+                host::launch(rows_kernel<VPT, F, kSm, kD>, dim3(grid), dim3(kRowThreads), smem, stream, a);
             };
             if (depth == 1) go(std::integral_constant<int, 1>{});
             else if (depth == 2) go(std::integral_constant<int, 2>{});
@@ -514,14 +519,14 @@ void launch_long(const RowArgs& a, cudaStream_t stream) {
             static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F, true>), kRowThreads);
             const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
             const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-            rows_kernel<VPT, F, true><<<grid, kRowThreads, 0, stream>>>(a);
+            host::launch(rows_kernel<VPT, F, true>, dim3(grid), dim3(kRowThreads), 0, stream, a);
             return;
         }
     }
     static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F>), kRowThreads);
     const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
     const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-    rows_kernel<VPT, F><<<grid, kRowThreads, 0, stream>>>(a);
+    host::launch(rows_kernel<VPT, F>, dim3(grid), dim3(kRowThreads), 0, stream, a);
 }
 
 template <unsigned F>
@@ -535,12 +540,12 @@ int launch_rows(const RowArgs& a, cudaStream_t stream) {
         const long long cap = static_cast<long long>(host::num_sms()) * 8;
         const int grid = static_cast<int>(want < cap ? want : cap);
         switch (lanes) {
-            case 1: short_rows_kernel<1, F><<<grid, kRowThreads, 0, stream>>>(a); break;
-            case 2: short_rows_kernel<2, F><<<grid, kRowThreads, 0, stream>>>(a); break;
-            case 4: short_rows_kernel<4, F><<<grid, kRowThreads, 0, stream>>>(a); break;
-            case 8: short_rows_kernel<8, F><<<grid, kRowThreads, 0, stream>>>(a); break;
-            case 16: short_rows_kernel<16, F><<<grid, kRowThreads, 0, stream>>>(a); break;
-            default: short_rows_kernel<32, F><<<grid, kRowThreads, 0, stream>>>(a); break;
+            case 1: host::launch(short_rows_kernel<1, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 2: host::launch(short_rows_kernel<2, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 4: host::launch(short_rows_kernel<4, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 8: host::launch(short_rows_kernel<8, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 16: host::launch(short_rows_kernel<16, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            default: host::launch(short_rows_kernel<32, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
         }
         return host::check_launch("short_rows_kernel");
     }

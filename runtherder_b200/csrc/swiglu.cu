@@ -84,6 +84,7 @@ template <int kSteps>
 __global__ void __launch_bounds__(kElemThreads) swiglu_kernel(uint4* __restrict__ y, const uint4* gate,
                                                               const uint4* up, long long n_vec) {
     const long long base = static_cast<long long>(blockIdx.x) * (kElemThreads * kElemUnroll) + threadIdx.x;
+    pdl_enter();
     uint4 gv[kElemUnroll], uv[kElemUnroll];
 #pragma unroll
     for (int k = 0; k < kElemUnroll; ++k) {
@@ -108,9 +109,11 @@ swiglu_quant_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, void* y
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_vecs = inter_dim / kVec;
     __shared__ float s_mx[2][kWarps];
+    pdl_wait();
 
     int parity = 0;
     for (long long row = blockIdx.x; row < num_tokens; row += gridDim.x, parity ^= 1) {
+        if (row + gridDim.x >= num_tokens) pdl_trigger();   // last row of this CTA
         const size_t row_off = static_cast<size_t>(row) * n_vecs;
         const uint4* g_row = static_cast<const uint4*>(gate) + row_off;
         const uint4* u_row = static_cast<const uint4*>(up) + row_off;
@@ -231,6 +234,7 @@ swiglu_quant_staged_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, 
         pipe::mbar_init_fence();
     }
     __syncthreads();
+    pdl_wait();
 
     if (tid >= kThreads) {
         if (tid == kThreads) {
@@ -256,6 +260,7 @@ swiglu_quant_staged_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, 
     int parity = 0, s = 0;
     uint32_t phase = 0;
     for (long long row = blockIdx.x; row < num_tokens; row += gridDim.x, parity ^= 1) {
+        if (row + gridDim.x >= num_tokens) pdl_trigger();   // last row of this CTA
         const size_t row_off = static_cast<size_t>(row) * n_vecs;
         uint4 yw[VPT];
         uint32_t m2 = 0u, gmin = kGateMinInit;
@@ -355,7 +360,7 @@ int launch_swiglu_quant_staged(int8_t* q, float* x_scale, void* y, const void* g
     const int tuned = host::tuning(host::kSwigluCtasPerSm);
     const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
-    swiglu_quant_staged_kernel<VPT, kStoreY, kSteps><<<grid, 256 + 32, smem, stream>>>(q, x_scale, y, gate, up, num_tokens,
+    host::launch(swiglu_quant_staged_kernel<VPT, kStoreY, kSteps>, dim3(grid), dim3(256 + 32), smem, stream, q, x_scale, y, gate, up, num_tokens,
                                                                                        inter_dim, stages, host::device_error_word());
     return host::check_launch("swiglu_quant_staged_kernel");
 }
@@ -373,6 +378,7 @@ swiglu_quant_prefetch_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_vecs = inter_dim / kVec;
     const int slots_per_row = (n_vecs + kThreads - 1) / kThreads;
+    pdl_wait();
 
     // producer cursor: the next (row, slot-in-row) to fetch
     long long p_row = blockIdx.x;
@@ -394,6 +400,7 @@ swiglu_quant_prefetch_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale
 
     int parity = 0, ring = 0;
     for (long long row = blockIdx.x; row < num_tokens; row += gridDim.x, parity ^= 1) {
+        if (row + gridDim.x >= num_tokens) pdl_trigger();   // last row of this CTA
         const size_t row_off = static_cast<size_t>(row) * n_vecs;
         uint4 yw[VPT];
         uint32_t m2 = 0u, gmin = kGateMinInit;
@@ -490,7 +497,7 @@ int launch_swiglu_quant_prefetch(int8_t* q, float* x_scale, void* y, const void*
     const int tuned = host::tuning(host::kSwigluCtasPerSm);
     const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
-    swiglu_quant_prefetch_kernel<VPT, kStoreY, 1, kDepth><<<grid, 256, smem, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
+    host::launch(swiglu_quant_prefetch_kernel<VPT, kStoreY, 1, kDepth>, dim3(grid), dim3(256), smem, stream, q, x_scale, y, gate, up, num_tokens, inter_dim);
     return host::check_launch("swiglu_quant_prefetch_kernel");
 }
 
@@ -505,8 +512,8 @@ int launch_swiglu_quant_steps(int8_t* q, float* x_scale, void* y, const void* ga
     const long long cap =
         static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : (y ? resident_y : resident_n));
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
-    if (y) swiglu_quant_kernel<kThreads, VPT, true, kSteps><<<grid, kThreads, 0, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
-    else swiglu_quant_kernel<kThreads, VPT, false, kSteps><<<grid, kThreads, 0, stream>>>(q, x_scale, y, gate, up, num_tokens, inter_dim);
+    if (y) host::launch(swiglu_quant_kernel<kThreads, VPT, true, kSteps>, dim3(grid), dim3(kThreads), 0, stream, q, x_scale, y, gate, up, num_tokens, inter_dim);
+    else host::launch(swiglu_quant_kernel<kThreads, VPT, false, kSteps>, dim3(grid), dim3(kThreads), 0, stream, q, x_scale, y, gate, up, num_tokens, inter_dim);
     return host::check_launch("swiglu_quant_kernel");
 }
 
@@ -569,9 +576,9 @@ extern "C" int rh_swiglu_bf16(void* y, const void* gate, const void* up, long lo
     uint4* yp = static_cast<uint4*>(y);
     const uint4 *gp = static_cast<const uint4*>(gate), *up_ = static_cast<const uint4*>(up);
     switch (rcp_steps()) {
-        case 0: swiglu_kernel<0><<<g, kElemThreads, 0, s>>>(yp, gp, up_, n_vec); break;
-        case 1: swiglu_kernel<1><<<g, kElemThreads, 0, s>>>(yp, gp, up_, n_vec); break;
-        default: swiglu_kernel<2><<<g, kElemThreads, 0, s>>>(yp, gp, up_, n_vec); break;
+        case 0: host::launch(swiglu_kernel<0>, dim3(g), dim3(kElemThreads), 0, s, yp, gp, up_, n_vec); break;
+        case 1: host::launch(swiglu_kernel<1>, dim3(g), dim3(kElemThreads), 0, s, yp, gp, up_, n_vec); break;
+        default: host::launch(swiglu_kernel<2>, dim3(g), dim3(kElemThreads), 0, s, yp, gp, up_, n_vec); break;
     }
     return host::check_launch("swiglu_kernel");
 }

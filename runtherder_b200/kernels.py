@@ -58,6 +58,11 @@ def _fp8_ptr(t, numel, name):
     return _ptr(t, None, numel, name)
 
 
+def tune(key: str, value: int) -> None:
+    """Set a process-wide tuning knob of the library (`rh_tune`); value <= 0 restores the default."""
+    call("rh_tune", key.encode(), int(value))
+
+
 def rmsnorm_bf16_forward(y, x, g, num_tokens: int, hidden_dim: int, eps: float, stream=None) -> None:
     """y = (x / rms(x)) * g; y may alias x.  (rmsnorm.cuh:15-22)"""
     n = num_tokens * hidden_dim

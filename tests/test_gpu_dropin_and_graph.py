@@ -116,3 +116,78 @@ def test_decode_glue_advances_positions_inside_a_graph():
         g.replay()
     torch.cuda.synchronize()
     assert seen.tolist() == [[5, 100, 100], [12, 101, 101], [19, 102, 102], [26, 103, 103]]
+
+
+def test_dependent_launch_keeps_stream_order_for_device_scalars_and_in_place_chains():
+    """Kernels are launched so that each may be scheduled while its predecessor drains and orders itself
+    on the device.  A captured run of 64 steps [append a KV row at *at_pos; advance *at_pos] (read-after-
+    write on the scalar, kernel to kernel) and an in-place chain rmsnorm_add -> swiglu -> quantise on
+    shared buffers (write-after-read) must give exactly the bytes of the same calls launched without the
+    attribute and with a synchronise between them."""
+    from gpu_util import bits_equal
+    from runtherder_b200 import kernels as K
+    steps, hkv, d, hidden = 64, 8, 128, 1024
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(steps, hkv * d, device="cuda", generator=gen).to(torch.bfloat16)
+    at_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def append_all(sync):
+        cache = torch.zeros(steps + 2, hkv, d, dtype=torch.uint8, device="cuda")
+        scale = torch.zeros(steps + 2, hkv, dtype=torch.float32, device="cuda")
+        at_pos.fill_(1)
+        for s in range(steps):
+            K.quantize_kv_fp8(cache, scale, x[s], at_pos, hkv, hkv, d)
+            K.decode_advance(None, None, at_pos, None, 1)
+            if sync:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return cache, scale
+
+    K.tune("no_pdl", 1)
+    want_cache, want_scale = append_all(sync=True)
+    K.tune("no_pdl", 0)
+    got_cache, got_scale = append_all(sync=False)
+    assert at_pos.item() == 1 + steps
+    assert bits_equal(got_cache, want_cache) and bits_equal(got_scale, want_scale)
+    assert bool((want_scale[1:steps + 1] > 0).all()) and bool((want_scale[0] == 0).all())
+
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    cache = torch.zeros_like(want_cache)
+    scale = torch.zeros_like(want_scale)
+    with torch.cuda.stream(side):
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for s in range(steps):
+                K.quantize_kv_fp8(cache, scale, x[s], at_pos, hkv, hkv, d)
+                K.decode_advance(None, None, at_pos, None, 1)
+    at_pos.fill_(1)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert bits_equal(cache, want_cache) and bits_equal(scale, want_scale)
+
+    rows = 300
+    h0 = torch.randn(rows, hidden, device="cuda", generator=gen).to(torch.bfloat16)
+    mlp = torch.randn(rows, hidden, device="cuda", generator=gen).to(torch.bfloat16)
+    g = torch.randn(hidden, device="cuda", generator=gen).to(torch.bfloat16)
+
+    def chain(sync):
+        h, y, t = h0.clone(), torch.empty_like(h0), mlp.clone()
+        q = torch.empty(rows, hidden, dtype=torch.int8, device="cuda")
+        qs = torch.empty(rows, dtype=torch.float32, device="cuda")
+        for _ in range(6):
+            K.rmsnorm_add_bf16_forward(y, h, t, h, g, rows, hidden, 1e-5)      # h updated in place, y written
+            if sync: torch.cuda.synchronize()
+            K.swiglu_bf16_forward(t, y, t, rows * hidden)                      # t overwritten from y and itself
+            if sync: torch.cuda.synchronize()
+            K.quantize_per_token_int8(q, qs, t, rows, hidden)
+            if sync: torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        return h, y, t, q, qs
+
+    K.tune("no_pdl", 1)
+    want = chain(sync=True)
+    K.tune("no_pdl", 0)
+    got = chain(sync=False)
+    for a, b in zip(got, want):
+        assert bits_equal(a, b)
