@@ -52,6 +52,11 @@ def parse_args():
     p.add_argument("--cpu-seconds", type=float, default=15.0)
     p.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                    help="layer-chain configs: replay the forward from a CUDA graph (auto: on for the decode config)")
+    p.add_argument("--attention", action="store_true",
+                   help="with --config c2: time the split-KV flash decode over the FP8 cache at that depth instead "
+                        "of the row-wise chain (secondary line; not the headline metric)")
+    p.add_argument("--depth", type=int, default=0, help="--attention: override the context depth (keys attended)")
+    p.add_argument("--splits", type=int, default=32, help="--attention: split count (the reference uses 32)")
     p.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
                    help="set a library tuning knob (rh_tune) before measuring, e.g. no_pdl=1; repeatable")
     return p.parse_args()
@@ -305,6 +310,11 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    if args.attention:
+        if world != 1:
+            raise SystemExit("--attention is a single-GPU measurement (one query token does not shard)")
+        run_decode_attention(args, cfg, dev)
+        return
     if args.config != "c4":
         run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks)
         if world > 1:
@@ -510,6 +520,108 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
             line["ref_cuda"] = {"unavailable": str(exc)[:200]}
     if rank == 0:
         print(json.dumps(line), flush=True)
+
+
+def run_decode_attention(args, cfg, dev):
+    """Secondary measurement: one decode step's attention per layer — rh_flash_decode_split_bf16 over a
+    seeded FP8 cache of `depth` keys, one distinct cache per layer (28 x 16.8 MB at the decode config, more
+    than L2), replayed as one CUDA graph like the reference's decode loop.  Algorithmic bytes per call: the K
+    and V codes and their scales of every key, once (2*D + 8 bytes per key and kv head)."""
+    import math
+    import torch
+    from runtherder_b200 import kernels as Kn
+    depth = args.depth or (cfg.start_pos + 1)
+    Hq, Hkv, D, L, S = cfg.q_heads, cfg.kv_heads, cfg.head_dim, cfg.layers, args.splits
+    n_sets = int(min(L, max(2, 3e9 // (depth * Hkv * (2 * D + 8)))))
+    gen = torch.Generator(device=dev).manual_seed(cfg.seed + 77)
+    at0 = torch.zeros(1, dtype=torch.int32, device=dev)
+    sets = []
+    for _ in range(n_sets):
+        q = torch.randn(Hq, D, device=dev, generator=gen).to(torch.bfloat16)
+        kc = torch.empty(depth, Hkv, D, dtype=torch.uint8, device=dev); vc = torch.empty_like(kc)
+        ks = torch.empty(depth, Hkv, dtype=torch.float32, device=dev); vs = torch.empty_like(ks)
+        for codes, scales in ((kc, ks), (vc, vs)):
+            x = torch.randn(depth, Hkv, D, device=dev, generator=gen).to(torch.bfloat16)
+            Kn.quantize_kv_fp8(codes, scales, x, at0, 1, depth * Hkv, D)
+        sets.append((q, kc, ks, vc, vs))
+    cache_len = torch.tensor([depth - 1], dtype=torch.int32, device=dev)
+    partial = torch.empty(Kn.flash_split_scratch_floats(Hq, D, S), dtype=torch.float32, device=dev)
+    out = torch.empty(Hq, D, dtype=torch.bfloat16, device=dev)
+    scale = 1.0 / math.sqrt(D)
+
+    def forward_with(fn):
+        for l in range(L):
+            q, kc, ks, vc, vs = sets[l % n_sets]
+            fn(out, q, kc, vc, ks, vs, partial, S, cache_len, Hq, Hkv, D, scale)
+
+    def timed(fn, reps):
+        side = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(side):
+            forward_with(fn)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                forward_with(fn)
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        with ClockSampler(dev.index or 0) as clocks:
+            a.record()
+            for _ in range(reps):
+                graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps, clocks.summary()
+
+    K = args.steps
+    ms, clocks = timed(Kn.flash_decode_split_bf16, K)
+    bytes_per_call = depth * Hkv * (2 * D + 8)
+    peak, peak_kind = measured_peak()
+    achieved = bytes_per_call * L / (ms * 1e-3) / 1e9
+    line = {"metric": "flash-decode KV-cache GB/s", "value": round(achieved, 1), "unit": "GB/s", "n_gpus": 1, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "us_per_call": round(ms * 1e3 / L, 2),
+            "higher_is_better": True, "scaling": "replicas only", "vs_baseline": None, "dtype": "f32",
+            "io_dtypes": "bf16 q, fp8-e4m3 cache codes + fp32 scales in; bf16 out (f16 tensor-core operands, fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": f"{cfg.name}: decode attention", "depth": depth, "q_heads": Hq, "kv_heads": Hkv,
+                       "head_dim": D, "splits": S, "layers": L, "cache_sets": n_sets, "cuda_graph": True,
+                       "algorithmic_bytes_per_call": bytes_per_call,
+                       "l2": f"{n_sets} distinct caches of {bytes_per_call / 1e6:.1f} MB replayed in turn"},
+            "gpu_launches": 2 * L * K, "launches_per_step": 2 * L, "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "flash_decode_partial + reduce", "achieved": round(achieved, 1),
+                         "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
+                         "traffic": None,
+                         "note": "per-call time includes two graph-node launches; short histories are latency-bound"}}
+    if not args.no_refcuda:
+        try:
+            sys.path.insert(0, str(ROOT / "tests"))
+            from gpu_util import RefCuda
+            ref = RefCuda()
+
+            def ref_fn(out_, q, kc, vc, ks, vs, part, S_, cl, Hq_, Hkv_, D_, sc):
+                ref.flash_decode_split_bf16(out_, q, kc, vc, ks, vs, part, S_, cl, Hq_, Hkv_, D_, sc)
+            rms, _ = timed(ref_fn, max(3, min(K, 20)))
+            line["ref_cuda"] = {"us_per_call": round(rms * 1e3 / L, 2), "value": round(bytes_per_call * L / (rms * 1e-3) / 1e9, 1),
+                                "unit": "GB/s (same algorithmic bytes)", "launches_per_step": 2 * L,
+                                "what": "reference src/kernels/flash_decode.cu compiled for sm_100a, same caches, same graph replay"}
+        except Exception as exc:
+            line["ref_cuda"] = {"unavailable": str(exc)[:200]}
+    if not args.no_cpu:
+        try:
+            sys.path.insert(0, str(ROOT / "tests"))
+            from gpu_util import to_np
+            from oracle_lib import Oracle
+            orc = Oracle()
+            q, kc, ks, vc, vs = (to_np(t) for t in sets[0])
+            t0 = time.perf_counter()
+            orc.attention_decode_fp8(q, kc, vc, ks, vs, depth - 1, scale)
+            dt = time.perf_counter() - t0
+            line["cpu_baseline"] = {"value": round(bytes_per_call / dt / 1e9, 4), "unit": "GB/s", "cores": 1, "kind": "port",
+                                    "sample": f"one call ({depth} keys, {Hq} heads) of the double-precision oracle, {dt:.2f} s"}
+        except Exception as exc:
+            line["cpu_baseline"] = {"unavailable": str(exc)[:200]}
+    print(json.dumps(line), flush=True)
 
 
 def chain_roofline(cfg, i, o, rows, peak, peak_kind):

@@ -62,4 +62,11 @@ void qkv_bias_add_bf16_forward(__nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16
                                const __nv_bfloat16* k_bias, const __nv_bfloat16* v_bias, int n, int q_dim,
                                int kv_dim, cudaStream_t stream = nullptr);
 
+// include/runtherder/kernels/flash_decode.cuh:27-62 (the scratch size stays the reference's constexpr
+// flash_split_scratch_floats, same layout; rh_flash_split_scratch_floats is its C twin)
+void flash_decode_split_bf16(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_fp8_e4m3* k,
+                             const __nv_fp8_e4m3* v, const float* k_scale, const float* v_scale, float* partial,
+                             int num_splits, const int* cache_len, int num_q_heads, int num_kv_heads,
+                             int head_dim, float scale, cudaStream_t stream = nullptr);
+
 }  // namespace runtherder::kernels

@@ -101,6 +101,24 @@ int rh_embedding_lookup_bf16(void* out, const void* table, const int* token_ids,
 int rh_qkv_bias_add_bf16(void* q, void* k, void* v, const void* q_bias, const void* k_bias,
                          const void* v_bias, int n, int q_dim, int kv_dim, void* stream);
 
+/* Floats of scratch that rh_flash_decode_split_bf16 needs for `max_splits` splits: [Hq, splits] m,
+ * then l, then [Hq, splits, head_dim] acc in one slab (0 for non-positive arguments).
+ * Replaces flash_split_scratch_floats (include/runtherder/kernels/flash_decode.cuh:11-25). */
+size_t rh_flash_split_scratch_floats(int num_q_heads, int head_dim, int max_splits);
+
+/* Split-KV flash decode of one query token over the FP8 cache: out[h,:] = softmax_j(scale * q[h] .
+ * K[j,kvh]) V[j,kvh] over keys j = 0 .. *cache_len, K/V = E4M3 code * per-(token, kv head) scale
+ * (layout: include/runtherder/attention/kv_view.h:8-19); *cache_len is read on the device.
+ * `partial` is caller-owned scratch of rh_flash_split_scratch_floats(Hq, D, num_splits) floats;
+ * any num_splits >= 1 is correct at any *cache_len.  head_dim in {32, 64, 128, 256}.  The result
+ * differs from a serial fp32 evaluation by float reassociation only (at most 1 bf16 ulp).
+ * Replaces flash_decode_split_bf16 (include/runtherder/kernels/flash_decode.cuh:27-62,
+ * src/kernels/flash_decode.cu:271-325; called from src/attention/adaptive.cu:30-33). */
+int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_t* k, const uint8_t* v,
+                               const float* k_scale, const float* v_scale, float* partial, int num_splits,
+                               const int* cache_len, int num_q_heads, int num_kv_heads, int head_dim,
+                               float scale, void* stream);
+
 /* ---- Fused entry points (new; each equals a chain of the reference's calls) --------------- */
 
 /* [residual add +] RMSNorm + per-token INT8 quantisation in one pass over the row.

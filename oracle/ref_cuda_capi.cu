@@ -1,5 +1,5 @@
 // C-linkage entry points onto the reference's own CUDA kernels
-// (src/kernels/{rmsnorm,quantization,rope,activation,embedding}.cu), which the
+// (src/kernels/{rmsnorm,quantization,rope,activation,embedding,attention,flash_decode}.cu), which the
 // Makefile compiles for sm_100a from where they lie and links with this file
 // into _ref/libref_cuda.so.  It is the GPU-side oracle (identical intrinsics
 // and operation order) and the CUDA baseline the benchmark times beside the
@@ -7,6 +7,8 @@
 #include <cstdint>
 
 #include <runtherder/kernels/activation.cuh>
+#include <runtherder/kernels/attention.cuh>
+#include <runtherder/kernels/flash_decode.cuh>
 #include <runtherder/kernels/embedding.cuh>
 #include <runtherder/kernels/quantization.cuh>
 #include <runtherder/kernels/rmsnorm.cuh>
@@ -65,6 +67,25 @@ void refcuda_embedding_lookup(void* out, const void* table, const int* ids, int 
                               int hidden_dim, void* stream) {
     rk::embedding_lookup_bf16_forward(static_cast<bf16*>(out), static_cast<const bf16*>(table), ids,
                                       num_tokens, hidden_dim, static_cast<cudaStream_t>(stream));
+}
+
+// The naive causal attention the reference's flash tests use as their oracle.
+void refcuda_attention_causal(void* out, const void* q, const void* k, const void* v, const float* k_scale,
+                              const float* v_scale, int n_new, const int* cache_len, int num_q_heads,
+                              int num_kv_heads, int head_dim, float scale, void* stream) {
+    rk::attention_causal_bf16(static_cast<bf16*>(out), static_cast<const bf16*>(q),
+                              static_cast<const __nv_fp8_e4m3*>(k), static_cast<const __nv_fp8_e4m3*>(v), k_scale,
+                              v_scale, n_new, cache_len, num_q_heads, num_kv_heads, head_dim, scale,
+                              static_cast<cudaStream_t>(stream));
+}
+
+void refcuda_flash_decode_split(void* out, const void* q, const void* k, const void* v, const float* k_scale,
+                                const float* v_scale, float* partial, int num_splits, const int* cache_len,
+                                int num_q_heads, int num_kv_heads, int head_dim, float scale, void* stream) {
+    rk::flash_decode_split_bf16(static_cast<bf16*>(out), static_cast<const bf16*>(q),
+                                static_cast<const __nv_fp8_e4m3*>(k), static_cast<const __nv_fp8_e4m3*>(v), k_scale,
+                                v_scale, partial, num_splits, cache_len, num_q_heads, num_kv_heads, head_dim, scale,
+                                static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

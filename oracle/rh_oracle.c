@@ -322,6 +322,58 @@ ORC_API void orc_add_rows(uint16_t* out, const uint16_t* x, const uint16_t* bias
 }
 
 /* ------------------------------------------------------------------------ */
+/* Decode attention over the FP8 cache: the formula of the reference's naive  */
+/* kernel (src/kernels/attention.cu:31-86 at n_new == 1, which its own        */
+/* tests/kernels/test_flash_decode.cpp:117-126 uses as the oracle of          */
+/* flash_decode_split_bf16): scores q . (code * k_scale) * scale over keys     */
+/* 0..cache_len, softmax, weighted sum of code * v_scale, bf16 output.  The   */
+/* reference evaluates it in fp32 in a kernel-specific order and documents    */
+/* that orders differ "in the last bits, not in value"                        */
+/* (include/runtherder/kernels/flash_decode.cuh:45-46); this restatement       */
+/* evaluates it in double, so it is the value every order approximates.       */
+/* out_f32 (optional) receives the unrounded result.  No host counterpart in  */
+/* the reference: pinned on the GPU, within one bf16 ulp, to the reference's  */
+/* naive and split kernels built for sm_100a.                                 */
+/* ------------------------------------------------------------------------ */
+ORC_API void orc_attention_decode_fp8(uint16_t* out, float* out_f32, const uint16_t* q, const uint8_t* k,
+                                      const uint8_t* v, const float* k_scale, const float* v_scale,
+                                      int cache_len, int num_q_heads, int num_kv_heads, int head_dim,
+                                      float scale, double* score_buf /* cache_len + 1 doubles */) {
+    const int n_keys = cache_len + 1;
+    const int group = num_q_heads / num_kv_heads;
+    for (int qh = 0; qh < num_q_heads; ++qh) {
+        const int kvh = qh / group;
+        const uint16_t* q_row = q + (size_t)qh * head_dim;
+        double m = -INFINITY;
+        for (int j = 0; j < n_keys; ++j) {
+            const size_t row = (size_t)j * num_kv_heads + kvh;
+            double s = 0.0;
+            for (int d = 0; d < head_dim; ++d)
+                s += (double)orc_bf16_to_f32(q_row[d]) *
+                     ((double)orc_e4m3_to_f32(k[row * head_dim + d]) * (double)k_scale[row]);
+            s *= (double)scale;
+            score_buf[j] = s;
+            if (s > m) m = s;
+        }
+        double denom = 0.0;
+        for (int j = 0; j < n_keys; ++j) {
+            score_buf[j] = exp(score_buf[j] - m);
+            denom += score_buf[j];
+        }
+        for (int d = 0; d < head_dim; ++d) {
+            double acc = 0.0;
+            for (int j = 0; j < n_keys; ++j) {
+                const size_t row = (size_t)j * num_kv_heads + kvh;
+                acc += score_buf[j] * ((double)orc_e4m3_to_f32(v[row * head_dim + d]) * (double)v_scale[row]);
+            }
+            const float r = (float)(acc / denom);
+            if (out_f32) out_f32[(size_t)qh * head_dim + d] = r;
+            out[(size_t)qh * head_dim + d] = orc_f32_to_bf16(r);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------ */
 /* Chains, as the reference's layer composition issues them.  Each stage     */
 /* rounds to bf16 exactly where the reference stores a bf16 tensor.          */
 /* ------------------------------------------------------------------------ */

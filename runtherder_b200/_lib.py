@@ -32,6 +32,8 @@ SIGNATURES = {
     "rh_rope_bf16": [_p, _p, _p, _p, _i, _i, _i, _i, _p],
     "rh_embedding_lookup_bf16": [_p, _p, _p, _i, _i, _p],
     "rh_qkv_bias_add_bf16": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p],
+    "rh_flash_split_scratch_floats": [_i, _i, _i],
+    "rh_flash_decode_split_bf16": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
     "rh_rmsnorm_add_quant_int8": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p],
     "rh_swiglu_quant_int8": [_p, _p, _p, _p, _p, _i, _i, _p],
     "rh_rope_kv_fp8": [_p, _p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
@@ -48,7 +50,8 @@ SIGNATURES = {
     "rh_selfcheck_bounded_wait": [_i, _p, _p],
     "rh_selftest_static": [_p, _i, _p],
 }
-_RESTYPES = {"rh_status_string": C.c_char_p, "rh_last_error_string": C.c_char_p}
+_RESTYPES = {"rh_status_string": C.c_char_p, "rh_last_error_string": C.c_char_p,
+             "rh_flash_split_scratch_floats": C.c_size_t}
 
 
 class RhError(RuntimeError):

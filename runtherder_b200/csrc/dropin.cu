@@ -73,4 +73,15 @@ void qkv_bias_add_bf16_forward(__nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16
                  "qkv_bias_add_bf16_forward");
 }
 
+void flash_decode_split_bf16(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_fp8_e4m3* k,
+                             const __nv_fp8_e4m3* v, const float* k_scale, const float* v_scale, float* partial,
+                             int num_splits, const int* cache_len, int num_q_heads, int num_kv_heads,
+                             int head_dim, float scale, cudaStream_t stream) {
+    die_on_error(rh_flash_decode_split_bf16(out, q, reinterpret_cast<const std::uint8_t*>(k),
+                                            reinterpret_cast<const std::uint8_t*>(v), k_scale, v_scale, partial,
+                                            num_splits, cache_len, num_q_heads, num_kv_heads, head_dim, scale,
+                                            stream),
+                 "flash_decode_split_bf16");
+}
+
 }  // namespace runtherder::kernels

@@ -19,7 +19,8 @@ TensorOrPtr = Union[torch.Tensor, int, None]
 __all__ = [
     "RhError", "rmsnorm_bf16_forward", "rmsnorm_add_bf16_forward", "quantize_per_token_int8",
     "dequantize_w8a8", "quantize_kv_fp8", "dequantize_kv_fp8", "swiglu_bf16_forward", "rope_bf16",
-    "embedding_lookup_bf16_forward", "qkv_bias_add_bf16_forward", "stage_positions", "decode_advance", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
+    "embedding_lookup_bf16_forward", "qkv_bias_add_bf16_forward", "stage_positions", "decode_advance",
+    "flash_split_scratch_floats", "flash_decode_split_bf16", "tune", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
 ]
 
 
@@ -146,6 +147,24 @@ def decode_advance(token_slot, position, decode_pos, next_token, step: int = 1, 
     """token_slot[0] = next_token[0]; position[0] += step; decode_pos[0] += step — graph-capturable step update."""
     call("rh_decode_advance", _ptr(token_slot, _I32, 1, "token_slot"), _ptr(position, _I32, 1, "position"),
          _ptr(decode_pos, _I32, 1, "decode_pos"), _ptr(next_token, _I32, 1, "next_token"), step, _stream(stream))
+
+
+def flash_split_scratch_floats(num_q_heads: int, head_dim: int, max_splits: int) -> int:
+    """Floats of scratch a split decode needs (flash_decode.cuh:11-25)."""
+    from ._lib import lib
+    return int(lib.rh_flash_split_scratch_floats(num_q_heads, head_dim, max_splits))
+
+
+def flash_decode_split_bf16(out, q, k, v, k_scale, v_scale, partial, num_splits: int, cache_len, num_q_heads: int,
+                            num_kv_heads: int, head_dim: int, scale: float, stream=None) -> None:
+    """One query token attends keys 0..*cache_len of the FP8 cache; cache_len is a device-resident int32,
+    partial caller-owned fp32 scratch of flash_split_scratch_floats(...) floats.  (flash_decode.cuh:27-62)"""
+    need = flash_split_scratch_floats(num_q_heads, head_dim, num_splits)
+    call("rh_flash_decode_split_bf16", _ptr(out, _BF, num_q_heads * head_dim, "out"),
+         _ptr(q, _BF, num_q_heads * head_dim, "q"), _fp8_ptr(k, None, "k"), _fp8_ptr(v, None, "v"),
+         _ptr(k_scale, _F32, None, "k_scale"), _ptr(v_scale, _F32, None, "v_scale"),
+         _ptr(partial, _F32, need, "partial"), num_splits, _ptr(cache_len, _I32, 1, "cache_len"), num_q_heads,
+         num_kv_heads, head_dim, float(scale), _stream(stream))
 
 
 # ---- fused entry points ---------------------------------------------------------------------

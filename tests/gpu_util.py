@@ -79,3 +79,13 @@ class RefCuda:
 
     def embedding_lookup_bf16_forward(self, out, table, ids, T, H, stream=None):
         self.lib.refcuda_embedding_lookup(out.data_ptr(), table.data_ptr(), ids.data_ptr(), T, H, _s(stream))
+
+    def attention_causal_bf16(self, out, q, k, v, k_scale, v_scale, n_new, cache_len, Hq, Hkv, D, scale, stream=None):
+        self.lib.refcuda_attention_causal(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), k_scale.data_ptr(),
+                                          v_scale.data_ptr(), n_new, cache_len.data_ptr(), Hq, Hkv, D, scale, _s(stream))
+
+    def flash_decode_split_bf16(self, out, q, k, v, k_scale, v_scale, partial, num_splits, cache_len, Hq, Hkv, D, scale,
+                                stream=None):
+        self.lib.refcuda_flash_decode_split(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                            k_scale.data_ptr(), v_scale.data_ptr(), partial.data_ptr(), num_splits,
+                                            cache_len.data_ptr(), Hq, Hkv, D, scale, _s(stream))

@@ -46,6 +46,7 @@ def load_oracle() -> C.CDLL:
         "orc_rmsnorm_add_quant_int8": ([_p, _p, _p, _p, _p, _p, _p, _l, _i, _f, _p], None),
         "orc_swiglu_quant_int8": ([_p, _p, _p, _p, _p, _l, _i], None),
         "orc_rope_kv_fp8": ([_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _l, _i, _i, _i], None),
+        "orc_attention_decode_fp8": ([_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p], None),
         "orc_synth_normal_bf16": ([_p, _sz, _u64, _u64, _u64, _f, _p, _i], None),
         "orc_synth_uniform_bf16": ([_p, _sz, _u64, _u64, _u64, _f, _f], None),
         "orc_synth_ids_i32": ([_p, _sz, _u64, _u64, _u64, _i32], None),
@@ -107,6 +108,8 @@ def load_ref_cuda():
         "refcuda_swiglu": [_p, _p, _p, _i, _p],
         "refcuda_rope": [_p, _p, _p, _p, _i, _i, _i, _i, _p],
         "refcuda_embedding_lookup": [_p, _p, _p, _i, _i, _p],
+        "refcuda_attention_causal": [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
+        "refcuda_flash_decode_split": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)
@@ -156,6 +159,17 @@ class Oracle:
         q, s = np.zeros((total, D), np.uint8), np.zeros(total, np.float32)
         self.lib.orc_quantize_kv_fp8(ptr(q), ptr(s), ptr(x), at_pos, rows_per_pos, R, D)
         return q, s
+
+    def attention_decode_fp8(self, q, k, v, k_scale, v_scale, cache_len, scale):
+        """q [Hq, D] bf16 bits; k, v [n, Hkv, D] uint8 codes; scales [n, Hkv] -> (bf16 bits, float32) [Hq, D]."""
+        Hq, D = q.shape
+        Hkv = k.shape[1]
+        out = np.empty((Hq, D), np.uint16)
+        out_f = np.empty((Hq, D), np.float32)
+        buf = np.empty(cache_len + 1, np.float64)
+        self.lib.orc_attention_decode_fp8(ptr(out), ptr(out_f), ptr(q), ptr(k), ptr(v), ptr(k_scale), ptr(v_scale),
+                                          cache_len, Hq, Hkv, D, scale, ptr(buf))
+        return out, out_f
 
     def add_rows(self, x, bias):
         n, dim = x.shape

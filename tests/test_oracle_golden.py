@@ -203,3 +203,31 @@ def test_oracle_matches_compiled_reference_live():
     tt = t.copy()
     ref.refhost_rope(ptr(tt), 40000, 3, 5, 96, 500000.0)
     assert np.array_equal(ORC.rope_theta(t.reshape(3, 5, 96), 40000, 500000.0).ravel(), tt)
+
+
+def test_attention_oracle_is_within_one_ulp_of_the_reference_kernels():
+    """The reference has no host attention; its naive kernel (the oracle of its flash tests) and its split
+    decode kernel were run on a B200 by tests/golden/make_golden_attention.py.  The double-precision
+    restatement must round to within one bf16 ulp of both on every element that is not a cancellation
+    residue, and within 1.5 * 2^-7 of the row maximum everywhere."""
+    data = np.load(GOLD / "reference_cuda_attention.npz")
+    cases = data["cases"]
+    assert len(cases) >= 5
+
+    def ordered(bits):
+        b = bits.astype(np.int32)
+        return np.where(b & 0x8000, -(b & 0x7FFF), b & 0x7FFF)
+
+    for idx, (cache_len, Hq, Hkv, D, _splits, _q_mul) in enumerate(cases):
+        cache_len, D = int(cache_len), int(D)
+        g = lambda name: np.ascontiguousarray(data[f"case{idx}/{name}"])
+        bits, exact = ORC.attention_decode_fp8(g("q"), g("k_codes"), g("v_codes"), g("k_scale"), g("v_scale"),
+                                               cache_len, 1.0 / np.sqrt(np.float32(D)).item())
+        rowmax = np.abs(exact).max(axis=1, keepdims=True)
+        significant = np.abs(exact) >= rowmax / 64
+        for name in ("out_naive", "out_split"):
+            ref_bits = g(name)
+            ref_val = (ref_bits.astype(np.uint32) << 16).view(np.float32)
+            assert (np.abs(ref_val - exact) <= 1.5 * 2.0 ** -7 * rowmax).all(), (idx, name)
+            assert np.abs(ordered(ref_bits) - ordered(bits))[significant].max() <= 1, (idx, name)
+            assert (ordered(ref_bits) == ordered(bits)).mean() > 0.99, (idx, name)
