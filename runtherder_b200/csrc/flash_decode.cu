@@ -6,25 +6,29 @@
 // its group and spends ~30 warp instructions per key and query head on scalar dequantise + FMA.
 //
 // Here a CTA owns (kv head, split) and serves every query head of the group from one pass over the
-// rows, so the cache is read once.  The two contractions run on the tensor cores as
-// mma.sync.m16n8k16 (f16 inputs, fp32 accumulate): the query heads are rows 0..7 of the 16-row tile
-// (the op is bound by HBM and by instruction issue, not by tensor throughput, and a decode step has
-// no 64-row tile to give a tcgen05 instruction); rows 8..15 carry the low halves of the softmax
-// weights in the second product, so weights enter with 22 bits.  E4M3 converts to f16 exactly with
-// one cvt per pair of codes, and the per-key scales never touch the operands:
-//   score_j  = (q . Kcodes_j) * ks_j * scale            -> applied to the fp32 accumulator
-//   O        = sum_j 2^(score_j + lg2 vs_j - m) Vcodes_j -> the V scale rides in the exponent
-//   l        = sum_j 2^(score_j - m)                     -> m = running max of score_j + lg2 vs_j
+// rows, so the cache is read once.  Both contractions run on the tensor cores as mma.sync.m16n8k16
+// (f16 inputs, fp32 accumulate) in the form that fills the 16-row operand with cache data and puts
+// the few query heads on the 8-wide side — the op is bound by HBM and by instruction issue, and a
+// decode step has no 64-row tile to give a tcgen05 instruction:
+//   S^T[16 keys x 8 cols]  = K[16 keys x 16 dims]    . q^T[16 dims x 8 cols]   per k-step
+//   O^T[16 dims x 8 cols] += V^T[16 dims x 16 keys]  . W^T[16 keys x 8 cols]   per 16-dim block
+// E4M3 converts to f16 exactly, two codes per cvt, and the per-key scales never touch the operands:
+//   score_j  = (q . Kcodes_j) * ks_j * scale             -> applied to the fp32 accumulator
+//   O        = sum_j 2^(score_j + lg2 vs_j - m) Vcodes_j  -> the V scale rides in the exponent
+//   l        = sum_j 2^(score_j - m)                      -> m = running max of score_j + lg2 vs_j
 // so the weights handed to the second mma lie in (0, 1] whatever the scales are.  q is scaled by a
 // power of two per head into f16's normal range (exact), the weights by 2^10 to keep small ones out
-// of the f16 subnormals; both factors are divided out again in fp32.
+// of the f16 subnormals; both factors are divided out again in fp32.  A weight enters as hi + lo
+// (two f16, 22 bits): with at most four query heads per kv head the lo halves ride in the four idle
+// columns of the same mma, wider groups issue a second one.
 //
-// Layout tricks that keep the key loop free of barriers and cross-lane traffic: the dot product over
-// head_dim is order-free, so lane (r, c) of a warp takes a quarter of a K row (every fourth 16-byte
-// chunk) and consumes it 4 bytes per k-step; the sum over keys is order-free too, so lane (r, c)
-// takes keys 4c..4c+3 of a 16-key tile for the PV product and transposes their bytes into key pairs
-// with four prmt per 16 bytes.  Each lane stages exactly the bytes it consumes through its own slots
-// of a cp.async ring, several tiles ahead.
+// Layout tricks that keep the key loop free of barriers: the dot product over head_dim is
+// order-free, so lane (r, c) of a warp takes a quarter of the K rows of keys r and r+8 of a tile
+// (every fourth 16-byte chunk) and consumes it 4 bytes per k-step; the sum over keys is order-free
+// too, so lane (r, c) takes keys 4c..4c+3 for the second product and transposes their bytes into key
+// pairs with four prmt per 16 bytes; the weights change from "row = key" to "row = column" with one
+// movmatrix per 8 keys.  Each lane stages exactly the bytes it consumes through its own slots of a
+// cp.async ring, several tiles ahead.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
@@ -38,12 +42,15 @@ namespace {
 
 constexpr int kFdWarps = 4;
 constexpr int kFdThreads = kFdWarps * 32;
-constexpr int kFdTileKeys = 16;        // keys per warp iteration = one k16 step of the PV product
-constexpr int kFdRows = 8;             // query heads per CTA (rows 0..7 of the m16 tile)
+constexpr int kFdSubKeys = 16;         // one k16 step of the second product
+constexpr int kFdSubs = 1;              // sub-tiles folded together per trip (2 = two independent instruction
+                                        // streams per warp: measured no faster, 20 more registers)
+constexpr int kFdTileKeys = kFdSubs * kFdSubKeys;   // keys per warp iteration
+constexpr int kFdCols = 8;             // the 8-wide side of both products
 constexpr float kFdLog2e = 1.4426950408889634f;
 constexpr float kFdMInit = -1.0e30f;   // running max before any key (finite: differences stay defined)
 constexpr float kFdLgFloor = -100.0f;  // floor of lg2(v_scale): a zero scale must not give -inf - -inf
-constexpr float kFdWeightShift = 10.0f;  // PV weights are 2^10 * softmax weight in f16
+constexpr float kFdWeightShift = 10.0f;  // weights enter the second product as 2^10 * softmax weight
 
 struct FdArgs {
     const __nv_bfloat16* q;
@@ -57,13 +64,16 @@ struct FdArgs {
     int num_q_heads;
     int num_kv_heads;
     int group;          // query heads per kv head
-    int row_chunks;     // ceil(group / 8): CTAs per (kv head, split)
+    int heads_per_cta;  // 4 (hi and lo halves of the weights share one mma) or 8
+    int row_chunks;     // ceil(group / heads_per_cta): CTAs per (kv head, split)
     float scale_log2e;  // softmax scale * log2(e)
 };
 
-__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_codes) {
-    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_codes), __NV_E4M3);
-    return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+// Four E4M3 codes of a 32-bit word -> two f16x2 (codes 0,1 and codes 2,3).
+__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t word, uint32_t& lo, uint32_t& hi) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+        : "=r"(lo), "=r"(hi)
+        : "r"(word));
 }
 
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
@@ -71,22 +81,21 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// D(16x8, fp32) += A(16x16, f16, row) * B(16x8, f16, col); rows 8..15 of A are zero here.
-__device__ __forceinline__ void mma_rows8(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    const uint32_t zero = 0u;
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(zero), "r"(a2), "r"(zero), "r"(b0), "r"(b1));
-}
-
-// Same with all 16 rows of A in use: rows 8..15 carry the low halves of the weights.
-__device__ __forceinline__ void mma_rows16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                           uint32_t b0, uint32_t b1) {
+// D(16x8, fp32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 8x8 transpose of 16-bit elements across the warp: lane (r, c) gives elements (r, 2c), (r, 2c+1)
+// and receives (2c, r), (2c+1, r).
+__device__ __forceinline__ uint32_t transpose_8x8_b16(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
 }
 
 // w = hi + lo with hi = f16(w), lo = f16(w - hi): 22 significant bits across the two halves.
@@ -108,9 +117,19 @@ __device__ __forceinline__ float lg2_approx(float x) {
     return y;
 }
 
-// cp.async of kBytes (4, 8 or 16) from global to shared memory; an invalid source zero-fills.
+// cp.async of kBytes (4, 8 or 16) from global to shared memory.
 template <int kBytes>
-__device__ __forceinline__ void fd_cp_async(void* smem_dst, const void* gmem_src, bool valid) {
+__device__ __forceinline__ void fd_cp_async(void* smem_dst, const void* gmem_src) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    if constexpr (kBytes == 16) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(gmem_src), "n"(kBytes) : "memory");
+    }
+}
+// The same with a validity flag: an invalid source is not read and the destination is zero-filled.
+template <int kBytes>
+__device__ __forceinline__ void fd_cp_async_zfill(void* smem_dst, const void* gmem_src, bool valid) {
     const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
     const int src_bytes = valid ? kBytes : 0;
     if constexpr (kBytes == 16) {
@@ -137,7 +156,7 @@ __device__ __forceinline__ void fd_lds(uint32_t* dst, const unsigned char* src) 
 
 // Geometry of the per-warp staging ring.  A stage holds one 16-key tile exactly as the lanes consume
 // it: every lane copies (cp.async) the bytes it will itself read back, so a stage needs no barrier,
-// only the lane's own wait_group.  [2 K blocks][chunks][32 lanes] + [4 V keys][chunks][32 lanes] + 32 scales.
+// only the lane's own wait_group.  [2 K rows][chunks][32 lanes] + [4 V keys][chunks][32 lanes] + 32 scales.
 template <int D>
 struct FdRing {
     static constexpr int kKChunk = (D / 4 >= 16) ? 16 : D / 4;   // bytes per cp.async of a K quarter-row
@@ -146,16 +165,17 @@ struct FdRing {
     static constexpr int kVChunks = (D / 8) / kVChunk;
     static constexpr int kKBytes = 2 * (D / 4) * 32;
     static constexpr int kVBytes = 4 * (D / 8) * 32;
-    static constexpr int kStageBytes = kKBytes + kVBytes + 32 * 4;
-    static constexpr int kStages = (D <= 128) ? 4 : 3;
+    static constexpr int kSubBytes = kKBytes + kVBytes + 32 * 4;   // one 16-key sub-tile
+    static constexpr int kStageBytes = kFdSubs * kSubBytes;
+    static constexpr int kStages = 4;
     static constexpr int kRingBytes = kFdWarps * kStages * kStageBytes;
-    static constexpr int kOPitch = 66;   // see the merge below
-    static constexpr int kMergeBytes = kFdWarps * (D / 8) * kOPitch * 4 + 2 * kFdWarps * kFdRows * 4;
+    // merge buffers: per warp the accumulators as the lanes hold them, then m and l per column
+    static constexpr int kMergeBytes = kFdWarps * (D / 16) * 32 * 16 + 2 * kFdWarps * kFdCols * 4;
     static constexpr int kSmemBytes = kRingBytes > kMergeBytes ? kRingBytes : kMergeBytes;
 };
 
-// One 16-key tile as a warp holds it: lane (r, c) has the c-th quarter of the K rows of columns r of
-// the two 8-key blocks, and 1/8 of the V rows of keys 4c..4c+3.
+// One 16-key tile as a warp holds it: lane (r, c) has its quarter of the K rows of (tile-local) keys
+// ka = 4*(r/2) + r%2 and kb = ka + 2, and its eighth of the V rows of keys 4c..4c+3.
 template <int D>
 struct FdTile {
     uint32_t kw[2][D / 16];
@@ -169,30 +189,26 @@ struct FdTile {
 // the current one is computed (at the reference's 32 splits and depth 8196 that is a warp's whole
 // share, in flight at once).  The four states are merged through shared memory (reusing the ring)
 // and written to the scratch slab as (m, l, acc[D]) per query head.
-template <int D>
-__global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 3 : 1)) flash_decode_partial_kernel(const FdArgs p) {
+// kWide: more than four query heads per CTA — the eight columns are eight heads and the weights'
+// low halves take a second mma; otherwise columns 4..7 repeat heads 0..3 and carry the low halves.
+template <int D, bool kWide>
+__global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_partial_kernel(const FdArgs p) {
     using Ring = FdRing<D>;
-    constexpr int kKWords = D / 16;   // 32-bit words of a K row per lane (= k-steps of the QK product)
+    constexpr int kKWords = D / 16;   // 32-bit words of a K row per lane (= k-steps of the first product)
     constexpr int kVWords = D / 32;   // 32-bit words of a V row per lane
-    constexpr int kNB = D / 8;        // 8-wide output blocks of the PV product
+    constexpr int kMB = D / 16;       // 16-dim blocks of the second product
+    constexpr int kHeads = kWide ? 8 : 4;
     static_assert(D == 32 || D == 64 || D == 128 || D == 256, "head_dim");
 
     extern __shared__ __align__(16) unsigned char fd_smem[];
-    // After the key loop the ring is reused for the merge.  Per warp and output block: 8 rows x 8
-    // columns of the accumulator tile, padded to 66 floats so that the 8-byte stores of a block and
-    // the reads across blocks both spread over all banks.
-    constexpr int kOPitch = Ring::kOPitch;
-    float* const s_o = reinterpret_cast<float*>(fd_smem);                       // [warp][nb][kOPitch]
-    float* const s_m = s_o + kFdWarps * kNB * kOPitch;                          // [warp][row]
-    float* const s_l = s_m + kFdWarps * kFdRows;                                // [warp][row]
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r = lane >> 2, c = lane & 3;
     const int kvh = blockIdx.x / p.row_chunks;
     const int chunk = blockIdx.x - kvh * p.row_chunks;
     const int split = blockIdx.y;
-    const int head_in_group = chunk * kFdRows + r;
-    const bool row_valid = head_in_group < p.group;
+    const int head_in_group = chunk * kHeads + (kWide ? r : (r & 3));   // the head of column r
+    const bool col_valid = head_in_group < p.group;
     const int qh = kvh * p.group + head_in_group;
 
     pdl_enter();
@@ -207,10 +223,16 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 3 : 1)) flash_decode_p
     const int end = min(tile_hi * kFdTileKeys, n_keys);
 
     const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * D;   // bytes between keys
+    const int key_a = 4 * (r >> 1) + (r & 1);                            // tile-local key of row r (row r+8: +2)
     // Lane c takes chunk c of every group of four kKChunk-byte chunks of a K row (not one contiguous
     // quarter): the four lanes of a row then cover whole 32-byte sectors with each copy instruction.
-    const uint8_t* k_lane = p.k + static_cast<size_t>(kvh) * D + c * Ring::kKChunk;
-    const uint8_t* v_lane = p.v + static_cast<size_t>(kvh) * D + r * (D / 8);
+    const uint8_t* const k_lane = p.k + static_cast<size_t>(kvh) * D + c * Ring::kKChunk + key_a * row_stride;
+    const uint8_t* const k_lane_b = k_lane + 2 * row_stride;   // row r+8 of the tile
+    const uint8_t* const v_lane = p.v + static_cast<size_t>(kvh) * D + r * (D / 8) + (4 * c) * row_stride;
+    const uint8_t* const v_lane1 = v_lane + row_stride;
+    const uint8_t* const v_lane2 = v_lane1 + row_stride;
+    const uint8_t* const v_lane3 = v_lane2 + row_stride;
+    const float* const s_lane = (lane >= 16 ? p.v_scale : p.k_scale) + static_cast<size_t>(lane & 15) * p.num_kv_heads + kvh;
 
     const int my_tiles = n_tiles > warp ? (n_tiles - warp + kFdWarps - 1) / kFdWarps : 0;
     unsigned char* const ring = fd_smem + static_cast<size_t>(warp) * Ring::kStages * Ring::kStageBytes;
@@ -218,38 +240,53 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 3 : 1)) flash_decode_p
     // issue the copies of this warp's i-th tile (or nothing) and close the group
     auto issue_tile = [&](int i) {
         if (i < my_tiles) {
-            const int kb = start + (warp + i * kFdWarps) * kFdTileKeys;
-            unsigned char* const st = ring + (i % Ring::kStages) * Ring::kStageBytes;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int key = kb + 4 * (r >> 1) + 2 * j + (r & 1);   // column r of 8-key block j
-                const bool live = key < end;
-                const uint8_t* src = live ? k_lane + static_cast<size_t>(key) * row_stride : p.k;
+            for (int u = 0; u < kFdSubs; ++u) {
+                const int kb = start + (warp + i * kFdWarps) * kFdTileKeys + u * kFdSubKeys;
+                unsigned char* const st = ring + (i % Ring::kStages) * Ring::kStageBytes + u * Ring::kSubBytes;
+                const size_t off = static_cast<size_t>(kb) * row_stride;
+                const float* const s_src = s_lane + static_cast<size_t>(kb) * p.num_kv_heads;
+                if (kb + kFdSubKeys <= end) {   // every sub-tile but the last of the history
 #pragma unroll
-                for (int ch = 0; ch < Ring::kKChunks; ++ch)
-                    fd_cp_async<Ring::kKChunk>(st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk,
-                                               src + ch * 4 * Ring::kKChunk, live);
+                    for (int j = 0; j < 2; ++j)
+#pragma unroll
+                        for (int ch = 0; ch < Ring::kKChunks; ++ch)
+                            fd_cp_async<Ring::kKChunk>(st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk,
+                                                       (j == 0 ? k_lane : k_lane_b) + off + ch * 4 * Ring::kKChunk);
+#pragma unroll
+                    for (int i4 = 0; i4 < 4; ++i4)
+#pragma unroll
+                        for (int ch = 0; ch < Ring::kVChunks; ++ch)
+                            fd_cp_async<Ring::kVChunk>(st + Ring::kKBytes + ((i4 * Ring::kVChunks + ch) * 32 + lane) * Ring::kVChunk,
+                                                       (i4 == 0 ? v_lane : i4 == 1 ? v_lane1 : i4 == 2 ? v_lane2 : v_lane3) + off + ch * Ring::kVChunk);
+                    fd_cp_async<4>(st + Ring::kKBytes + Ring::kVBytes + lane * 4, s_src);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const bool live = kb + key_a + 2 * j < end;
+#pragma unroll
+                        for (int ch = 0; ch < Ring::kKChunks; ++ch)
+                            fd_cp_async_zfill<Ring::kKChunk>(st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk,
+                                                             live ? k_lane + off + (2 * j) * row_stride + ch * 4 * Ring::kKChunk : p.k, live);
+                    }
+#pragma unroll
+                    for (int i4 = 0; i4 < 4; ++i4) {
+                        const bool live = kb + 4 * c + i4 < end;
+#pragma unroll
+                        for (int ch = 0; ch < Ring::kVChunks; ++ch)
+                            fd_cp_async_zfill<Ring::kVChunk>(st + Ring::kKBytes + ((i4 * Ring::kVChunks + ch) * 32 + lane) * Ring::kVChunk,
+                                                             live ? v_lane + off + i4 * row_stride + ch * Ring::kVChunk : p.v, live);
+                    }
+                    const bool live = kb + (lane & 15) < end;
+                    fd_cp_async_zfill<4>(st + Ring::kKBytes + Ring::kVBytes + lane * 4, live ? s_src : p.k_scale, live);
+                }
             }
-#pragma unroll
-            for (int i4 = 0; i4 < 4; ++i4) {
-                const int key = kb + 4 * c + i4;
-                const bool live = key < end;
-                const uint8_t* src = live ? v_lane + static_cast<size_t>(key) * row_stride : p.v;
-#pragma unroll
-                for (int ch = 0; ch < Ring::kVChunks; ++ch)
-                    fd_cp_async<Ring::kVChunk>(st + Ring::kKBytes + ((i4 * Ring::kVChunks + ch) * 32 + lane) * Ring::kVChunk,
-                                               src + ch * Ring::kVChunk, live);
-            }
-            const int key = kb + (lane & 15);
-            const bool live = key < end;
-            const float* src = (lane >= 16 ? p.v_scale : p.k_scale) + (live ? static_cast<size_t>(key) * p.num_kv_heads + kvh : 0);
-            fd_cp_async<4>(st + Ring::kKBytes + Ring::kVBytes + lane * 4, src, live);
         }
         cp_async_commit();
     };
-    // read back what this lane copied for its i-th tile
-    auto read_tile = [&](FdTile<D>& tl, int i) {
-        const unsigned char* const st = ring + (i % Ring::kStages) * Ring::kStageBytes;
+    // read back what this lane copied for sub-tile u of its i-th tile
+    auto read_tile = [&](FdTile<D>& tl, int i, int u) {
+        const unsigned char* const st = ring + (i % Ring::kStages) * Ring::kStageBytes + u * Ring::kSubBytes;
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -268,12 +305,13 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 3 : 1)) flash_decode_p
 #pragma unroll
     for (int i = 0; i < Ring::kStages - 1; ++i) issue_tile(i);   // in flight while q is prepared
 
-    // ---- q fragment: head r, the lane's quarter of the dims, scaled by a power of two into (-2, 2) ----
-    uint32_t qa0[kKWords], qa2[kKWords];
-    float row_factor = 0.0f;   // scale * log2e * 2^e: turns the raw accumulator into log2-domain scores
+    // ---- q as the B operand: column r, the lane's quarter of the dims, scaled by a power of two
+    //      into (-2, 2); word s holds the four dims of k-step s ----
+    uint32_t qb0[kKWords], qb1[kKWords];
+    float factor0, factor1;   // scale * log2e * 2^e of the heads of columns 2c and 2c+1
     {
         float qf[D / 4];
-        if (row_valid) {
+        if (col_valid) {
             const __nv_bfloat16* src = p.q + static_cast<size_t>(qh) * D + c * Ring::kKChunk;   // same dims as k_lane
 #pragma unroll
             for (int i = 0; i < D / 4; i += 2) {
@@ -295,130 +333,179 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 3 : 1)) flash_decode_p
         e = amax > 0.0f ? max(-100, min(100, e)) : 0;
         const float down = __int_as_float((127 - e) << 23);   // 2^-e
         const float up = __int_as_float((127 + e) << 23);     // 2^e
-        row_factor = p.scale_log2e * up;
+        const float factor = p.scale_log2e * up;               // of column r
+        factor0 = __shfl_sync(0xffffffffu, factor, 4 * (2 * c));
+        factor1 = __shfl_sync(0xffffffffu, factor, 4 * (2 * c + 1));
 #pragma unroll
         for (int s = 0; s < kKWords; ++s) {
-            qa0[s] = pack_f16x2(qf[4 * s] * down, qf[4 * s + 1] * down);
-            qa2[s] = pack_f16x2(qf[4 * s + 2] * down, qf[4 * s + 3] * down);
+            qb0[s] = pack_f16x2(qf[4 * s] * down, qf[4 * s + 1] * down);
+            qb1[s] = pack_f16x2(qf[4 * s + 2] * down, qf[4 * s + 3] * down);
         }
     }
 
-    float o[kNB][4];
+    // accumulator of block mb: [dim 16r+2mb][col 2c], [same][col 2c+1], [dim 16r+2mb+1][col 2c], [same][col 2c+1]
+    float o[kMB][4];
 #pragma unroll
-    for (int nb = 0; nb < kNB; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.0f;
-    float m_run = kFdMInit, l_run = 0.0f;
+    for (int mb = 0; mb < kMB; ++mb) o[mb][0] = o[mb][1] = o[mb][2] = o[mb][3] = 0.0f;
+    float m0 = kFdMInit, m1 = kFdMInit, l0 = 0.0f, l1 = 0.0f;   // columns 2c and 2c+1
 
-    auto fold_tile = [&](const FdTile<D>& tl, int t) {
-        const int kb = start + t * kFdTileKeys;
-        // ---- S = Q K^T: two blocks of 8 keys, kKWords k-steps each ----
-        // (even and odd k-steps accumulate separately: four dependent chains instead of two)
-        float s0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        float s2[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s3[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    auto fold_tile = [&](const FdTile<D> (&tl)[kFdSubs], int t) {
+        // ---- S^T = K q^T per sub-tile: rows = keys (r -> key_a, r+8 -> key_a+2), columns = heads ----
+        float score[kFdSubs][4], shifted[kFdSubs][4];   // [key a, col 0], [key a, col 1], [key b, col 0], [key b, col 1]
+        float t0 = -INFINITY, t1 = -INFINITY;
 #pragma unroll
-        for (int s = 0; s < kKWords; s += 2) {
-            mma_rows8(s0, qa0[s], qa2[s], e4m3x2_to_f16x2(tl.kw[0][s] & 0xffffu), e4m3x2_to_f16x2(tl.kw[0][s] >> 16));
-            mma_rows8(s1, qa0[s], qa2[s], e4m3x2_to_f16x2(tl.kw[1][s] & 0xffffu), e4m3x2_to_f16x2(tl.kw[1][s] >> 16));
-            mma_rows8(s2, qa0[s + 1], qa2[s + 1], e4m3x2_to_f16x2(tl.kw[0][s + 1] & 0xffffu), e4m3x2_to_f16x2(tl.kw[0][s + 1] >> 16));
-            mma_rows8(s3, qa0[s + 1], qa2[s + 1], e4m3x2_to_f16x2(tl.kw[1][s + 1] & 0xffffu), e4m3x2_to_f16x2(tl.kw[1][s + 1] >> 16));
+        for (int u = 0; u < kFdSubs; ++u) {
+            const int kb = start + t * kFdTileKeys + u * kFdSubKeys;
+            float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // two chains
+#pragma unroll
+            for (int s = 0; s < kKWords; s += 2) {
+                uint32_t a0, a1, a2, a3;
+                e4m3x4_to_f16x2x2(tl[u].kw[0][s], a0, a2);
+                e4m3x4_to_f16x2x2(tl[u].kw[1][s], a1, a3);
+                mma_16x8x16(sa, a0, a1, a2, a3, qb0[s], qb1[s]);
+                e4m3x4_to_f16x2x2(tl[u].kw[0][s + 1], a0, a2);
+                e4m3x4_to_f16x2x2(tl[u].kw[1][s + 1], a1, a3);
+                mma_16x8x16(sb, a0, a1, a2, a3, qb0[s + 1], qb1[s + 1]);
+            }
+            // scores in the log2 domain
+            const float lg = fmaxf(lg2_approx(tl[u].sc), kFdLgFloor);   // meaningful in lanes 16..31 (v scales)
+            const float ks_a = __shfl_sync(0xffffffffu, tl[u].sc, key_a), ks_b = __shfl_sync(0xffffffffu, tl[u].sc, key_a + 2);
+            const float lg_a = __shfl_sync(0xffffffffu, lg, 16 + key_a), lg_b = __shfl_sync(0xffffffffu, lg, 18 + key_a);
+            const bool live_a = kb + key_a < end, live_b = kb + key_a + 2 < end;
+            score[u][0] = live_a ? (sa[0] + sb[0]) * (ks_a * factor0) : -INFINITY;
+            score[u][1] = live_a ? (sa[1] + sb[1]) * (ks_a * factor1) : -INFINITY;
+            score[u][2] = live_b ? (sa[2] + sb[2]) * (ks_b * factor0) : -INFINITY;
+            score[u][3] = live_b ? (sa[3] + sb[3]) * (ks_b * factor1) : -INFINITY;
+            shifted[u][0] = score[u][0] + lg_a;
+            shifted[u][1] = score[u][1] + lg_a;
+            shifted[u][2] = score[u][2] + lg_b;
+            shifted[u][3] = score[u][3] + lg_b;
+            t0 = fmaxf(t0, fmaxf(shifted[u][0], shifted[u][2]));
+            t1 = fmaxf(t1, fmaxf(shifted[u][1], shifted[u][3]));
         }
-
-        // ---- scores of keys kb+4c+{0,1,2,3} for head r, in the log2 domain ----
-        const float lg = fmaxf(lg2_approx(tl.sc), kFdLgFloor);   // meaningful in lanes 16..31 (v scales)
-        float score[4], shifted[4];
-        const float raw[4] = {s0[0] + s2[0], s0[1] + s2[1], s1[0] + s3[0], s1[1] + s3[1]};
-        float tile_max = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float ks = __shfl_sync(0xffffffffu, tl.sc, 4 * c + i);
-            const float lgv = __shfl_sync(0xffffffffu, lg, 16 + 4 * c + i);
-            const bool live = kb + 4 * c + i < end;
-            score[i] = live ? raw[i] * (ks * row_factor) : -INFINITY;
-            shifted[i] = score[i] + lgv;
-            tile_max = fmaxf(tile_max, shifted[i]);
+        for (int off = 4; off < 32; off <<= 1) {   // over the 8 key rows
+            t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, off));
+            t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, off));
         }
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
-        tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
-        const float m_new = fmaxf(m_run, tile_max);
-        const float corr = ex2_approx(m_run - m_new);
-        m_run = m_new;
-        float w[4], psum = 0.0f;
+        const float n0 = fmaxf(m0, t0), n1 = fmaxf(m1, t1);
+        const float corr0 = ex2_approx(m0 - n0), corr1 = ex2_approx(m1 - n1);
+        m0 = n0;
+        m1 = n1;
+        if (__any_sync(0xffffffffu, corr0 != 1.0f || corr1 != 1.0f)) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            w[i] = ex2_approx(shifted[i] - m_new + kFdWeightShift);
-            psum += ex2_approx(score[i] - m_new);
-        }
-        l_run = l_run * corr + psum;
-        if (__any_sync(0xffffffffu, corr != 1.0f)) {
-#pragma unroll
-            for (int nb = 0; nb < kNB; ++nb) {
-                o[nb][0] *= corr;
-                o[nb][1] *= corr;
-                o[nb][2] *= corr;
-                o[nb][3] *= corr;
+            for (int mb = 0; mb < kMB; ++mb) {
+                o[mb][0] *= corr0;
+                o[mb][1] *= corr1;
+                o[mb][2] *= corr0;
+                o[mb][3] *= corr1;
             }
         }
-
-        // ---- O += W V: weights of the 16 keys as the A fragment, V bytes transposed to key pairs ----
-        // Rows 8..15 of the tile, idle otherwise, carry the weights' low halves: the f16 rounding of a
-        // weight (2^-12) would show in the bf16 result where the sum over keys cancels.
-        uint32_t wa0, wa1, wa2, wa3;
-        split_f16x2(w[0], w[1], wa0, wa1);
-        split_f16x2(w[2], w[3], wa2, wa3);
+        const float ns0 = n0 - kFdWeightShift, ns1 = n1 - kFdWeightShift;
+        float p0 = 0.0f, p1 = 0.0f;
 #pragma unroll
-        for (int wc = 0; wc < kVWords; ++wc) {
-            const uint32_t t01 = __byte_perm(tl.vw[0][wc], tl.vw[1][wc], 0x5140);   // k0.b0 k1.b0 k0.b1 k1.b1
-            const uint32_t t23 = __byte_perm(tl.vw[2][wc], tl.vw[3][wc], 0x5140);
-            const uint32_t u01 = __byte_perm(tl.vw[0][wc], tl.vw[1][wc], 0x7362);   // k0.b2 k1.b2 k0.b3 k1.b3
-            const uint32_t u23 = __byte_perm(tl.vw[2][wc], tl.vw[3][wc], 0x7362);
-            mma_rows16(o[4 * wc + 0], wa0, wa1, wa2, wa3, e4m3x2_to_f16x2(t01 & 0xffffu), e4m3x2_to_f16x2(t23 & 0xffffu));
-            mma_rows16(o[4 * wc + 1], wa0, wa1, wa2, wa3, e4m3x2_to_f16x2(t01 >> 16), e4m3x2_to_f16x2(t23 >> 16));
-            mma_rows16(o[4 * wc + 2], wa0, wa1, wa2, wa3, e4m3x2_to_f16x2(u01 & 0xffffu), e4m3x2_to_f16x2(u23 & 0xffffu));
-            mma_rows16(o[4 * wc + 3], wa0, wa1, wa2, wa3, e4m3x2_to_f16x2(u01 >> 16), e4m3x2_to_f16x2(u23 >> 16));
+        for (int u = 0; u < kFdSubs; ++u) {
+            const float w0 = ex2_approx(shifted[u][0] - ns0), w1 = ex2_approx(shifted[u][1] - ns1);
+            const float w2 = ex2_approx(shifted[u][2] - ns0), w3 = ex2_approx(shifted[u][3] - ns1);
+            p0 += ex2_approx(score[u][0] - n0) + ex2_approx(score[u][2] - n0);
+            p1 += ex2_approx(score[u][1] - n1) + ex2_approx(score[u][3] - n1);
+
+            // ---- weights as the B operand: [key][col] -> [col][key pairs] by an 8x8 transpose per 8 keys.
+            //      The f16 rounding of a weight (2^-12) would show in the bf16 result where the sum over
+            //      keys cancels, so the low halves go in as well. ----
+            uint32_t hi_a, lo_a, hi_b, lo_b;
+            split_f16x2(w0, w1, hi_a, lo_a);   // key a, columns 2c, 2c+1
+            split_f16x2(w2, w3, hi_b, lo_b);   // key b
+            uint32_t b0, b1;
+            [[maybe_unused]] uint32_t b0_lo = 0u, b1_lo = 0u;
+            if constexpr (kWide) {
+                b0 = transpose_8x8_b16(hi_a);
+                b1 = transpose_8x8_b16(hi_b);
+                b0_lo = transpose_8x8_b16(lo_a);
+                b1_lo = transpose_8x8_b16(lo_b);
+            } else {   // columns 4..7 (lanes c >= 2) repeat heads 0..3: they carry the low halves
+                b0 = transpose_8x8_b16(c >= 2 ? lo_a : hi_a);
+                b1 = transpose_8x8_b16(c >= 2 ? lo_b : hi_b);
+            }
+
+            // ---- O^T += V^T W^T: V bytes of keys 4c..4c+3 transposed into key pairs ----
+#pragma unroll
+            for (int wc = 0; wc < kVWords; ++wc) {
+                const uint32_t t01 = __byte_perm(tl[u].vw[0][wc], tl[u].vw[1][wc], 0x5140);   // k0.b0 k1.b0 k0.b1 k1.b1
+                const uint32_t t23 = __byte_perm(tl[u].vw[2][wc], tl[u].vw[3][wc], 0x5140);
+                const uint32_t u01 = __byte_perm(tl[u].vw[0][wc], tl[u].vw[1][wc], 0x7362);   // k0.b2 k1.b2 k0.b3 k1.b3
+                const uint32_t u23 = __byte_perm(tl[u].vw[2][wc], tl[u].vw[3][wc], 0x7362);
+                uint32_t a0, a1, a2, a3;
+                e4m3x4_to_f16x2x2(t01, a0, a1);   // dim 4wc (rows r) and dim 4wc+1 (rows r+8), keys 4c, 4c+1
+                e4m3x4_to_f16x2x2(t23, a2, a3);   // the same dims, keys 4c+2, 4c+3
+                mma_16x8x16(o[2 * wc], a0, a1, a2, a3, b0, b1);
+                if constexpr (kWide) mma_16x8x16(o[2 * wc], a0, a1, a2, a3, b0_lo, b1_lo);
+                e4m3x4_to_f16x2x2(u01, a0, a1);   // dims 4wc+2, 4wc+3
+                e4m3x4_to_f16x2x2(u23, a2, a3);
+                mma_16x8x16(o[2 * wc + 1], a0, a1, a2, a3, b0, b1);
+                if constexpr (kWide) mma_16x8x16(o[2 * wc + 1], a0, a1, a2, a3, b0_lo, b1_lo);
+            }
         }
+        l0 = l0 * corr0 + p0;
+        l1 = l1 * corr1 + p1;
     };
 
     for (int i = 0; i < my_tiles; ++i) {
         issue_tile(i + Ring::kStages - 1);          // into the stage read one trip ago
         cp_async_wait<Ring::kStages - 1>();         // tile i has landed (this lane's own copies)
-        FdTile<D> tl;
-        read_tile(tl, i);
+        FdTile<D> tl[kFdSubs];
+#pragma unroll
+        for (int u = 0; u < kFdSubs; ++u) read_tile(tl[u], i, u);
         fold_tile(tl, warp + i * kFdWarps);
     }
     cp_async_wait<0>();
     __syncthreads();   // every warp is done with its ring: the merge may overwrite it
 
-    // ---- merge the four warps ----
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    if (c == 0) {
-        s_m[warp * kFdRows + r] = m_run;
-        s_l[warp * kFdRows + r] = l_run;
+    // ---- merge the warps: accumulators as the lanes hold them, m and l per column ----
+    float4* const s_o = reinterpret_cast<float4*>(fd_smem);                          // [warp][mb][lane]
+    float* const s_m = reinterpret_cast<float*>(s_o + kFdWarps * kMB * 32);          // [warp][col]
+    float* const s_l = s_m + kFdWarps * kFdCols;                                     // [warp][col]
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    if (r == 0) {
+        s_m[warp * kFdCols + 2 * c] = m0;
+        s_m[warp * kFdCols + 2 * c + 1] = m1;
+        s_l[warp * kFdCols + 2 * c] = l0;
+        s_l[warp * kFdCols + 2 * c + 1] = l1;
     }
 #pragma unroll
-    for (int nb = 0; nb < kNB; ++nb)
-        *reinterpret_cast<float2*>(&s_o[(warp * kNB + nb) * kOPitch + r * 8 + 2 * c]) =
-            make_float2(o[nb][0] + o[nb][2], o[nb][1] + o[nb][3]);
+    for (int mb = 0; mb < kMB; ++mb) s_o[(warp * kMB + mb) * 32 + lane] = make_float4(o[mb][0], o[mb][1], o[mb][2], o[mb][3]);
     __syncthreads();
 
     const long long hs = static_cast<long long>(p.num_q_heads) * p.num_splits;
-    const int rows_here = min(kFdRows, p.group - chunk * kFdRows);
+    const int heads_here = min(kHeads, p.group - chunk * kHeads);
     const float unshift = ex2_approx(-kFdWeightShift);
-    for (int idx = threadIdx.x; idx < rows_here * D; idx += kFdThreads) {
-        const int row = idx / D, d = idx - row * D;
-        float big = s_m[row];
+    const float* const s_of = reinterpret_cast<const float*>(s_o);
+    for (int idx = threadIdx.x; idx < heads_here * D; idx += kFdThreads) {
+        const int h = idx / D, d = idx - h * D;
+        // dim d sits in lane row d/(D/8), block (d % (D/8)) / 2, odd dims in elements 2, 3; column h in
+        // lane c = h/2, element h%2
+        const int lane_r = d / (D / 8), within = d % (D / 8);
+        const int at = ((within >> 1) * 32 + lane_r * 4 + (h >> 1)) * 4 + (h & 1) + 2 * (within & 1);
+        float big = s_m[h];
 #pragma unroll
-        for (int wv = 1; wv < kFdWarps; ++wv) big = fmaxf(big, s_m[wv * kFdRows + row]);
-        const int at = (d % kNB) * kOPitch + row * 8 + d / kNB;   // column `col` of output block nb is dim col*D/8 + nb
+        for (int wv = 1; wv < kFdWarps; ++wv) big = fmaxf(big, s_m[wv * kFdCols + h]);
         float a = 0.0f;
 #pragma unroll
-        for (int wv = 0; wv < kFdWarps; ++wv)
-            a += s_o[wv * kNB * kOPitch + at] * ex2_approx(s_m[wv * kFdRows + row] - big);
-        const long long slot = static_cast<long long>(kvh * p.group + chunk * kFdRows + row) * p.num_splits + split;
+        for (int wv = 0; wv < kFdWarps; ++wv) {
+            float part = s_of[wv * kMB * 128 + at];
+            if constexpr (!kWide) part += s_of[wv * kMB * 128 + at + 8];   // column h+4: lane c+2, the low halves
+            a += part * ex2_approx(s_m[wv * kFdCols + h] - big);
+        }
+        const long long slot = static_cast<long long>(kvh * p.group + chunk * kHeads + h) * p.num_splits + split;
         p.partial[2 * hs + slot * D + d] = a * unshift;
         if (d == 0) {
             float l = 0.0f;
 #pragma unroll
-            for (int wv = 0; wv < kFdWarps; ++wv) l += s_l[wv * kFdRows + row] * ex2_approx(s_m[wv * kFdRows + row] - big);
+            for (int wv = 0; wv < kFdWarps; ++wv) l += s_l[wv * kFdCols + h] * ex2_approx(s_m[wv * kFdCols + h] - big);
             p.partial[slot] = big;
             p.partial[hs + slot] = l;
         }
@@ -496,8 +583,8 @@ __global__ void __launch_bounds__(kFdReduceThreads) flash_decode_reduce_kernel(_
     }
 }
 
-template <int D>
-void launch_partial(const FdArgs& a, cudaStream_t stream) {
+template <int D, bool kWide>
+void launch_partial_as(const FdArgs& a, cudaStream_t stream) {
     const dim3 grid(static_cast<unsigned>(a.num_kv_heads * a.row_chunks), static_cast<unsigned>(a.num_splits));
     constexpr int smem = FdRing<D>::kSmemBytes;
     if constexpr (smem > 48 * 1024) {   // opt in once per device; the attribute is per device and idempotent
@@ -506,12 +593,18 @@ void launch_partial(const FdArgs& a, cudaStream_t stream) {
         cudaGetDevice(&dev);
         const unsigned bit = 1u << (dev & 31);
         if ((configured.load(std::memory_order_relaxed) & bit) == 0) {
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(&flash_decode_partial_kernel<D>),
+            cudaFuncSetAttribute(reinterpret_cast<const void*>(&flash_decode_partial_kernel<D, kWide>),
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             configured.fetch_or(bit, std::memory_order_relaxed);
         }
     }
-    host::launch(flash_decode_partial_kernel<D>, grid, dim3(kFdThreads), static_cast<size_t>(smem), stream, a);
+    host::launch(flash_decode_partial_kernel<D, kWide>, grid, dim3(kFdThreads), static_cast<size_t>(smem), stream, a);
+}
+
+template <int D>
+void launch_partial(const FdArgs& a, cudaStream_t stream) {
+    if (a.heads_per_cta > 4) launch_partial_as<D, true>(a, stream);
+    else launch_partial_as<D, false>(a, stream);
 }
 
 }  // namespace
@@ -555,7 +648,8 @@ extern "C" int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_
     a.num_q_heads = num_q_heads;
     a.num_kv_heads = num_kv_heads;
     a.group = num_q_heads / num_kv_heads;
-    a.row_chunks = (a.group + kFdRows - 1) / kFdRows;
+    a.heads_per_cta = a.group > 4 ? 8 : 4;
+    a.row_chunks = (a.group + a.heads_per_cta - 1) / a.heads_per_cta;
     a.scale_log2e = scale * kFdLog2e;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (head_dim) {
