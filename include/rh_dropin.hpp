@@ -69,4 +69,9 @@ void flash_decode_split_bf16(__nv_bfloat16* out, const __nv_bfloat16* q, const _
                              int num_splits, const int* cache_len, int num_q_heads, int num_kv_heads,
                              int head_dim, float scale, cudaStream_t stream = nullptr);
 
+// include/runtherder/kernels/flash_prefill.cuh:27-40
+void flash_prefill_bf16(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_fp8_e4m3* k, const __nv_fp8_e4m3* v,
+                        const float* k_scale, const float* v_scale, int n_new, const int* cache_len, int num_q_heads,
+                        int num_kv_heads, int head_dim, float scale, cudaStream_t stream = nullptr);
+
 }  // namespace runtherder::kernels

@@ -119,6 +119,18 @@ int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_t* k, const
                                const int* cache_len, int num_q_heads, int num_kv_heads, int head_dim,
                                float scale, void* stream);
 
+/* Causal attention of n_new query tokens over the FP8 cache (prefill, chunked prefill): token t
+ * attends keys 0 .. *cache_len + t.  out, q: [n_new, Hq, head_dim] bf16; k, v: [*cache_len + n_new,
+ * Hkv, head_dim] E4M3 with per-(token, kv head) scales; *cache_len is read on the device.
+ * head_dim must be 128 (as in the reference).  Operands narrow to f16 before the tensor-core
+ * products as in the reference (q magnitudes must lie in f16's range); accumulation and softmax
+ * are fp32.  Results are within one bf16 ulp of the exact value (tests/test_gpu_flash_prefill.py).
+ * Replaces flash_prefill_bf16 (include/runtherder/kernels/flash_prefill.cuh:27-40,
+ * src/kernels/flash_prefill.cu:213-241; called from src/attention/adaptive.cu:37-40). */
+int rh_flash_prefill_bf16(void* out, const void* q, const uint8_t* k, const uint8_t* v, const float* k_scale,
+                          const float* v_scale, int n_new, const int* cache_len, int num_q_heads,
+                          int num_kv_heads, int head_dim, float scale, void* stream);
+
 /* ---- Fused entry points (new; each equals a chain of the reference's calls) --------------- */
 
 /* [residual add +] RMSNorm + per-token INT8 quantisation in one pass over the row.

@@ -1,5 +1,5 @@
 // C-linkage entry points onto the reference's own CUDA kernels
-// (src/kernels/{rmsnorm,quantization,rope,activation,embedding,attention,flash_decode}.cu), which the
+// (src/kernels/{rmsnorm,quantization,rope,activation,embedding,attention,flash_decode,flash_prefill}.cu), which the
 // Makefile compiles for sm_100a from where they lie and links with this file
 // into _ref/libref_cuda.so.  It is the GPU-side oracle (identical intrinsics
 // and operation order) and the CUDA baseline the benchmark times beside the
@@ -9,6 +9,7 @@
 #include <runtherder/kernels/activation.cuh>
 #include <runtherder/kernels/attention.cuh>
 #include <runtherder/kernels/flash_decode.cuh>
+#include <runtherder/kernels/flash_prefill.cuh>
 #include <runtherder/kernels/embedding.cuh>
 #include <runtherder/kernels/quantization.cuh>
 #include <runtherder/kernels/rmsnorm.cuh>
@@ -86,6 +87,14 @@ void refcuda_flash_decode_split(void* out, const void* q, const void* k, const v
                                 static_cast<const __nv_fp8_e4m3*>(k), static_cast<const __nv_fp8_e4m3*>(v), k_scale,
                                 v_scale, partial, num_splits, cache_len, num_q_heads, num_kv_heads, head_dim, scale,
                                 static_cast<cudaStream_t>(stream));
+}
+
+void refcuda_flash_prefill(void* out, const void* q, const void* k, const void* v, const float* k_scale,
+                           const float* v_scale, int n_new, const int* cache_len, int num_q_heads, int num_kv_heads,
+                           int head_dim, float scale, void* stream) {
+    rk::flash_prefill_bf16(static_cast<bf16*>(out), static_cast<const bf16*>(q), static_cast<const __nv_fp8_e4m3*>(k),
+                           static_cast<const __nv_fp8_e4m3*>(v), k_scale, v_scale, n_new, cache_len, num_q_heads,
+                           num_kv_heads, head_dim, scale, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -373,6 +373,18 @@ ORC_API void orc_attention_decode_fp8(uint16_t* out, float* out_f32, const uint1
     }
 }
 
+/* The same for n_new query tokens (prefill / chunked prefill): token t attends */
+/* keys 0..cache_len + t (src/kernels/attention.cu:45-49).  q, out: [n_new, Hq, D]. */
+ORC_API void orc_attention_causal_fp8(uint16_t* out, float* out_f32, const uint16_t* q, const uint8_t* k,
+                                      const uint8_t* v, const float* k_scale, const float* v_scale, int n_new,
+                                      int cache_len, int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                      double* score_buf /* cache_len + n_new doubles */) {
+    const size_t row = (size_t)num_q_heads * head_dim;
+    for (int t = 0; t < n_new; ++t)
+        orc_attention_decode_fp8(out + t * row, out_f32 ? out_f32 + t * row : NULL, q + t * row, k, v, k_scale,
+                                 v_scale, cache_len + t, num_q_heads, num_kv_heads, head_dim, scale, score_buf);
+}
+
 /* ------------------------------------------------------------------------ */
 /* Chains, as the reference's layer composition issues them.  Each stage     */
 /* rounds to bf16 exactly where the reference stores a bf16 tensor.          */

@@ -34,6 +34,7 @@ SIGNATURES = {
     "rh_qkv_bias_add_bf16": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _p],
     "rh_flash_split_scratch_floats": [_i, _i, _i],
     "rh_flash_decode_split_bf16": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
+    "rh_flash_prefill_bf16": [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
     "rh_rmsnorm_add_quant_int8": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p],
     "rh_swiglu_quant_int8": [_p, _p, _p, _p, _p, _i, _i, _p],
     "rh_rope_kv_fp8": [_p, _p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],

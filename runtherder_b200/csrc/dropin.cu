@@ -84,4 +84,13 @@ void flash_decode_split_bf16(__nv_bfloat16* out, const __nv_bfloat16* q, const _
                  "flash_decode_split_bf16");
 }
 
+void flash_prefill_bf16(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_fp8_e4m3* k, const __nv_fp8_e4m3* v,
+                        const float* k_scale, const float* v_scale, int n_new, const int* cache_len, int num_q_heads,
+                        int num_kv_heads, int head_dim, float scale, cudaStream_t stream) {
+    die_on_error(rh_flash_prefill_bf16(out, q, reinterpret_cast<const std::uint8_t*>(k),
+                                       reinterpret_cast<const std::uint8_t*>(v), k_scale, v_scale, n_new, cache_len,
+                                       num_q_heads, num_kv_heads, head_dim, scale, stream),
+                 "flash_prefill_bf16");
+}
+
 }  // namespace runtherder::kernels

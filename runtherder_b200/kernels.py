@@ -20,7 +20,7 @@ __all__ = [
     "RhError", "rmsnorm_bf16_forward", "rmsnorm_add_bf16_forward", "quantize_per_token_int8",
     "dequantize_w8a8", "quantize_kv_fp8", "dequantize_kv_fp8", "swiglu_bf16_forward", "rope_bf16",
     "embedding_lookup_bf16_forward", "qkv_bias_add_bf16_forward", "stage_positions", "decode_advance",
-    "flash_split_scratch_floats", "flash_decode_split_bf16", "tune", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
+    "flash_split_scratch_floats", "flash_decode_split_bf16", "flash_prefill_bf16", "tune", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
 ]
 
 
@@ -165,6 +165,16 @@ def flash_decode_split_bf16(out, q, k, v, k_scale, v_scale, partial, num_splits:
          _ptr(k_scale, _F32, None, "k_scale"), _ptr(v_scale, _F32, None, "v_scale"),
          _ptr(partial, _F32, need, "partial"), num_splits, _ptr(cache_len, _I32, 1, "cache_len"), num_q_heads,
          num_kv_heads, head_dim, float(scale), _stream(stream))
+
+
+def flash_prefill_bf16(out, q, k, v, k_scale, v_scale, n_new: int, cache_len, num_q_heads: int, num_kv_heads: int,
+                       head_dim: int, scale: float, stream=None) -> None:
+    """n_new query tokens attend causally over the FP8 cache (token t sees keys 0..*cache_len + t); cache_len is
+    a device-resident int32.  head_dim 128.  (flash_prefill.cuh:27-40)"""
+    call("rh_flash_prefill_bf16", _ptr(out, _BF, n_new * num_q_heads * head_dim, "out"),
+         _ptr(q, _BF, n_new * num_q_heads * head_dim, "q"), _fp8_ptr(k, None, "k"), _fp8_ptr(v, None, "v"),
+         _ptr(k_scale, _F32, None, "k_scale"), _ptr(v_scale, _F32, None, "v_scale"), n_new,
+         _ptr(cache_len, _I32, 1, "cache_len"), num_q_heads, num_kv_heads, head_dim, float(scale), _stream(stream))
 
 
 # ---- fused entry points ---------------------------------------------------------------------

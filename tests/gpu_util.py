@@ -84,6 +84,10 @@ class RefCuda:
         self.lib.refcuda_attention_causal(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), k_scale.data_ptr(),
                                           v_scale.data_ptr(), n_new, cache_len.data_ptr(), Hq, Hkv, D, scale, _s(stream))
 
+    def flash_prefill_bf16(self, out, q, k, v, k_scale, v_scale, n_new, cache_len, Hq, Hkv, D, scale, stream=None):
+        self.lib.refcuda_flash_prefill(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), k_scale.data_ptr(),
+                                       v_scale.data_ptr(), n_new, cache_len.data_ptr(), Hq, Hkv, D, scale, _s(stream))
+
     def flash_decode_split_bf16(self, out, q, k, v, k_scale, v_scale, partial, num_splits, cache_len, Hq, Hkv, D, scale,
                                 stream=None):
         self.lib.refcuda_flash_decode_split(out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),

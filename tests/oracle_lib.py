@@ -47,6 +47,7 @@ def load_oracle() -> C.CDLL:
         "orc_swiglu_quant_int8": ([_p, _p, _p, _p, _p, _l, _i], None),
         "orc_rope_kv_fp8": ([_p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i, _l, _i, _i, _i], None),
         "orc_attention_decode_fp8": ([_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _p], None),
+        "orc_attention_causal_fp8": ([_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p], None),
         "orc_synth_normal_bf16": ([_p, _sz, _u64, _u64, _u64, _f, _p, _i], None),
         "orc_synth_uniform_bf16": ([_p, _sz, _u64, _u64, _u64, _f, _f], None),
         "orc_synth_ids_i32": ([_p, _sz, _u64, _u64, _u64, _i32], None),
@@ -110,6 +111,7 @@ def load_ref_cuda():
         "refcuda_embedding_lookup": [_p, _p, _p, _i, _i, _p],
         "refcuda_attention_causal": [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
         "refcuda_flash_decode_split": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
+        "refcuda_flash_prefill": [_p, _p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _f, _p],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)
@@ -169,6 +171,17 @@ class Oracle:
         buf = np.empty(cache_len + 1, np.float64)
         self.lib.orc_attention_decode_fp8(ptr(out), ptr(out_f), ptr(q), ptr(k), ptr(v), ptr(k_scale), ptr(v_scale),
                                           cache_len, Hq, Hkv, D, scale, ptr(buf))
+        return out, out_f
+
+    def attention_causal_fp8(self, q, k, v, k_scale, v_scale, cache_len, scale):
+        """q [n_new, Hq, D] bf16 bits; k, v [cache_len + n_new, Hkv, D] codes -> (bf16 bits, float32) [n_new, Hq, D]."""
+        n_new, Hq, D = q.shape
+        Hkv = k.shape[1]
+        out = np.empty((n_new, Hq, D), np.uint16)
+        out_f = np.empty((n_new, Hq, D), np.float32)
+        buf = np.empty(cache_len + n_new, np.float64)
+        self.lib.orc_attention_causal_fp8(ptr(out), ptr(out_f), ptr(q), ptr(k), ptr(v), ptr(k_scale), ptr(v_scale),
+                                          n_new, cache_len, Hq, Hkv, D, scale, ptr(buf))
         return out, out_f
 
     def add_rows(self, x, bias):
