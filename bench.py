@@ -53,8 +53,9 @@ def parse_args():
     p.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                    help="layer-chain configs: replay the forward from a CUDA graph (auto: on for the decode config)")
     p.add_argument("--attention", action="store_true",
-                   help="with --config c2: time the split-KV flash decode over the FP8 cache at that depth instead "
-                        "of the row-wise chain (secondary line; not the headline metric)")
+                   help="time the attention over the FP8 cache instead of the row-wise chain (secondary line; not the "
+                        "headline metric): the split-KV flash decode for --config c2 (or any config with --depth), "
+                        "the causal prefill for configs with more than one token (c1, c3)")
     p.add_argument("--depth", type=int, default=0, help="--attention: override the context depth (keys attended)")
     p.add_argument("--splits", type=int, default=32, help="--attention: split count (the reference uses 32)")
     p.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
@@ -313,7 +314,10 @@ def main():
     if args.attention:
         if world != 1:
             raise SystemExit("--attention is a single-GPU measurement (one query token does not shard)")
-        run_decode_attention(args, cfg, dev)
+        if cfg.tokens > 1 and not args.depth:
+            run_prefill_attention(args, cfg, dev)
+        else:
+            run_decode_attention(args, cfg, dev)
         return
     if args.config != "c4":
         run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks)
@@ -619,6 +623,106 @@ def run_decode_attention(args, cfg, dev):
             dt = time.perf_counter() - t0
             line["cpu_baseline"] = {"value": round(bytes_per_call / dt / 1e9, 4), "unit": "GB/s", "cores": 1, "kind": "port",
                                     "sample": f"one call ({depth} keys, {Hq} heads) of the double-precision oracle, {dt:.2f} s"}
+        except Exception as exc:
+            line["cpu_baseline"] = {"unavailable": str(exc)[:200]}
+    print(json.dumps(line), flush=True)
+
+
+def measured_tensor_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def run_prefill_attention(args, cfg, dev):
+    """Secondary measurement: the causal prefill attention of one layer — rh_flash_prefill_bf16 on `tokens` new
+    tokens over an (initially empty) FP8 cache, a few distinct q/cache sets used in turn.  FLOPs per call:
+    4 * head_dim * q_heads * T (T + 1) / 2 (both products, causal half)."""
+    import math
+    import torch
+    from runtherder_b200 import kernels as Kn
+    T, Hq, Hkv, D = cfg.tokens, cfg.q_heads, cfg.kv_heads, cfg.head_dim
+    n_sets = 3
+    gen = torch.Generator(device=dev).manual_seed(cfg.seed + 78)
+    at0 = torch.zeros(1, dtype=torch.int32, device=dev)
+    sets = []
+    for _ in range(n_sets):
+        q = torch.randn(T, Hq, D, device=dev, generator=gen).to(torch.bfloat16)
+        kc = torch.empty(T, Hkv, D, dtype=torch.uint8, device=dev); vc = torch.empty_like(kc)
+        ks = torch.empty(T, Hkv, dtype=torch.float32, device=dev); vs = torch.empty_like(ks)
+        for codes, scales in ((kc, ks), (vc, vs)):
+            x = torch.randn(T, Hkv, D, device=dev, generator=gen).to(torch.bfloat16)
+            Kn.quantize_kv_fp8(codes, scales, x, at0, 1, T * Hkv, D)
+        sets.append((q, kc, ks, vc, vs, torch.empty(T, Hq, D, dtype=torch.bfloat16, device=dev)))
+    cache_len = torch.zeros(1, dtype=torch.int32, device=dev)
+    scale = 1.0 / math.sqrt(D)
+    flops = 4.0 * D * Hq * T * (T + 1) / 2
+
+    def timed(fn, reps):
+        for i in range(max(args.warmup, 3)):
+            fn(*sets[i % n_sets])
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        with ClockSampler(dev.index or 0) as clocks:
+            a.record()
+            for i in range(reps):
+                fn(*sets[i % n_sets])
+            b.record()
+            torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps, clocks.summary()
+
+    def ours(q, kc, ks, vc, vs, out):
+        Kn.flash_prefill_bf16(out, q, kc, vc, ks, vs, T, cache_len, Hq, Hkv, D, scale)
+
+    K = args.steps
+    ms, clocks = timed(ours, K)
+    peak, peak_kind = measured_tensor_peak()
+    achieved = flops / (ms * 1e-3) / 1e12
+    line = {"metric": "flash-prefill TFLOP/s", "value": round(achieved, 1), "unit": "TFLOP/s", "n_gpus": 1, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "replicas only",
+            "vs_baseline": None, "dtype": "f32",
+            "io_dtypes": "bf16 q, fp8-e4m3 cache codes + fp32 scales in; bf16 out (f16 tensor-core operands, fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": f"{cfg.name}: causal prefill attention, one layer", "tokens": T, "q_heads": Hq,
+                       "kv_heads": Hkv, "head_dim": D, "cache_len": 0, "sets": n_sets, "flops_per_call": flops,
+                       "l2": "q + out of one call are 2 x %.0f MB; %d sets used in turn" % (T * Hq * D * 2 / 1e6, n_sets)},
+            "gpu_launches": K, "launches_per_step": 1, "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "flash_prefill_kernel", "achieved": round(achieved, 1), "peak": peak,
+                         "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "note": "mma.sync kernel: its own ceiling is the legacy tensor path (one m16n8k16 per 8 cycles "
+                                 "per SM sub-partition = 576 TFLOP/s at 1.9 GHz), not the tcgen05 figure the peak was measured with"}}
+    if not args.no_refcuda:
+        try:
+            sys.path.insert(0, str(ROOT / "tests"))
+            from gpu_util import RefCuda
+            ref = RefCuda()
+
+            def theirs(q, kc, ks, vc, vs, out):
+                ref.flash_prefill_bf16(out, q, kc, vc, ks, vs, T, cache_len, Hq, Hkv, D, scale)
+            rms, _ = timed(theirs, max(2, min(K, 5)))
+            line["ref_cuda"] = {"ms_per_step": round(rms, 4), "value": round(flops / (rms * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
+                                "what": "reference src/kernels/flash_prefill.cu compiled for sm_100a, same buffers"}
+        except Exception as exc:
+            line["ref_cuda"] = {"unavailable": str(exc)[:200]}
+    if not args.no_cpu:
+        try:
+            sys.path.insert(0, str(ROOT / "tests"))
+            from gpu_util import to_np
+            from oracle_lib import Oracle
+            orc = Oracle()
+            q, kc, ks, vc, vs, _ = sets[0]
+            n_s = min(16, T)
+            q_s = to_np(q[T - n_s:].contiguous())
+            t0 = time.perf_counter()
+            orc.attention_causal_fp8(q_s, to_np(kc), to_np(vc), to_np(ks), to_np(vs), T - n_s, scale)
+            dt = time.perf_counter() - t0
+            fl = 4.0 * D * Hq * sum(T - n_s + t + 1 for t in range(n_s))
+            line["cpu_baseline"] = {"value": round(fl / dt / 1e12, 6), "unit": "TFLOP/s", "cores": 1, "kind": "port",
+                                    "sample": f"the last {n_s} of {T} tokens through the double-precision oracle, {dt:.2f} s"}
         except Exception as exc:
             line["cpu_baseline"] = {"unavailable": str(exc)[:200]}
     print(json.dumps(line), flush=True)

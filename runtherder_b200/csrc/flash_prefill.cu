@@ -13,8 +13,11 @@
 // score, the V scale rides in the exponent of the weight (w = 2^(s + lg2 vs - m), at most 1) and the
 // softmax denominator accumulates w / vs, so V enters the second product as exact E4M3 values.
 //
+// Shared memory feeds the tensor cores here: with 16 query rows per warp every K/V fragment read serves one
+// product and the kernel is bound by shared-memory bandwidth (76 % of peak, tensor pipe 45 %), so for
+// prompts that fill the GPU a warp owns 32 rows and every fragment serves two.
 // Not a tcgen05 kernel: that is the next step for this op (a 128-row UMMA tile per CTA reads the K/V
-// operands from shared memory once instead of once per 16-row warp, which is what bounds this form).
+// operands from shared memory once per CTA instead of once per warp).
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
@@ -34,16 +37,21 @@ constexpr float kPfLog2e = 1.4426950408889634f;
 constexpr float kPfMInit = -1.0e30f;
 constexpr float kPfLgFloor = -100.0f;
 
-// shared-memory map (bytes)
+// shared-memory map (bytes); kMT = 16-row tiles per warp (1 or 2), which also is the number of f16
+// K/V tile buffers (the 2-tile form runs one CTA per SM and can afford to convert a tile ahead)
 constexpr int kPfTileF16 = kPfKeys * kPfRowBytes;                  // 16 KB: a converted K or V tile
 constexpr int kPfRawTile = kPfKeys * kPfD;                         // 8 KB: a raw E4M3 K or V tile
 constexpr int kPfRawStage = 2 * kPfRawTile + 2 * kPfKeys * 4;      // K, V, k scales, v scales
-constexpr int kPfOffK = 0;
-constexpr int kPfOffV = kPfOffK + kPfTileF16;
-constexpr int kPfOffRaw = kPfOffV + kPfTileF16;
-constexpr int kPfOffCst = kPfOffRaw + 2 * kPfRawStage;             // ksl[64], lgv[64], rvs[64]
-constexpr int kPfOffQ = kPfOffCst + 3 * kPfKeys * 4;               // [warps][16 rows][128] f16
-constexpr int pf_smem_bytes(int warps) { return kPfOffQ + warps * 16 * kPfRowBytes; }
+constexpr int kPfCstBytes = 3 * kPfKeys * 4;                       // ksl[64], lgv[64], rvs[64]
+template <int kMT>
+struct PfSmem {
+    static constexpr int kBufs = kMT;
+    static constexpr int kOffKV = 0;                                        // [buf][K, V] f16 tiles
+    static constexpr int kOffRaw = kOffKV + kBufs * 2 * kPfTileF16;         // [2] raw stages
+    static constexpr int kOffCst = kOffRaw + 2 * kPfRawStage;               // [buf] per-key constants
+    static constexpr int kOffQ = kOffCst + kBufs * kPfCstBytes;             // [warps][16 * kMT rows][128] f16
+    static constexpr int bytes(int warps) { return kOffQ + warps * 16 * kMT * kPfRowBytes; }
+};
 
 struct PfArgs {
     __nv_bfloat16* out;
@@ -58,7 +66,7 @@ struct PfArgs {
     int num_kv_heads;
     int group;           // query heads per kv head
     int heads_per_cta;   // min(group, 8)
-    int subs;            // 16-token sub-tiles per CTA: max(1, 8 / heads_per_cta)
+    int subs;            // token sub-tiles (one warp each) per CTA: max(1, 8 / heads_per_cta)
     int head_chunks;     // ceil(group / heads_per_cta)
     float scale_log2e;
 };
@@ -109,9 +117,15 @@ __device__ __forceinline__ void pf_cp_async4_zfill(uint32_t smem_addr, const voi
 // byte offset of 16-byte chunk `chunk` (0..15) of row `row` in an f16 tile: chunks are XORed with the
 // row so that the eight rows an ldmatrix reads, and the rows a conversion step writes, spread over banks
 __device__ __forceinline__ int pf_swz(int row, int chunk) { return row * kPfRowBytes + ((chunk ^ (row & 7)) << 4); }
+// the same for the 8 chunks of a raw 128-byte row
+__device__ __forceinline__ int pf_swz_raw(int row, int chunk) { return row * kPfD + ((chunk ^ (row & 7)) << 4); }
 
-// grid (token tiles, num_kv_heads * head_chunks); block = 32 * heads_here * subs threads.
-__global__ void __launch_bounds__(kPfMaxWarps * 32, 2) flash_prefill_kernel(const PfArgs p) {
+// grid (token tiles, num_kv_heads * head_chunks); block = 32 * heads_here * subs threads; a warp owns
+// 16 * kMT consecutive tokens of one query head.
+template <int kMT>
+__global__ void __launch_bounds__(kPfMaxWarps * 32, (kMT == 1 ? 2 : 1)) flash_prefill_kernel(const PfArgs p) {
+    using L = PfSmem<kMT>;
+    constexpr int kRows = 16 * kMT;   // tokens per warp
     extern __shared__ __align__(128) unsigned char pf_smem[];
     const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(pf_smem));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -121,32 +135,32 @@ __global__ void __launch_bounds__(kPfMaxWarps * 32, 2) flash_prefill_kernel(cons
     const int kvh = blockIdx.y / p.head_chunks;
     const int chunk = blockIdx.y - kvh * p.head_chunks;
     const int heads_here = min(p.heads_per_cta, p.group - chunk * p.heads_per_cta);
-    const int sub = warp / heads_here;                      // 16-token sub-tile of this warp
+    const int sub = warp / heads_here;                      // token sub-tile of this warp
     const int head = warp - sub * heads_here;               // its query head within the chunk
     const bool warp_active = sub < p.subs;                  // blockDim is sized for the widest chunk
     const int qh = kvh * p.group + chunk * p.heads_per_cta + head;
     const int tile = gridDim.x - 1 - blockIdx.x;            // long (late) token tiles first
-    const int tok0_cta = tile * 16 * p.subs;
-    const int tok0 = tok0_cta + 16 * sub;                   // first token of this warp
+    const int tok0_cta = tile * kRows * p.subs;
+    const int tok0 = tok0_cta + kRows * sub;                // first token of this warp
 
     pdl_enter();
     const int clen = *p.cache_len;
     const int total_keys = clen + p.n_new;
-    const int last_tok_cta = min(tok0_cta + 16 * p.subs, p.n_new) - 1;
+    const int last_tok_cta = min(tok0_cta + kRows * p.subs, p.n_new) - 1;
     const int n_tiles = min((total_keys + kPfKeys - 1) / kPfKeys, (clen + last_tok_cta) / kPfKeys + 1);
-    const int last_tok_warp = min(tok0 + 16, p.n_new) - 1;
+    const int last_tok_warp = min(tok0 + kRows, p.n_new) - 1;
     const int warp_last_tile = (warp_active && last_tok_warp >= tok0) ? (clen + last_tok_warp) / kPfKeys : -1;
 
-    // ---- raw tile copies (all threads): 64 K rows + 64 V rows of 128 bytes, 2 x 64 scales ----
+    // ---- raw tile copies (all threads): 64 K rows + 64 V rows of 128 bytes (chunks swizzled), 2 x 64 scales ----
     const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kPfD;
-    auto issue_raw = [&](int j, int stage) {
-        const uint32_t st = smem_base + kPfOffRaw + stage * kPfRawStage;
+    auto issue_raw = [&](int j) {
+        const uint32_t st = smem_base + L::kOffRaw + (j & 1) * kPfRawStage;
         for (int id = tid; id < 2 * kPfKeys * 8; id += n_threads) {
             const int which = id >> 9, row = (id >> 3) & 63, ch = id & 7;
             const int key = j * kPfKeys + row;
             const bool live = key < total_keys;
             const uint8_t* src = (which ? p.v : p.k) + (live ? static_cast<size_t>(key) * row_stride + static_cast<size_t>(kvh) * kPfD + ch * 16 : 0);
-            pf_cp_async16_zfill(st + which * kPfRawTile + row * kPfD + ch * 16, src, live);
+            pf_cp_async16_zfill(st + which * kPfRawTile + pf_swz_raw(row, ch), src, live);
         }
         for (int id = tid; id < 2 * kPfKeys; id += n_threads) {
             const int which = id >> 6, row = id & 63;
@@ -157,13 +171,41 @@ __global__ void __launch_bounds__(kPfMaxWarps * 32, 2) flash_prefill_kernel(cons
         }
         cp_async_commit();
     };
-    issue_raw(0, 0);
+    // ---- convert raw tile j into f16 buffer j % kBufs: 16 codes per step, 8 cvt, two swizzled 16-byte
+    //      stores; a quarter-warp works on eight consecutive rows of one chunk column, so the swizzles make
+    //      both the read and the stores conflict-free ----
+    auto convert = [&](int j) {
+        const unsigned char* const raw = pf_smem + L::kOffRaw + (j & 1) * kPfRawStage;
+        unsigned char* const kv = pf_smem + L::kOffKV + (j % L::kBufs) * 2 * kPfTileF16;
+        for (int id = tid; id < 2 * kPfKeys * 8; id += n_threads) {
+            const int which = id >> 9, ch = (id >> 6) & 7, row = id & 63;
+            const uint4 w = *reinterpret_cast<const uint4*>(raw + which * kPfRawTile + pf_swz_raw(row, ch));
+            uint4 h0, h1;
+            pf_e4m3x4_to_f16x2x2(w.x, h0.x, h0.y);
+            pf_e4m3x4_to_f16x2x2(w.y, h0.z, h0.w);
+            pf_e4m3x4_to_f16x2x2(w.z, h1.x, h1.y);
+            pf_e4m3x4_to_f16x2x2(w.w, h1.z, h1.w);
+            unsigned char* const dst = kv + which * kPfTileF16;
+            *reinterpret_cast<uint4*>(dst + pf_swz(row, 2 * ch)) = h0;
+            *reinterpret_cast<uint4*>(dst + pf_swz(row, 2 * ch + 1)) = h1;
+        }
+        float* const cst = reinterpret_cast<float*>(pf_smem + L::kOffCst + (j % L::kBufs) * kPfCstBytes);
+        for (int id = tid; id < kPfKeys; id += n_threads) {
+            const float* const sc = reinterpret_cast<const float*>(raw + 2 * kPfRawTile);
+            const float lg = fmaxf(pf_lg2(sc[kPfKeys + id]), kPfLgFloor);
+            cst[id] = sc[id] * p.scale_log2e;
+            cst[kPfKeys + id] = lg;
+            cst[2 * kPfKeys + id] = pf_ex2(-lg);
+        }
+    };
+    issue_raw(0);
 
-    // ---- Q: this warp's 16 rows, bf16 -> f16, swizzled (operands narrow to f16 as in the reference) ----
-    const uint32_t q_s = smem_base + kPfOffQ + warp * 16 * kPfRowBytes;
+    // ---- Q: this warp's rows, bf16 -> f16, swizzled (operands narrow to f16 as in the reference) ----
+    const int q_off = L::kOffQ + warp * kRows * kPfRowBytes;
+    const uint32_t q_s = smem_base + q_off;
     if (warp_active) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 8 * kMT; ++i) {
             const int id = lane + 32 * i, row = id >> 4, ch = id & 15;
             const int tok = tok0 + row;
             uint4 w = make_uint4(0u, 0u, 0u, 0u);
@@ -174,159 +216,199 @@ __global__ void __launch_bounds__(kPfMaxWarps * 32, 2) flash_prefill_kernel(cons
             h.y = pf_pack_f16x2(bf_lo(w.y), bf_hi(w.y));
             h.z = pf_pack_f16x2(bf_lo(w.z), bf_hi(w.z));
             h.w = pf_pack_f16x2(bf_lo(w.w), bf_hi(w.w));
-            *reinterpret_cast<uint4*>(pf_smem + kPfOffQ + warp * 16 * kPfRowBytes + pf_swz(row, ch)) = h;
+            *reinterpret_cast<uint4*>(pf_smem + q_off + pf_swz(row, ch)) = h;
         }
     }
 
-    float o[16][4];
+    float o[kMT][16][4];
+    float m_run[kMT][2], l_run[kMT][2];   // rows r and r+8 of each 16-row tile
 #pragma unroll
-    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-    float m_lo = kPfMInit, m_hi = kPfMInit, l_lo = 0.0f, l_hi = 0.0f;   // rows r and r+8
-    const int qpos_lo = clen + tok0 + r, qpos_hi = qpos_lo + 8;
-
-    float* const cst = reinterpret_cast<float*>(pf_smem + kPfOffCst);
-    const float2* const ksl2 = reinterpret_cast<const float2*>(cst);
-    const float2* const lgv2 = reinterpret_cast<const float2*>(cst + kPfKeys);
-    const float2* const rvs2 = reinterpret_cast<const float2*>(cst + 2 * kPfKeys);
+    for (int t = 0; t < kMT; ++t) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n) o[t][n][0] = o[t][n][1] = o[t][n][2] = o[t][n][3] = 0.0f;
+        m_run[t][0] = m_run[t][1] = kPfMInit;
+        l_run[t][0] = l_run[t][1] = 0.0f;
+    }
 
     // per-lane ldmatrix row/chunk selectors
     const int a_row = (lane & 7) + 8 * ((lane >> 3) & 1), a_ch = lane >> 4;          // Q: A operand
     const int k_row = (lane & 7) + 8 * (lane >> 4), k_ch = (lane >> 3) & 1;          // K: B operand of Q K^T
     const int v_row = (lane & 7) + 8 * ((lane >> 3) & 1), v_ch = lane >> 4;          // V: B operand of P V (transposed)
 
-    for (int j = 0; j < n_tiles; ++j) {
+    if constexpr (kMT == 2) {   // two f16 buffers: tile 0 is converted ahead of the loop
         cp_async_wait<0>();
-        __syncthreads();   // raw tile j has landed for every thread; everybody is done with the f16 tiles of j-1
-        if (j + 1 < n_tiles) issue_raw(j + 1, (j + 1) & 1);
-
-        // ---- convert raw tile j: 16 codes per step, 8 cvt, two swizzled 16-byte stores ----
-        const unsigned char* const raw = pf_smem + kPfOffRaw + (j & 1) * kPfRawStage;
-        for (int id = tid; id < 2 * kPfKeys * 8; id += n_threads) {
-            const int which = id >> 9, row = (id >> 3) & 63, ch = id & 7;
-            const uint4 w = *reinterpret_cast<const uint4*>(raw + which * kPfRawTile + row * kPfD + ch * 16);
-            uint4 h0, h1;
-            pf_e4m3x4_to_f16x2x2(w.x, h0.x, h0.y);
-            pf_e4m3x4_to_f16x2x2(w.y, h0.z, h0.w);
-            pf_e4m3x4_to_f16x2x2(w.z, h1.x, h1.y);
-            pf_e4m3x4_to_f16x2x2(w.w, h1.z, h1.w);
-            unsigned char* const dst = pf_smem + (which ? kPfOffV : kPfOffK);
-            *reinterpret_cast<uint4*>(dst + pf_swz(row, 2 * ch)) = h0;
-            *reinterpret_cast<uint4*>(dst + pf_swz(row, 2 * ch + 1)) = h1;
-        }
-        for (int id = tid; id < kPfKeys; id += n_threads) {
-            const float* const sc = reinterpret_cast<const float*>(raw + 2 * kPfRawTile);
-            const float lg = fmaxf(pf_lg2(sc[kPfKeys + id]), kPfLgFloor);
-            cst[id] = sc[id] * p.scale_log2e;
-            cst[kPfKeys + id] = lg;
-            cst[2 * kPfKeys + id] = pf_ex2(-lg);
-        }
         __syncthreads();
+        if (1 < n_tiles) issue_raw(1);
+        convert(0);
+    }
 
+    for (int j = 0; j < n_tiles; ++j) {
+        if constexpr (kMT == 1) {
+            cp_async_wait<0>();
+            __syncthreads();   // raw tile j has landed for every thread; everybody is done with the f16 tiles of j-1
+            if (j + 1 < n_tiles) issue_raw(j + 1);
+            convert(j);
+            __syncthreads();
+        } else {
+            cp_async_wait<0>();
+            __syncthreads();   // f16 tile j is complete, raw tile j+1 has landed, f16 buffer (j+1)%2 is free again
+            if (j + 2 < n_tiles) issue_raw(j + 2);
+            if (j + 1 < n_tiles) convert(j + 1);   // other warps' products overlap this
+        }
         if (j > warp_last_tile) continue;   // every key of this tile is in this warp's future
 
-        // ---- S = Q K^T (16 x 64 per warp) ----
-        float s[8][4];
+        const uint32_t k_s = smem_base + L::kOffKV + (j % L::kBufs) * 2 * kPfTileF16, v_s = k_s + kPfTileF16;
+        const float* const cst = reinterpret_cast<const float*>(pf_smem + L::kOffCst + (j % L::kBufs) * kPfCstBytes);
+        const float2* const ksl2 = reinterpret_cast<const float2*>(cst);
+        const float2* const lgv2 = reinterpret_cast<const float2*>(cst + kPfKeys);
+        const float2* const rvs2 = reinterpret_cast<const float2*>(cst + 2 * kPfKeys);
+
+        // ---- S = Q K^T (16 * kMT x 64 per warp): every K fragment feeds kMT products ----
+        float s[kMT][8][4];
 #pragma unroll
-        for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+        for (int t = 0; t < kMT; ++t)
+#pragma unroll
+            for (int n = 0; n < 8; ++n) s[t][n][0] = s[t][n][1] = s[t][n][2] = s[t][n][3] = 0.0f;
 #pragma unroll
         for (int kk = 0; kk < kPfD / 16; ++kk) {
-            uint32_t a[4];
-            pf_ldsm_x4(a, q_s + pf_swz(a_row, 2 * kk + a_ch));
+            uint32_t a[kMT][4];
+#pragma unroll
+            for (int t = 0; t < kMT; ++t) pf_ldsm_x4(a[t], q_s + pf_swz(16 * t + a_row, 2 * kk + a_ch));
 #pragma unroll
             for (int nn = 0; nn < 4; ++nn) {
                 uint32_t b[4];
-                pf_ldsm_x4(b, smem_base + kPfOffK + pf_swz(16 * nn + k_row, 2 * kk + k_ch));
-                pf_mma(s[2 * nn], a, b[0], b[1]);
-                pf_mma(s[2 * nn + 1], a, b[2], b[3]);
+                pf_ldsm_x4(b, k_s + pf_swz(16 * nn + k_row, 2 * kk + k_ch));
+#pragma unroll
+                for (int t = 0; t < kMT; ++t) {
+                    pf_mma(s[t][2 * nn], a[t], b[0], b[1]);
+                    pf_mma(s[t][2 * nn + 1], a[t], b[2], b[3]);
+                }
             }
         }
 
         // ---- log2-domain scores with the V scale in the exponent, causal mask, online softmax ----
         const bool diag = j * kPfKeys + kPfKeys - 1 > clen + tok0;   // some key of the tile is masked for some row
-        float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const float2 kk = ksl2[n * 4 + c], lg = lgv2[n * 4 + c];
-            s[n][0] = fmaf(s[n][0], kk.x, lg.x);
-            s[n][1] = fmaf(s[n][1], kk.y, lg.y);
-            s[n][2] = fmaf(s[n][2], kk.x, lg.x);
-            s[n][3] = fmaf(s[n][3], kk.y, lg.y);
-            if (diag) {
-                const int kpos = j * kPfKeys + 8 * n + 2 * c;
-                if (kpos > qpos_lo) s[n][0] = -INFINITY;
-                if (kpos + 1 > qpos_lo) s[n][1] = -INFINITY;
-                if (kpos > qpos_hi) s[n][2] = -INFINITY;
-                if (kpos + 1 > qpos_hi) s[n][3] = -INFINITY;
+        for (int t = 0; t < kMT; ++t) {
+            const int qpos_lo = clen + tok0 + 16 * t + r, qpos_hi = qpos_lo + 8;
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const float2 kk = ksl2[n * 4 + c], lg = lgv2[n * 4 + c];
+                s[t][n][0] = fmaf(s[t][n][0], kk.x, lg.x);
+                s[t][n][1] = fmaf(s[t][n][1], kk.y, lg.y);
+                s[t][n][2] = fmaf(s[t][n][2], kk.x, lg.x);
+                s[t][n][3] = fmaf(s[t][n][3], kk.y, lg.y);
+                if (diag) {
+                    const int kpos = j * kPfKeys + 8 * n + 2 * c;
+                    if (kpos > qpos_lo) s[t][n][0] = -INFINITY;
+                    if (kpos + 1 > qpos_lo) s[t][n][1] = -INFINITY;
+                    if (kpos > qpos_hi) s[t][n][2] = -INFINITY;
+                    if (kpos + 1 > qpos_hi) s[t][n][3] = -INFINITY;
+                }
+                mx_lo = fmaxf(mx_lo, fmaxf(s[t][n][0], s[t][n][1]));
+                mx_hi = fmaxf(mx_hi, fmaxf(s[t][n][2], s[t][n][3]));
             }
-            mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
-            mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
-        }
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);
-        const float corr_lo = pf_ex2(m_lo - n_lo), corr_hi = pf_ex2(m_hi - n_hi);
-        m_lo = n_lo;
-        m_hi = n_hi;
-        float sum_lo = 0.0f, sum_hi = 0.0f;
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float n_lo = fmaxf(m_run[t][0], mx_lo), n_hi = fmaxf(m_run[t][1], mx_hi);
+            const float corr_lo = pf_ex2(m_run[t][0] - n_lo), corr_hi = pf_ex2(m_run[t][1] - n_hi);
+            m_run[t][0] = n_lo;
+            m_run[t][1] = n_hi;
+            float sum_lo = 0.0f, sum_hi = 0.0f;
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            const float2 rv = rvs2[n * 4 + c];
-            s[n][0] = pf_ex2(s[n][0] - n_lo);
-            s[n][1] = pf_ex2(s[n][1] - n_lo);
-            s[n][2] = pf_ex2(s[n][2] - n_hi);
-            s[n][3] = pf_ex2(s[n][3] - n_hi);
-            sum_lo = fmaf(s[n][0], rv.x, fmaf(s[n][1], rv.y, sum_lo));
-            sum_hi = fmaf(s[n][2], rv.x, fmaf(s[n][3], rv.y, sum_hi));
-        }
-        l_lo = fmaf(l_lo, corr_lo, sum_lo);
-        l_hi = fmaf(l_hi, corr_hi, sum_hi);
-        if (__any_sync(0xffffffffu, corr_lo != 1.0f || corr_hi != 1.0f)) {
+            for (int n = 0; n < 8; ++n) {
+                const float2 rv = rvs2[n * 4 + c];
+                s[t][n][0] = pf_ex2(s[t][n][0] - n_lo);
+                s[t][n][1] = pf_ex2(s[t][n][1] - n_lo);
+                s[t][n][2] = pf_ex2(s[t][n][2] - n_hi);
+                s[t][n][3] = pf_ex2(s[t][n][3] - n_hi);
+                sum_lo = fmaf(s[t][n][0], rv.x, fmaf(s[t][n][1], rv.y, sum_lo));
+                sum_hi = fmaf(s[t][n][2], rv.x, fmaf(s[t][n][3], rv.y, sum_hi));
+            }
+            l_run[t][0] = fmaf(l_run[t][0], corr_lo, sum_lo);
+            l_run[t][1] = fmaf(l_run[t][1], corr_hi, sum_hi);
+            if (__any_sync(0xffffffffu, corr_lo != 1.0f || corr_hi != 1.0f)) {
 #pragma unroll
-            for (int n = 0; n < 16; ++n) {
-                o[n][0] *= corr_lo;
-                o[n][1] *= corr_lo;
-                o[n][2] *= corr_hi;
-                o[n][3] *= corr_hi;
+                for (int n = 0; n < 16; ++n) {
+                    o[t][n][0] *= corr_lo;
+                    o[t][n][1] *= corr_lo;
+                    o[t][n][2] *= corr_hi;
+                    o[t][n][3] *= corr_hi;
+                }
             }
         }
 
-        // ---- O += W V (V as exact E4M3 values; four 16-key steps) ----
+        // ---- O += W V (V as exact E4M3 values; four 16-key steps; every V fragment feeds kMT products) ----
 #pragma unroll
         for (int kc = 0; kc < kPfKeys / 16; ++kc) {
-            uint32_t a[4];
-            a[0] = pf_pack_f16x2(s[2 * kc][0], s[2 * kc][1]);
-            a[1] = pf_pack_f16x2(s[2 * kc][2], s[2 * kc][3]);
-            a[2] = pf_pack_f16x2(s[2 * kc + 1][0], s[2 * kc + 1][1]);
-            a[3] = pf_pack_f16x2(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+            uint32_t a[kMT][4];
+#pragma unroll
+            for (int t = 0; t < kMT; ++t) {
+                a[t][0] = pf_pack_f16x2(s[t][2 * kc][0], s[t][2 * kc][1]);
+                a[t][1] = pf_pack_f16x2(s[t][2 * kc][2], s[t][2 * kc][3]);
+                a[t][2] = pf_pack_f16x2(s[t][2 * kc + 1][0], s[t][2 * kc + 1][1]);
+                a[t][3] = pf_pack_f16x2(s[t][2 * kc + 1][2], s[t][2 * kc + 1][3]);
+            }
 #pragma unroll
             for (int nn = 0; nn < kPfD / 16; ++nn) {
                 uint32_t b[4];
-                pf_ldsm_x4_trans(b, smem_base + kPfOffV + pf_swz(16 * kc + v_row, 2 * nn + v_ch));
-                pf_mma(o[2 * nn], a, b[0], b[1]);
-                pf_mma(o[2 * nn + 1], a, b[2], b[3]);
+                pf_ldsm_x4_trans(b, v_s + pf_swz(16 * kc + v_row, 2 * nn + v_ch));
+#pragma unroll
+                for (int t = 0; t < kMT; ++t) {
+                    pf_mma(o[t][2 * nn], a[t], b[0], b[1]);
+                    pf_mma(o[t][2 * nn + 1], a[t], b[2], b[3]);
+                }
             }
         }
     }
 
     // ---- normalise and store ----
     if (!warp_active) return;
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
-    const int tok_lo = tok0 + r, tok_hi = tok_lo + 8;
-    __nv_bfloat16* const out_lo = p.out + (static_cast<size_t>(tok_lo) * p.num_q_heads + qh) * kPfD + 2 * c;
-    __nv_bfloat16* const out_hi = p.out + (static_cast<size_t>(tok_hi) * p.num_q_heads + qh) * kPfD + 2 * c;
 #pragma unroll
-    for (int n = 0; n < 16; ++n) {
-        if (tok_lo < p.n_new)
-            *reinterpret_cast<__nv_bfloat162*>(out_lo + 8 * n) = __floats2bfloat162_rn(o[n][0] * inv_lo, o[n][1] * inv_lo);
-        if (tok_hi < p.n_new)
-            *reinterpret_cast<__nv_bfloat162*>(out_hi + 8 * n) = __floats2bfloat162_rn(o[n][2] * inv_hi, o[n][3] * inv_hi);
+    for (int t = 0; t < kMT; ++t) {
+        float l_lo = l_run[t][0], l_hi = l_run[t][1];
+        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+        const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+        const int tok_lo = tok0 + 16 * t + r, tok_hi = tok_lo + 8;
+        __nv_bfloat16* const out_lo = p.out + (static_cast<size_t>(tok_lo) * p.num_q_heads + qh) * kPfD + 2 * c;
+        __nv_bfloat16* const out_hi = p.out + (static_cast<size_t>(tok_hi) * p.num_q_heads + qh) * kPfD + 2 * c;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            if (tok_lo < p.n_new)
+                *reinterpret_cast<__nv_bfloat162*>(out_lo + 8 * n) = __floats2bfloat162_rn(o[t][n][0] * inv_lo, o[t][n][1] * inv_lo);
+            if (tok_hi < p.n_new)
+                *reinterpret_cast<__nv_bfloat162*>(out_hi + 8 * n) = __floats2bfloat162_rn(o[t][n][2] * inv_hi, o[t][n][3] * inv_hi);
+        }
     }
+}
+
+template <int kMT>
+int launch_prefill(PfArgs a, cudaStream_t stream, const char* fn) {
+    const int warps = a.heads_per_cta * a.subs;
+    const int tokens_per_cta = 16 * kMT * a.subs;
+    const int smem = PfSmem<kMT>::bytes(warps);
+    {   // opt in to the shared memory once per device
+        static std::atomic<unsigned> configured{0};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const unsigned bit = 1u << (dev & 31);
+        if ((configured.load(std::memory_order_relaxed) & bit) == 0) {
+            cudaFuncSetAttribute(reinterpret_cast<const void*>(&flash_prefill_kernel<kMT>),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<kMT>::bytes(kPfMaxWarps));
+            configured.fetch_or(bit, std::memory_order_relaxed);
+        }
+    }
+    const dim3 grid(static_cast<unsigned>((a.n_new + tokens_per_cta - 1) / tokens_per_cta),
+                    static_cast<unsigned>(a.num_kv_heads * a.head_chunks));
+    RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
+    host::launch(flash_prefill_kernel<kMT>, grid, dim3(static_cast<unsigned>(warps * 32)), static_cast<size_t>(smem), stream, a);
+    return host::check_launch(fn);
 }
 
 }  // namespace
@@ -365,24 +447,11 @@ extern "C" int rh_flash_prefill_bf16(void* out, const void* q, const uint8_t* k,
     a.subs = kPfMaxWarps / a.heads_per_cta;
     a.head_chunks = (a.group + a.heads_per_cta - 1) / a.heads_per_cta;
     a.scale_log2e = scale * kPfLog2e;
-    const int warps = a.heads_per_cta * a.subs;
-    const int tokens_per_cta = 16 * a.subs;
-    const int smem = pf_smem_bytes(warps);
-    {   // opt in to the shared memory once per device
-        static std::atomic<unsigned> configured{0};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        const unsigned bit = 1u << (dev & 31);
-        if ((configured.load(std::memory_order_relaxed) & bit) == 0) {
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(&flash_prefill_kernel),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, pf_smem_bytes(kPfMaxWarps));
-            configured.fetch_or(bit, std::memory_order_relaxed);
-        }
-    }
-    const dim3 grid(static_cast<unsigned>((n_new + tokens_per_cta - 1) / tokens_per_cta),
-                    static_cast<unsigned>(num_kv_heads * a.head_chunks));
-    RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
-    host::launch(flash_prefill_kernel, grid, dim3(static_cast<unsigned>(warps * 32)), static_cast<size_t>(smem),
-                 static_cast<cudaStream_t>(stream), a);
-    return host::check_launch(fn);
+    // Two 16-row tiles per warp halve the shared-memory reads per product (one CTA per SM, 255 registers);
+    // short prompts do not fill the GPU with such CTAs and take the one-tile form (two CTAs per SM).
+    const long long ctas_wide = static_cast<long long>((n_new + 32 * a.subs - 1) / (32 * a.subs)) * num_kv_heads * a.head_chunks;
+    const int pick = host::tuning(host::kPrefillTiles);
+    const bool wide = pick == 2 || (pick != 1 && ctas_wide >= 2LL * host::num_sms());
+    return wide ? launch_prefill<2>(a, static_cast<cudaStream_t>(stream), fn)
+                : launch_prefill<1>(a, static_cast<cudaStream_t>(stream), fn);
 }

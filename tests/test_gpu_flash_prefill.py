@@ -91,14 +91,22 @@ def test_flash_prefill_matches_exact_attention_and_reference(orc, ref, n_new, ca
     q, kc, ks, vc, vs = make_case(n_new, cache_len, Hq, Hkv, D, seed=n_new * 7 + cache_len, **kw)
     scale = 1.0 / math.sqrt(D)
     cl = torch.tensor([cache_len], dtype=torch.int32, device="cuda")
-    out = torch.full((n_new, Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
-    K.flash_prefill_bf16(out, q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
+    outs = {}
+    try:
+        for tiles in (1, 2):       # 16 or 32 query rows per warp (the library picks by problem size)
+            K.tune("prefill_tiles", tiles)
+            outs[tiles] = torch.full((n_new, Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+            K.flash_prefill_bf16(outs[tiles], q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
+    finally:
+        K.tune("prefill_tiles", 0)
+    out = outs[1]
     out_naive, out_flash = torch.empty_like(out), torch.empty_like(out)
     ref.attention_causal_bf16(out_naive, q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
     ref.flash_prefill_bf16(out_flash, q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
     torch.cuda.synchronize()
     exact_bits, exact = orc.attention_causal_fp8(to_np(q), to_np(kc), to_np(vc), to_np(ks), to_np(vs), cache_len, scale)
-    check(out, exact_bits, exact, "this library")
+    check(outs[1], exact_bits, exact, "this library, 16 rows per warp")
+    check(outs[2], exact_bits, exact, "this library, 32 rows per warp")
     check(out_naive, exact_bits, exact, "reference naive kernel", significance=64)
     a, b = out_naive.float().flatten(), out.float().flatten()
     if flavour != "spread":
