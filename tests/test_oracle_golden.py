@@ -231,3 +231,31 @@ def test_attention_oracle_is_within_one_ulp_of_the_reference_kernels():
             assert (np.abs(ref_val - exact) <= 1.5 * 2.0 ** -7 * rowmax).all(), (idx, name)
             assert np.abs(ordered(ref_bits) - ordered(bits))[significant].max() <= 1, (idx, name)
             assert (ordered(ref_bits) == ordered(bits)).mean() > 0.99, (idx, name)
+
+
+def test_prefill_oracle_is_within_one_ulp_of_the_reference_naive_kernel():
+    """n_new > 1: the reference's naive causal kernel (run on a B200 by make_golden_attention.py) is the oracle of
+    its flash_prefill test; the double-precision restatement must round to within one bf16 ulp of it.  The
+    reference's flash_prefill kernel, which rounds its operands to f16, must stay within its own test's bounds
+    of the restatement (max-abs 5e-2 at this value range, cosine 0.998: tests/kernels/test_flash_prefill.cpp:88-89)."""
+    data = np.load(GOLD / "reference_cuda_attention.npz")
+    cases = data["prefill_cases"]
+    assert len(cases) >= 3
+
+    def ordered(bits):
+        b = bits.astype(np.int32)
+        return np.where(b & 0x8000, -(b & 0x7FFF), b & 0x7FFF)
+
+    for idx, (n_new, cache_len, Hq, Hkv, _q_mul) in enumerate(cases):
+        g = lambda name: np.ascontiguousarray(data[f"prefill{idx}/{name}"])
+        bits, exact = ORC.attention_causal_fp8(g("q"), g("k_codes"), g("v_codes"), g("k_scale"), g("v_scale"),
+                                               int(cache_len), 1.0 / np.sqrt(np.float32(128)).item())
+        rowmax = np.abs(exact).max(axis=-1, keepdims=True)
+        significant = np.abs(exact) >= rowmax / 64
+        naive = g("out_naive")
+        assert np.abs(ordered(naive) - ordered(bits))[significant].max() <= 1, idx
+        assert (ordered(naive) == ordered(bits)).mean() > 0.99, idx
+        flash = (g("out_flash").astype(np.uint32) << 16).view(np.float32).ravel().astype(np.float64)
+        e = exact.ravel().astype(np.float64)
+        assert np.dot(flash, e) / (np.linalg.norm(flash) * np.linalg.norm(e)) >= 0.998, idx
+        assert (np.abs(flash - e) <= 1.5 * 2.0 ** -7 * np.repeat(rowmax.ravel(), 128) * 4).all(), idx
