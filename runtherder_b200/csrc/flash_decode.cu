@@ -27,8 +27,9 @@
 // (every fourth 16-byte chunk) and consumes it 4 bytes per k-step; the sum over keys is order-free
 // too, so lane (r, c) takes keys 4c..4c+3 for the second product and transposes their bytes into key
 // pairs with four prmt per 16 bytes; the weights change from "row = key" to "row = column" with one
-// movmatrix per 8 keys.  Each lane stages exactly the bytes it consumes through its own slots of a
-// cp.async ring, several tiles ahead.
+// movmatrix per 8 keys.  A warp stages its tiles through its own cp.async ring, several tiles ahead:
+// V bytes and scales by the lane that consumes them, K rows as whole rows (full 128-byte lines per
+// request) read back across lanes after a __syncwarp — no CTA barrier in the key loop.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
@@ -154,9 +155,10 @@ __device__ __forceinline__ void fd_lds(uint32_t* dst, const unsigned char* src) 
     }
 }
 
-// Geometry of the per-warp staging ring.  A stage holds one 16-key tile exactly as the lanes consume
-// it: every lane copies (cp.async) the bytes it will itself read back, so a stage needs no barrier,
-// only the lane's own wait_group.  [2 K rows][chunks][32 lanes] + [4 V keys][chunks][32 lanes] + 32 scales.
+// Geometry of the per-warp staging ring.  A stage holds one 16-key tile: the 16 K rows (row-major,
+// odd rows rotated by four chunks; for head_dim 32 per consuming lane instead), the V bytes as
+// [4 keys][chunks][32 lanes] and 32 scales, each V byte and scale copied by the lane that reads it
+// back, so a stage needs the lane's own wait_group and a __syncwarp for the K rows.
 template <int D>
 struct FdRing {
     static constexpr int kKChunk = (D / 4 >= 16) ? 16 : D / 4;   // bytes per cp.async of a K quarter-row
@@ -234,6 +236,14 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_p
     const uint8_t* const v_lane3 = v_lane2 + row_stride;
     const float* const s_lane = (lane >= 16 ? p.v_scale : p.k_scale) + static_cast<size_t>(lane & 15) * p.num_kv_heads + kvh;
 
+    // K rows are staged as whole rows (a request covers full 128-byte lines: 8 lanes per row) and read back
+    // across lanes; odd rows keep their chunks rotated by four so the reads stay conflict-free.
+    constexpr bool kRowCopies = Ring::kKChunk == 16;
+    constexpr int kCPR = D / 16;                     // 16-byte chunks per K row
+    constexpr int kKCopies = kRowCopies ? 16 * kCPR / 32 : 0;
+    const int row_l = lane / (kCPR < 32 ? kCPR : 32), chunk_l = lane % (kCPR < 32 ? kCPR : 32);
+    auto k_swz = [](int row) { return kCPR >= 8 ? ((row & 1) << 2) : 0; };
+    const uint8_t* const k_row_lane = p.k + static_cast<size_t>(kvh) * D + chunk_l * 16 + row_l * row_stride;
     const int my_tiles = n_tiles > warp ? (n_tiles - warp + kFdWarps - 1) / kFdWarps : 0;
     unsigned char* const ring = fd_smem + static_cast<size_t>(warp) * Ring::kStages * Ring::kStageBytes;
 
@@ -247,12 +257,20 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_p
                 const size_t off = static_cast<size_t>(kb) * row_stride;
                 const float* const s_src = s_lane + static_cast<size_t>(kb) * p.num_kv_heads;
                 if (kb + kFdSubKeys <= end) {   // every sub-tile but the last of the history
+                    if constexpr (kRowCopies) {   // whole 128-byte lines per request: 32 / kCPR rows per instruction
 #pragma unroll
-                    for (int j = 0; j < 2; ++j)
+                        for (int i2 = 0; i2 < kKCopies; ++i2) {
+                            const int row = i2 * (32 / kCPR) + row_l;
+                            fd_cp_async<16>(st + row * D + ((chunk_l ^ k_swz(row)) << 4), k_row_lane + off + i2 * (32 / kCPR) * row_stride);
+                        }
+                    } else {
 #pragma unroll
-                        for (int ch = 0; ch < Ring::kKChunks; ++ch)
-                            fd_cp_async<Ring::kKChunk>(st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk,
-                                                       (j == 0 ? k_lane : k_lane_b) + off + ch * 4 * Ring::kKChunk);
+                        for (int j = 0; j < 2; ++j)
+#pragma unroll
+                            for (int ch = 0; ch < Ring::kKChunks; ++ch)
+                                fd_cp_async<Ring::kKChunk>(st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk,
+                                                           (j == 0 ? k_lane : k_lane_b) + off + ch * 4 * Ring::kKChunk);
+                    }
 #pragma unroll
                     for (int i4 = 0; i4 < 4; ++i4)
 #pragma unroll
@@ -261,13 +279,23 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_p
                                                        (i4 == 0 ? v_lane : i4 == 1 ? v_lane1 : i4 == 2 ? v_lane2 : v_lane3) + off + ch * Ring::kVChunk);
                     fd_cp_async<4>(st + Ring::kKBytes + Ring::kVBytes + lane * 4, s_src);
                 } else {
+                    if constexpr (kRowCopies) {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const bool live = kb + key_a + 2 * j < end;
+                        for (int i2 = 0; i2 < kKCopies; ++i2) {
+                            const int row = i2 * (32 / kCPR) + row_l;
+                            const bool live = kb + row < end;
+                            fd_cp_async_zfill<16>(st + row * D + ((chunk_l ^ k_swz(row)) << 4),
+                                                  live ? k_row_lane + off + i2 * (32 / kCPR) * row_stride : p.k, live);
+                        }
+                    } else {
 #pragma unroll
-                        for (int ch = 0; ch < Ring::kKChunks; ++ch)
-                            fd_cp_async_zfill<Ring::kKChunk>(st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk,
-                                                             live ? k_lane + off + (2 * j) * row_stride + ch * 4 * Ring::kKChunk : p.k, live);
+                        for (int j = 0; j < 2; ++j) {
+                            const bool live = kb + key_a + 2 * j < end;
+#pragma unroll
+                            for (int ch = 0; ch < Ring::kKChunks; ++ch)
+                                fd_cp_async_zfill<Ring::kKChunk>(st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk,
+                                                                 live ? k_lane + off + (2 * j) * row_stride + ch * 4 * Ring::kKChunk : p.k, live);
+                        }
                     }
 #pragma unroll
                     for (int i4 = 0; i4 < 4; ++i4) {
@@ -290,9 +318,15 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_p
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int ch = 0; ch < Ring::kKChunks; ++ch)
-                fd_lds<Ring::kKChunk>(&tl.kw[j][ch * (Ring::kKChunk / 4)],
-                                      st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk);
+            for (int ch = 0; ch < Ring::kKChunks; ++ch) {
+                if constexpr (kRowCopies) {   // row key_a + 2j, chunk 4*ch + c of it (copied by other lanes)
+                    const int row = key_a + 2 * j;
+                    fd_lds<16>(&tl.kw[j][ch * 4], st + row * D + (((4 * ch + c) ^ k_swz(row)) << 4));
+                } else {
+                    fd_lds<Ring::kKChunk>(&tl.kw[j][ch * (Ring::kKChunk / 4)],
+                                          st + ((j * Ring::kKChunks + ch) * 32 + lane) * Ring::kKChunk);
+                }
+            }
 #pragma unroll
         for (int i4 = 0; i4 < 4; ++i4)
 #pragma unroll
@@ -451,8 +485,10 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_p
     };
 
     for (int i = 0; i < my_tiles; ++i) {
+        if constexpr (kRowCopies) __syncwarp();     // every lane has read the stage that is refilled next
         issue_tile(i + Ring::kStages - 1);          // into the stage read one trip ago
-        cp_async_wait<Ring::kStages - 1>();         // tile i has landed (this lane's own copies)
+        cp_async_wait<Ring::kStages - 1>();         // this lane's copies of tile i have landed
+        if constexpr (kRowCopies) __syncwarp();     // ... and the other lanes' K rows
         FdTile<D> tl[kFdSubs];
 #pragma unroll
         for (int u = 0; u < kFdSubs; ++u) read_tile(tl[u], i, u);
