@@ -56,6 +56,9 @@ def parse_args():
                    help="time the attention over the FP8 cache instead of the row-wise chain (secondary line; not the "
                         "headline metric): the split-KV flash decode for --config c2 (or any config with --depth), "
                         "the causal prefill for configs with more than one token (c1, c3)")
+    p.add_argument("--with-attention", action="store_true",
+                   help="layer-chain configs: run the attention over the FP8 cache inside every layer (flash decode for "
+                        "the decode config, flash prefill otherwise), between the KV append and the quantisation of its output")
     p.add_argument("--depth", type=int, default=0, help="--attention: override the context depth (keys attended)")
     p.add_argument("--splits", type=int, default=32, help="--attention: split count (the reference uses 32)")
     p.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE",
@@ -458,11 +461,26 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
         o["at_pos"].fill_(cfg.start_pos + b)
     for i in ins:
         i["positions"] = torch.arange(cfg.start_pos + b, cfg.start_pos + e, dtype=torch.int32, device=dev)
+    partial = None
+    if args.with_attention:
+        if world != 1:
+            raise SystemExit("--with-attention is a single-GPU measurement (attention does not shard by rows)")
+        from runtherder_b200 import kernels as Kn
+        partial = torch.empty(Kn.flash_split_scratch_floats(cfg.q_heads, cfg.head_dim, layer_ops.ATTENTION_SPLITS),
+                              dtype=torch.float32, device=dev)
+        if cfg.start_pos > 0:      # decode: give every layer's cache a seeded history to attend
+            gen = torch.Generator(device=dev).manual_seed(cfg.seed + 79)
+            zero = torch.zeros(1, dtype=torch.int32, device=dev)
+            for o in outs:
+                for codes, scales in ((o["k_cache"], o["k_scale"]), (o["v_cache"], o["v_scale"])):
+                    x = torch.randn(cfg.start_pos, cfg.kv_heads, cfg.head_dim, device=dev, generator=gen).to(torch.bfloat16)
+                    Kn.quantize_kv_fp8(codes, scales, x, zero, 1, cfg.start_pos * cfg.kv_heads, cfg.head_dim)
 
     def forward():
         n = 0
         for l in range(L):
-            n += layer_ops.fused_layer_step(cfg, ins[l % n_sets], outs[l % n_sets], with_embedding=(l == 0))
+            n += layer_ops.fused_layer_step(cfg, ins[l % n_sets], outs[l % n_sets], with_embedding=(l == 0),
+                                            attention_partial=partial)
         return n
 
     use_graph = args.graph == "on" or (args.graph == "auto" and cfg.tokens == 1)
@@ -506,7 +524,8 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
             "config": {"workload": cfg.name, "token_rows": T, "rows_per_gpu": rows, "layers": L, "hidden": cfg.hidden,
                        "inter": cfg.inter, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads, "head_dim": cfg.head_dim,
                        "int8": cfg.int8, "qk_norm": cfg.qk_norm, "start_pos": cfg.start_pos, "seed": cfg.seed,
-                       "ops_per_layer": [n for n, _ in cfg.chain_ops()], "algorithmic_bytes_per_row_per_layer": per_row,
+                       "ops_per_layer": [n for n, _ in cfg.chain_ops()] + (["attention (flash decode: 2 launches)" if T == 1 else "attention (flash prefill)"] if partial is not None else []),
+                       "algorithmic_bytes_per_row_per_layer": per_row,
                        "buffer_sets": n_sets, "cuda_graph": graph is not None, "parallelism": f"rows/{world}",
                        "l2": f"{n_sets} rotating buffer sets; a set is {'larger' if layer_bytes > 126e6 else 'smaller'} than the 126 MB L2"},
             "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "clocks": clocks.summary()}
@@ -519,7 +538,7 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
 
     if world == 1 and not args.no_refcuda:
         try:
-            line["ref_cuda"] = time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph, max(3, min(K, 20)))
+            line["ref_cuda"] = time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph, max(3, min(K, 20)), partial)
         except Exception as exc:
             line["ref_cuda"] = {"unavailable": str(exc)[:200]}
     if rank == 0:
@@ -753,7 +772,7 @@ def chain_roofline(cfg, i, o, rows, peak, peak_kind):
             "note": "back-to-back launches on one buffer set" + ("" if rows * bpr > 126e6 else " that fits in L2: latency-bound, not an HBM figure")}
 
 
-def time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph, reps):
+def time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph, reps, partial=None):
     import torch
     sys.path.insert(0, str(ROOT / "tests"))
     from gpu_util import RefCuda
@@ -767,7 +786,8 @@ def time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph
             n = 1
             ref.embedding_lookup_bf16_forward(outs[0]["emb"], ins[0]["table"], ins[0]["ids"], rows, cfg.hidden)
             for l in range(L):
-                n += layer_ops.reference_sequence(ref, cfg, ins[l % n_sets], outs[l % n_sets], scratch, dedup_quant=dedup)
+                n += layer_ops.reference_sequence(ref, cfg, ins[l % n_sets], outs[l % n_sets], scratch, dedup_quant=dedup,
+                                                  attention_partial=partial)
             return n
         n = forward()
         torch.cuda.synchronize()

@@ -56,9 +56,32 @@ def alloc_outputs(cfg: LayerConfig, rows: int, device="cuda", slots: Optional[in
     return o
 
 
+ATTENTION_SPLITS = 32   # what the reference's AdaptiveAttention passes (src/attention/adaptive.cu:13)
+
+
+def attention_step(api, cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dict[str, torch.Tensor], partial: torch.Tensor,
+                   stream=None) -> int:
+    """The attention between the KV append and the quantisation of its output, as AdaptiveAttention dispatches
+    it (src/attention/adaptive.cu:24-41): split-KV flash decode for one token, flash prefill otherwise.  Reads
+    the rotated q and the layer's cache, with *at_pos as the number of keys cached before these tokens; writes
+    i["attn"].  `api` offers the reference's function names.  Returns the number of kernels launched."""
+    import math
+    T = i["x"].shape[0]
+    scale = 1.0 / math.sqrt(cfg.head_dim)
+    if T == 1:
+        api.flash_decode_split_bf16(i["attn"], i["q"], o["k_cache"], o["v_cache"], o["k_scale"], o["v_scale"], partial,
+                                    ATTENTION_SPLITS, o["at_pos"], cfg.q_heads, cfg.kv_heads, cfg.head_dim, scale, stream)
+        return 2
+    api.flash_prefill_bf16(i["attn"], i["q"], o["k_cache"], o["v_cache"], o["k_scale"], o["v_scale"], T, o["at_pos"],
+                           cfg.q_heads, cfg.kv_heads, cfg.head_dim, scale, stream)
+    return 1
+
+
 def fused_layer_step(cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dict[str, torch.Tensor], stream=None,
-                     with_embedding: bool = False) -> int:
-    """Enqueue one layer's fused chain; returns the number of kernels launched.
+                     with_embedding: bool = False, attention_partial: Optional[torch.Tensor] = None) -> int:
+    """Enqueue one layer's fused chain; returns the number of kernels launched.  With `attention_partial`
+    (fp32 scratch of flash_split_scratch_floats(Hq, D, ATTENTION_SPLITS) floats) the attention over the FP8
+    cache runs between the KV append and the quantisation of its output.
 
     Reads i[x, residual, q, k, v, attn, gate, up, ...]; q is rotated in place; h_attn / h_ffn receive
     the updated residual stream (the reference passes h_out == residual; separate buffers here keep the
@@ -78,6 +101,8 @@ def fused_layer_step(cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dict[str, 
                   i["inv_freq"], o["k_cache"], o["k_scale"], o["v_cache"], o["v_scale"], o["at_pos"], T,
                   cfg.q_heads, cfg.kv_heads, cfg.head_dim, stream)
     n += 2
+    if attention_partial is not None:
+        n += attention_step(K, cfg, i, o, attention_partial, stream)
     if cfg.int8:
         K.quantize_per_token_int8(o["q_attn_out"], o["s_attn_out"], i["attn"], T, cfg.q_dim, stream)
         K.rmsnorm_add_quant_int8(o["q_ffn_in"], o["s_ffn_in"], o["h_ffn"], None, i["x"], o["h_attn"], i["g_ffn"], T, H,
@@ -93,7 +118,8 @@ def fused_layer_step(cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dict[str, 
 
 
 def reference_sequence(api, cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dict[str, torch.Tensor],
-                       scratch: Dict[str, torch.Tensor], stream=None, dedup_quant: bool = False) -> int:
+                       scratch: Dict[str, torch.Tensor], stream=None, dedup_quant: bool = False,
+                       attention_partial: Optional[torch.Tensor] = None) -> int:
     """The same layer through the reference's own call sequence.  `api` offers the reference's function
     names.  scratch: bf16 `normed`, `ffn_normed`, `act` [T,I] and (int8) `q8` [T,max K], `s8` [T].
     With dedup_quant the repeated quantisation of the same rows (x3 for q/k/v, x2 for gate/up) is
@@ -125,6 +151,8 @@ def reference_sequence(api, cfg: LayerConfig, i: Dict[str, torch.Tensor], o: Dic
     api.quantize_kv_fp8(o["k_cache"], o["k_scale"], i["k"], o["at_pos"], cfg.kv_heads, T * cfg.kv_heads, D, stream)
     api.quantize_kv_fp8(o["v_cache"], o["v_scale"], i["v"], o["at_pos"], cfg.kv_heads, T * cfg.kv_heads, D, stream)
     n += 3
+    if attention_partial is not None:
+        n += attention_step(api, cfg, i, o, attention_partial, stream)
     if cfg.int8:
         quant(o["q_attn_out"], o["s_attn_out"], i["attn"], cfg.q_dim, 1)
     api.rmsnorm_add_bf16_forward(ffn_normed, o["h_ffn"], i["x"], o["h_attn"], i["g_ffn"], T, H, cfg.eps, stream)

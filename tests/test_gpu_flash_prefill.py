@@ -172,3 +172,43 @@ def test_cache_len_is_read_on_the_device_and_arguments_are_checked():
     assert status(n_new=0) == 1 and status(Hq=3) == 1 and status(cache=None) == 1     # RH_ERR_INVALID_ARG
     assert status(D=64) == 2                                                          # RH_ERR_UNSUPPORTED_DIM
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("mode", ["prefill", "decode"])
+def test_layer_chain_with_attention_feeds_the_attention_output_through(orc, mode):
+    """fused_layer_step(..., attention_partial=...) runs RoPE + KV append, then the attention over the cache it
+    just wrote (flash prefill for T > 1, split-KV flash decode for T = 1, as src/attention/adaptive.cu:24-41
+    dispatches), then quantises the attention output: the attention result must match the oracle on the
+    rotated q and the cache contents, and the INT8 codes must be those of that result."""
+    from dataclasses import replace
+    from runtherder_b200 import kernels as K, layer_ops, synth
+    from runtherder_b200.configs import C0
+    if mode == "prefill":
+        cfg, hist = C0, 0
+    else:
+        hist = 150
+        cfg = replace(C0, tokens=1, start_pos=hist, max_seq=hist + 1)
+    T = cfg.tokens
+    ins = synth.make_inputs(cfg)
+    outs = layer_ops.alloc_outputs(cfg, T, slots=cfg.cache_slots)
+    outs["at_pos"].fill_(hist)
+    ins["positions"] = torch.arange(hist, hist + T, dtype=torch.int32, device="cuda")
+    if hist:
+        g = torch.Generator(device="cuda").manual_seed(4)
+        zero = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for codes, scales in ((outs["k_cache"], outs["k_scale"]), (outs["v_cache"], outs["v_scale"])):
+            x = torch.randn(hist, cfg.kv_heads, cfg.head_dim, device="cuda", generator=g).to(torch.bfloat16)
+            K.quantize_kv_fp8(codes, scales, x, zero, 1, hist * cfg.kv_heads, cfg.head_dim)
+    partial = torch.empty(K.flash_split_scratch_floats(cfg.q_heads, cfg.head_dim, layer_ops.ATTENTION_SPLITS),
+                          dtype=torch.float32, device="cuda")
+    launches = layer_ops.fused_layer_step(cfg, ins, outs, attention_partial=partial)
+    torch.cuda.synchronize()
+    assert launches == 5 + (2 if T == 1 else 1)
+    scale = 1.0 / math.sqrt(cfg.head_dim)
+    q_rot = to_np(ins["q"]).reshape(T, cfg.q_heads, cfg.head_dim)
+    bits, exact = orc.attention_causal_fp8(q_rot, to_np(outs["k_cache"])[:hist + T], to_np(outs["v_cache"])[:hist + T],
+                                           to_np(outs["k_scale"])[:hist + T], to_np(outs["v_scale"])[:hist + T], hist, scale)
+    attn = ins["attn"].view(T, cfg.q_heads, cfg.head_dim)
+    check(attn, bits, exact, f"attention inside the {mode} chain")
+    oq, os_ = orc.quant_int8(to_np(ins["attn"]).reshape(T, cfg.q_dim))
+    assert np.array_equal(to_np(outs["q_attn_out"]), oq) and np.array_equal(to_np(outs["s_attn_out"]), os_)
