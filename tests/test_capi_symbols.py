@@ -21,6 +21,8 @@ REFERENCE_CXX_SYMBOLS = [
     "_ZN10runtherder7kernels19swiglu_bf16_forwardEP13__nv_bfloat16PKS1_S4_iP11CUstream_st",
     "_ZN10runtherder7kernels9rope_bf16EP13__nv_bfloat16S2_PKiPKfiiiiP11CUstream_st",
     "_ZN10runtherder7kernels29embedding_lookup_bf16_forwardEP13__nv_bfloat16PKS1_PKiiiP11CUstream_st",
+    "_ZN10runtherder7kernels23flash_decode_split_bf16EP13__nv_bfloat16PKS1_PK13__nv_fp8_e4m3S7_PKfS9_PfiPKiiiifP11CUstream_st",
+    "_ZN10runtherder7kernels18flash_prefill_bf16EP13__nv_bfloat16PKS1_PK13__nv_fp8_e4m3S7_PKfS9_iPKiiiifP11CUstream_st",
 ]
 # bias.cu does not compile in the reference as shipped, so no reference object defines this one
 BIAS_CXX_SYMBOL = "_ZN10runtherder7kernels25qkv_bias_add_bf16_forwardEP13__nv_bfloat16S2_S2_PKS1_S4_S4_iiiP11CUstream_st"
