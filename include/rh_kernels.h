@@ -162,6 +162,17 @@ int rh_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v
                    uint8_t* v_cache, float* v_scale, const int* at_pos, int seq_len, int num_q_heads,
                    int num_kv_heads, int head_dim, void* stream);
 
+/* The same with Qwen2's projection biases folded in (no QK-norm): every q/k/v row is first
+ * bf16(float(x) + float(bias)) — q_bias [Hq*D], k_bias and v_bias [Hkv*D] — then rotated / appended.
+ * Equals qkv_bias_add_bf16_forward followed by rope_bf16 and KVCache::append
+ * (src/model/supported/llama/qwen2.cu's layer; src/kernels/bias.cu:64-90), one launch and one pass over
+ * q/k/v instead of two; q, k_out and both caches are bit-identical to that sequence.  v_in is read
+ * only (the separate bias kernel rewrites it in place; nothing reads it afterwards). */
+int rh_bias_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v_in, const void* q_bias,
+                        const void* k_bias, const void* v_bias, const int* positions, const float* inv_freq,
+                        uint8_t* k_cache, float* k_scale, uint8_t* v_cache, float* v_scale, const int* at_pos,
+                        int seq_len, int num_q_heads, int num_kv_heads, int head_dim, void* stream);
+
 /* ---- Decode-loop glue on the device ------------------------------------------------------- */
 
 /* positions[i] = start_pos + i for i < n, *decode_pos = start_pos: what LlamaModel::stage

@@ -38,6 +38,7 @@ SIGNATURES = {
     "rh_rmsnorm_add_quant_int8": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p],
     "rh_swiglu_quant_int8": [_p, _p, _p, _p, _p, _i, _i, _p],
     "rh_rope_kv_fp8": [_p, _p, _p, _p, _p, _p, _f, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
+    "rh_bias_rope_kv_fp8": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p],
     "rh_stage_positions": [_p, _p, _i, _i, _p],
     "rh_decode_advance": [_p, _p, _p, _p, _i, _p],
     "rh_rope_inv_freq_plain": [_p, _i, _f],

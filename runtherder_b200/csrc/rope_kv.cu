@@ -46,7 +46,24 @@ struct RopeArgs {
     int num_kv_heads;
     int groups_per_item;  // head groups one warp handles for its token
     int items_per_token;
+    // Qwen2's projection biases (src/kernels/bias.cu:64-90), [Hq*D], [Hkv*D], [Hkv*D]; all three or none.
+    // x = bf16(float(x) + float(bias)) is applied to a row as it is loaded, before norm / rotation / append.
+    const void* q_bias;
+    const void* k_bias;
+    const void* v_bias;
 };
+
+// row + bias on packed bf16 words: every element bf16(float(x) + float(b)) (src/kernels/bias.cu:15-28)
+__device__ __forceinline__ uint4 add_bias_row(const uint4& x, const uint4& b) {
+    const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 t = add2_rn(bf2_to_f2(xw[k]), bf2_to_f2(bw[k]));
+        o[k] = pack_bf16x2(t.x, t.y);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
 
 // The rotation.  The reference writes `a*c - b*s` and `a*s + b*c` (src/kernels/rope.cu:53-54) and
 // nvcc contracts each into one product plus a fused multiply-add on the FIRST product; the
@@ -124,7 +141,14 @@ __global__ void __launch_bounds__(256) rope_kv_generic_kernel(const RopeArgs p) 
     for (int g = g_begin; g < g_end; ++g) {
         const int r = g * kHeadsPerGroup + hslot;
         const int role = role_next;
-        const uint4 lo_v = lo_next, hi_v = hi_next;
+        uint4 lo_v = lo_next, hi_v = hi_next;
+        if (p.q_bias != nullptr && role != 3) {
+            const int head = role == 0 ? r : (role == 1 ? r - Hq : r - Hq - Hkv);
+            const uint4* bias = static_cast<const uint4*>(role == 0 ? p.q_bias : (role == 1 ? p.k_bias : p.v_bias)) +
+                                static_cast<size_t>(head) * kVecsPerRow;
+            lo_v = add_bias_row(lo_v, ld_weight(bias + sub));
+            hi_v = add_bias_row(hi_v, ld_weight(bias + sub + kLanesPerHead));
+        }
         if (g + 1 < g_end) {  // prefetch the next group's rows while this one is processed
             src_next = row_src(r + kHeadsPerGroup, role_next);
             if (role_next != 3) {
@@ -340,12 +364,19 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeArgs p) {
     int slot = 0;
     for (int g = g_begin; g < g_end; ++g) {
         cp_async_wait<kRopeDepth - 1>();
-        const uint4 lo_v = mine[slot * 64], hi_v = mine[slot * 64 + 32];
+        uint4 lo_v = mine[slot * 64], hi_v = mine[slot * 64 + 32];
         // refill this slot with the group kDepth ahead; the copy is tied to the values just read so it
         // cannot be issued before they have left shared memory
         if (g + kRopeDepth < g_end) fetch(g + kRopeDepth, slot, lo_v.x ^ hi_v.w);
         cp_async_commit();
         slot = (slot + 1 == kRopeDepth) ? 0 : slot + 1;
+        if (p.q_bias != nullptr) {               // warp-uniform: the group's role picks the bias tensor
+            const uint4* bias = g < gq ? static_cast<const uint4*>(p.q_bias) + static_cast<size_t>(g * kHeadsPerGroup + hslot) * kVecsPerRow
+                                : g < gq + gk ? static_cast<const uint4*>(p.k_bias) + static_cast<size_t>((g - gq) * kHeadsPerGroup + hslot) * kVecsPerRow
+                                              : static_cast<const uint4*>(p.v_bias) + static_cast<size_t>((g - gq - gk) * kHeadsPerGroup + hslot) * kVecsPerRow;
+            lo_v = add_bias_row(lo_v, ld_weight(bias + sub));
+            hi_v = add_bias_row(hi_v, ld_weight(bias + sub + kLanesPerHead));
+        }
 
         if (g < gq) {                            // Q: rotate in place
             uint4* rowp = static_cast<uint4*>(p.q) + (static_cast<size_t>(token) * Hq + g * kHeadsPerGroup + hslot) * kVecsPerRow;
@@ -512,6 +543,31 @@ extern "C" int rh_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, co
                    (reinterpret_cast<uintptr_t>(v_cache) & 7u) == 0,
                RH_ERR_MISALIGNED, "rh_rope_kv_fp8: pointers must be 16-byte aligned (caches: 8)");
     RopeArgs p{q, k_out_or_null, k_in, v_in, q_norm_or_null, k_norm_or_null, eps, positions, inv_freq,
-               k_cache, k_scale, v_cache, v_scale, at_pos, seq_len, num_q_heads, num_kv_heads, 0, 0};
+               k_cache, k_scale, v_cache, v_scale, at_pos, seq_len, num_q_heads, num_kv_heads, 0, 0,
+               nullptr, nullptr, nullptr};
     return dispatch_rope(p, head_dim, norm, true, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rh_bias_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v_in, const void* q_bias,
+                                   const void* k_bias, const void* v_bias, const int* positions, const float* inv_freq,
+                                   uint8_t* k_cache, float* k_scale, uint8_t* v_cache, float* v_scale,
+                                   const int* at_pos, int seq_len, int num_q_heads, int num_kv_heads, int head_dim,
+                                   void* stream) {
+    const char* const fn = "rh_bias_rope_kv_fp8";
+    if (int e = check_rope(fn, seq_len, num_q_heads, num_kv_heads, head_dim)) return e;
+    RH_REQUIRE(q && k_in && v_in && positions && inv_freq && k_cache && k_scale && v_cache && v_scale,
+               RH_ERR_INVALID_ARG, "%s: null pointer", fn);
+    RH_REQUIRE(q_bias && k_bias && v_bias, RH_ERR_INVALID_ARG, "%s: the three biases must be given", fn);
+    RH_REQUIRE(at_pos != nullptr, RH_ERR_INVALID_ARG, "%s: at_pos must not be null", fn);
+    RH_REQUIRE(head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256,
+               RH_ERR_UNSUPPORTED_DIM, "%s: head_dim must be 16, 32, 64, 128 or 256 (got %d)", fn, head_dim);
+    RH_REQUIRE(host::aligned16(q) && host::aligned16(k_out_or_null) && host::aligned16(k_in) && host::aligned16(v_in) &&
+                   host::aligned16(q_bias) && host::aligned16(k_bias) && host::aligned16(v_bias) &&
+                   host::aligned16(inv_freq) && (reinterpret_cast<uintptr_t>(k_cache) & 7u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(v_cache) & 7u) == 0,
+               RH_ERR_MISALIGNED, "%s: pointers must be 16-byte aligned (caches: 8)", fn);
+    RopeArgs p{q, k_out_or_null, k_in, v_in, nullptr, nullptr, 1.0f, positions, inv_freq,
+               k_cache, k_scale, v_cache, v_scale, at_pos, seq_len, num_q_heads, num_kv_heads, 0, 0,
+               q_bias, k_bias, v_bias};
+    return dispatch_rope(p, head_dim, false, true, static_cast<cudaStream_t>(stream));
 }

@@ -20,7 +20,7 @@ __all__ = [
     "RhError", "rmsnorm_bf16_forward", "rmsnorm_add_bf16_forward", "quantize_per_token_int8",
     "dequantize_w8a8", "quantize_kv_fp8", "dequantize_kv_fp8", "swiglu_bf16_forward", "rope_bf16",
     "embedding_lookup_bf16_forward", "qkv_bias_add_bf16_forward", "stage_positions", "decode_advance",
-    "flash_split_scratch_floats", "flash_decode_split_bf16", "flash_prefill_bf16", "tune", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
+    "flash_split_scratch_floats", "flash_decode_split_bf16", "flash_prefill_bf16", "tune", "bias_rope_kv_fp8", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
 ]
 
 
@@ -206,6 +206,21 @@ def rope_kv_fp8(q, k_out, k_in, v_in, q_norm, k_norm, eps: float, positions, inv
     call("rh_rope_kv_fp8", _ptr(q, _BF, nq, "q"), _ptr(k_out, _BF, nk, "k_out"), _ptr(k_in, _BF, nk, "k_in"),
          _ptr(v_in, _BF, nk, "v_in"), _ptr(q_norm, _BF, head_dim, "q_norm"), _ptr(k_norm, _BF, head_dim, "k_norm"),
          eps, _ptr(positions, _I32, seq_len, "positions"), _ptr(inv_freq, _F32, head_dim // 2, "inv_freq"),
+         _fp8_ptr(k_cache, None, "k_cache"), _ptr(k_scale, _F32, None, "k_scale"),
+         _fp8_ptr(v_cache, None, "v_cache"), _ptr(v_scale, _F32, None, "v_scale"), _ptr(at_pos, _I32, 1, "at_pos"),
+         seq_len, num_q_heads, num_kv_heads, head_dim, _stream(stream))
+
+
+def bias_rope_kv_fp8(q, k_out, k_in, v_in, q_bias, k_bias, v_bias, positions, inv_freq, k_cache, k_scale, v_cache,
+                     v_scale, at_pos, seq_len: int, num_q_heads: int, num_kv_heads: int, head_dim: int,
+                     stream=None) -> None:
+    """Qwen2: projection biases + RoPE + FP8 KV-cache append in one launch; equals qkv_bias_add_bf16_forward
+    followed by rope_kv_fp8 (v_in is left unmodified)."""
+    nq, nk = seq_len * num_q_heads * head_dim, seq_len * num_kv_heads * head_dim
+    call("rh_bias_rope_kv_fp8", _ptr(q, _BF, nq, "q"), _ptr(k_out, _BF, nk, "k_out"), _ptr(k_in, _BF, nk, "k_in"),
+         _ptr(v_in, _BF, nk, "v_in"), _ptr(q_bias, _BF, num_q_heads * head_dim, "q_bias"),
+         _ptr(k_bias, _BF, num_kv_heads * head_dim, "k_bias"), _ptr(v_bias, _BF, num_kv_heads * head_dim, "v_bias"),
+         _ptr(positions, _I32, seq_len, "positions"), _ptr(inv_freq, _F32, head_dim // 2, "inv_freq"),
          _fp8_ptr(k_cache, None, "k_cache"), _ptr(k_scale, _F32, None, "k_scale"),
          _fp8_ptr(v_cache, None, "v_cache"), _ptr(v_scale, _F32, None, "v_scale"), _ptr(at_pos, _I32, 1, "at_pos"),
          seq_len, num_q_heads, num_kv_heads, head_dim, _stream(stream))

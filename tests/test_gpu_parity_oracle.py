@@ -166,6 +166,46 @@ def test_qkv_bias_add(n, q_dim, kv_dim):
     assert np.array_equal(to_np(vd), ORC.add_rows(v, vb))
 
 
+@pytest.mark.parametrize("T,Hq,Hkv,D", [(35, 28, 4, 128), (511, 28, 4, 128), (7, 6, 2, 128), (19, 12, 2, 64), (1, 28, 4, 128)])
+def test_bias_fused_into_rope_kv_equals_the_two_step_sequence(T, Hq, Hkv, D):
+    """rh_bias_rope_kv_fp8 (Qwen2: projection biases + RoPE + FP8 KV append in one launch) against the sequence
+    it replaces — qkv_bias_add_bf16_forward, then RoPE + append — on the same inputs: rotated q, rotated k, both
+    caches and their scales bit-identical; v_in untouched.  Qwen2-7B heads (28/4, the aligned kernel), head
+    counts that are not a multiple of the heads per warp (the generic kernel), head_dim 64, one token."""
+    K = _k(); to_dev, to_np = _gpu()
+    from runtherder_b200 import rope_tables
+    g = torch.Generator(device="cuda").manual_seed(T * 31 + Hq)
+    q = (torch.randn(T, Hq, D, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    k = (torch.randn(T, Hkv, D, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    v = (torch.randn(T, Hkv, D, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    qb, kb, vb = ((torch.randn(h * D, device="cuda", generator=g)).to(torch.bfloat16) for h in (Hq, Hkv, Hkv))
+    start = 40
+    positions = torch.arange(start, start + T, dtype=torch.int32, device="cuda")
+    inv = torch.from_numpy(rope_tables.rope_inv_freq_plain(D, 1.0e6)).cuda()
+    at = torch.tensor([start], dtype=torch.int32, device="cuda")
+    slots = start + T + 2
+
+    def caches():
+        return (torch.zeros(slots, Hkv, D, dtype=torch.uint8, device="cuda"), torch.zeros(slots, Hkv, dtype=torch.float32, device="cuda"),
+                torch.zeros(slots, Hkv, D, dtype=torch.uint8, device="cuda"), torch.zeros(slots, Hkv, dtype=torch.float32, device="cuda"))
+
+    # two steps
+    q1, k1, v1 = q.clone(), k.clone(), v.clone()
+    kc1, ks1, vc1, vs1 = caches()
+    K.qkv_bias_add_bf16_forward(q1, k1, v1, qb, kb, vb, T, Hq * D, Hkv * D)
+    K.rope_kv_fp8(q1, k1, k1, v1, None, None, 1e-6, positions, inv, kc1, ks1, vc1, vs1, at, T, Hq, Hkv, D)
+    # fused
+    q2, k2, v2 = q.clone(), k.clone(), v.clone()
+    kc2, ks2, vc2, vs2 = caches()
+    K.bias_rope_kv_fp8(q2, k2, k2, v2, qb, kb, vb, positions, inv, kc2, ks2, vc2, vs2, at, T, Hq, Hkv, D)
+    torch.cuda.synchronize()
+    for a, b in ((q1, q2), (k1, k2), (kc1, kc2), (ks1, ks2), (vc1, vc2), (vs1, vs2)):
+        assert np.array_equal(to_np(a), to_np(b))
+    assert np.array_equal(to_np(v2), to_np(v))                      # read only
+    assert np.array_equal(to_np(v1), ORC.add_rows(to_np(v).reshape(T, Hkv * D), to_np(vb)).reshape(T, Hkv, D))
+    assert bool((ks2[start:start + T] > 0).all()) and bool((ks2[:start] == 0).all())
+
+
 def test_dequantize_w8a8():
     K = _k(); to_dev, to_np = _gpu()
     rng = np.random.default_rng(2)

@@ -56,6 +56,20 @@ def test_capi_rejects_bad_arguments_before_launching():
     assert status("rh_dequantize_w8a8", A, A, A, A, 0, 5, None) == 1
     assert status("rh_tune", b"no_such_knob", 3) == 1
     assert status("rh_tune", b"rows_ctas_per_sm", 0) == 0
+    # attention over the FP8 cache (flash_decode.cu:288-293, flash_prefill.cu:227-229) and the bias-fused RoPE+KV
+    assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 0, A, 8, 2, 128, 0.1, None) == 1      # num_splits
+    assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 4, None, 8, 2, 128, 0.1, None) == 1   # cache_len null
+    assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 4, A, 8, 3, 128, 0.1, None) == 1      # 8 % 3
+    assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 4, A, 8, 2, 512, 0.1, None) == 2
+    assert status("rh_flash_decode_split_bf16", A, A + 2, A, A, A, A, A, 4, A, 8, 2, 128, 0.1, None) == 3
+    assert L.lib.rh_flash_split_scratch_floats(32, 128, 32) == 32 * 32 * 130
+    assert status("rh_flash_prefill_bf16", A, A, A, A, A, A, 0, A, 8, 2, 128, 0.1, None) == 1              # n_new
+    assert status("rh_flash_prefill_bf16", A, A, A, A, A, A, 4, A, 8, 2, 64, 0.1, None) == 2
+    assert b"128" in L.lib.rh_last_error_string()
+    assert status("rh_flash_prefill_bf16", A, A, A, A, None, A, 4, A, 8, 2, 128, 0.1, None) == 1
+    assert status("rh_bias_rope_kv_fp8", A, None, A, A, A, A, None, A, A, A, A, A, A, A, 1, 4, 1, 128, None) == 1   # a bias missing
+    assert status("rh_bias_rope_kv_fp8", A, None, A, A, A, A, A, A, A, A, A, A, A, A, 1, 4, 1, 48, None) == 2
+    assert status("rh_tune", b"prefill_tiles", 0) == 0 and status("rh_tune", b"no_pdl", 0) == 0
 
 
 def test_python_mirror_raises_like_the_reference_exits():
