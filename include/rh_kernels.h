@@ -165,7 +165,7 @@ int rh_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v
 /* The same with Qwen2's projection biases folded in (no QK-norm): every q/k/v row is first
  * bf16(float(x) + float(bias)) — q_bias [Hq*D], k_bias and v_bias [Hkv*D] — then rotated / appended.
  * Equals qkv_bias_add_bf16_forward followed by rope_bf16 and KVCache::append
- * (src/model/supported/llama/qwen2.cu's layer; src/kernels/bias.cu:64-90), one launch and one pass over
+ * (src/model/supported/llama/qwen2.cu:183-191; src/kernels/bias.cu:64-90), one launch and one pass over
  * q/k/v instead of two; q, k_out and both caches are bit-identical to that sequence.  v_in is read
  * only (the separate bias kernel rewrites it in place; nothing reads it afterwards). */
 int rh_bias_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v_in, const void* q_bias,
