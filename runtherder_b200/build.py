@@ -21,7 +21,7 @@ OUT = PKG / "_C"
 INCLUDE = PKG.parent / "include"
 LIB = OUT / "librh_kernels.so"
 
-SOURCES = ["capi.cu", "rows.cu", "swiglu.cu", "rope_kv.cu", "embedding.cu", "flash_decode.cu", "flash_prefill.cu", "synth.cu", "dropin.cu", "selftest_static.cu"]
+SOURCES = ["capi.cu", "rows.cu", "swiglu.cu", "rope_kv.cu", "embedding.cu", "flash_decode.cu", "flash_prefill.cu", "flash_prefill_tc.cu", "synth.cu", "dropin.cu", "selftest_static.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -416,6 +416,13 @@ int launch_prefill(PfArgs a, cudaStream_t stream, const char* fn) {
 
 using namespace rh;
 
+namespace rh {
+// flash_prefill_tc.cu: the same product on the 5th-generation tensor cores (tcgen05.mma, tensor memory)
+int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const uint8_t* v, const float* k_scale,
+                            const float* v_scale, int n_new, const int* cache_len, int num_q_heads, int num_kv_heads,
+                            float scale, cudaStream_t stream, const char* fn);
+}  // namespace rh
+
 extern "C" int rh_flash_prefill_bf16(void* out, const void* q, const uint8_t* k, const uint8_t* v, const float* k_scale,
                                      const float* v_scale, int n_new, const int* cache_len, int num_q_heads,
                                      int num_kv_heads, int head_dim, float scale, void* stream) {
@@ -451,6 +458,9 @@ extern "C" int rh_flash_prefill_bf16(void* out, const void* q, const uint8_t* k,
     // short prompts do not fill the GPU with such CTAs and take the one-tile form (two CTAs per SM).
     const long long ctas_wide = static_cast<long long>((n_new + 32 * a.subs - 1) / (32 * a.subs)) * num_kv_heads * a.head_chunks;
     const int pick = host::tuning(host::kPrefillTiles);
+    if (pick == 3)
+        return launch_flash_prefill_tc(out, q, k, v, k_scale, v_scale, n_new, cache_len, num_q_heads, num_kv_heads, scale,
+                                       static_cast<cudaStream_t>(stream), fn);
     const bool wide = pick == 2 || (pick != 1 && ctas_wide >= 2LL * host::num_sms());
     return wide ? launch_prefill<2>(a, static_cast<cudaStream_t>(stream), fn)
                 : launch_prefill<1>(a, static_cast<cudaStream_t>(stream), fn);

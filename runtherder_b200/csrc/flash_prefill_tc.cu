@@ -1,0 +1,456 @@
+// Causal prefill attention over the FP8-E4M3 KV cache on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory).  Same contract as flash_prefill.cu
+// (runtherder::kernels::flash_prefill_bf16, include/runtherder/kernels/flash_prefill.cuh:27-40).
+//
+// A CTA of 128 threads owns 128 query rows of one kv head — up to four query heads x 32 (64, 128)
+// consecutive tokens — and walks the causal key tiles of 64 keys:
+//   raw E4M3 rows of the tile (cp.async, each thread its own chunks)
+//     -> f16 operand tiles in shared memory in the canonical 128-byte-swizzled layouts (exact conversion)
+//     -> S[128 x 64] = Q K^T: eight tcgen05.mma (M=128, N=64, K=16), fp32 in tensor memory
+//     -> thread t loads row t of S (tcgen05.ld 32x32b), applies the K scale, the V scale in the exponent
+//        and the causal mask, runs its online softmax without any shuffle, writes its row of weights
+//        (f16) to shared memory and rescales its row of O in tensor memory when its maximum moved
+//     -> O[128 x 128] += W V: four tcgen05.mma (M=128, N=128, K=16), V read MN-major as stored.
+// One elected thread issues the products; completion comes back through mbarriers (tcgen05.commit).
+// Every mbarrier wait is bounded and agreed on by the whole CTA (__syncthreads_or), and every path out
+// of the kernel releases the tensor memory it allocated.
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include <atomic>
+
+#include "rh_common.cuh"
+#include "rh_kernels.h"
+#include "rh_pipeline.cuh"
+
+namespace rh {
+namespace tc {
+
+constexpr int kD = 128;          // head_dim
+constexpr int kKeys = 64;        // keys per tile (N of the first product, K of the second)
+constexpr int kRows = 128;       // query rows per CTA (M)
+constexpr int kThreads = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kMInit = -1.0e30f;
+constexpr float kLgFloor = -100.0f;
+constexpr int kTmemCols = 256;   // S: 64 columns, O: 128 columns; allocations are powers of two
+constexpr int kWaitLimit = 1 << 16;   // polls; each try_wait already blocks for a while in hardware
+
+// shared-memory map, relative to a 1024-byte aligned base
+constexpr int kOffQ = 0;                        // [2 dim blocks][128 rows][128 B]   32 KB
+constexpr int kOffK = kOffQ + 2 * kRows * 128;  // [2 dim blocks][64 keys][128 B]    16 KB
+constexpr int kOffV = kOffK + 2 * kKeys * 128;  // [2 dim blocks][64 keys][128 B]    16 KB (read MN-major)
+constexpr int kOffP = kOffV + 2 * kKeys * 128;  // [128 rows][128 B]                 16 KB
+constexpr int kOffRaw = kOffP + kRows * 128;    // raw K, raw V (8 KB each), 64 + 64 scales
+constexpr int kOffCst = kOffRaw + 2 * kKeys * kD + 2 * kKeys * 4;   // ksl[64], lgv[64], rvs[64]
+constexpr int kOffBar = kOffCst + 3 * kKeys * 4;                    // two mbarriers, the tmem base
+constexpr int kSmemBytes = kOffBar + 32 + 1024;                     // + slack for the alignment
+
+struct Args {
+    __nv_bfloat16* out;
+    const __nv_bfloat16* q;
+    const uint8_t* k;
+    const uint8_t* v;
+    const float* k_scale;
+    const float* v_scale;
+    const int* cache_len;
+    int* error_word;
+    int n_new;
+    int num_q_heads;
+    int num_kv_heads;
+    int group;           // query heads per kv head
+    int heads_per_cta;   // 1, 2 or 4
+    int tokens_per_cta;  // 128 / heads_per_cta
+    int head_chunks;     // ceil(group / heads_per_cta)
+    float scale_log2e;
+};
+
+__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t word, uint32_t& lo, uint32_t& hi) {
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+        : "=r"(lo), "=r"(hi)
+        : "r"(word));
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float lg2f(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void cp16_zfill(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp4_zfill(uint32_t dst, const void* src, bool valid) {
+    const int bytes = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// generic-proxy writes to shared memory -> visible to the tensor core's (async proxy) reads
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (SBO), operand blocks
+// `lbo_bytes` apart in the leading dimension (used by the MN-major operand only).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);              // start address, 16-byte units
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;    // leading-dimension byte offset
+    d |= static_cast<uint64_t>((1024u >> 4) & 0x3FFFu) << 32;        // stride-dimension byte offset
+    d |= static_cast<uint64_t>(1) << 46;                             // descriptor version of this architecture
+    d |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: f16 x f16 -> f32, M = 128, N = n, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+    return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pipe::smem_u32(bar)) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t addr) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+// byte offset of 16-byte chunk `chunk` (0..7) of 128-byte row `row`, swizzled with the row
+__device__ __forceinline__ int swz128(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+// grid (token tiles, num_kv_heads * head_chunks), 128 threads.
+__global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Args p) {
+    extern __shared__ unsigned char raw_smem[];
+    const uint32_t base = (pipe::smem_u32(raw_smem) + 1023u) & ~1023u;          // shared-space address, 1 KB aligned
+    unsigned char* const sm = raw_smem + (base - pipe::smem_u32(raw_smem));     // the same place, generic pointer
+    uint64_t* const bar_s = reinterpret_cast<uint64_t*>(sm + kOffBar);
+    uint64_t* const bar_o = bar_s + 1;
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 16);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int kvh = blockIdx.y / p.head_chunks;
+    const int chunk = blockIdx.y - kvh * p.head_chunks;
+    const int tile = gridDim.x - 1 - blockIdx.x;            // long (late) token tiles first
+    const int tok0 = tile * p.tokens_per_cta;
+    // row tid = (head slot tid / tokens_per_cta, token tid % tokens_per_cta)
+    const int head_slot = tid / p.tokens_per_cta;
+    const int tok = tok0 + (tid - head_slot * p.tokens_per_cta);
+    const int head_in_group = chunk * p.heads_per_cta + head_slot;
+    const bool row_valid = head_in_group < p.group && tok < p.n_new;
+    const int qh = kvh * p.group + head_in_group;
+
+    // ---- one-time set-up: barriers, tensor memory ----
+    if (tid == 0) {
+        pipe::mbar_init(bar_s, 1);
+        pipe::mbar_init(bar_o, 1);
+        pipe::mbar_init_fence();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pipe::smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + kKeys;                 // column offsets
+    const uint32_t my_lane = static_cast<uint32_t>(32 * warp) << 16;     // this warp's quarter of the 128 lanes
+
+    pdl_enter();
+    const int clen = *p.cache_len;
+    const int total_keys = clen + p.n_new;
+    const int last_tok = min(tok0 + p.tokens_per_cta, p.n_new) - 1;
+    const int n_tiles = min((total_keys + kKeys - 1) / kKeys, (clen + last_tok) / kKeys + 1);
+    const int qpos = clen + tok;
+
+    // ---- raw tile copies: thread t owns chunks t, t+128, ... (eight consecutive keys per quarter-warp) ----
+    const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kD;
+    auto issue_raw = [&](int j) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int id = tid + i * kThreads, which = id >> 9, ch = (id >> 6) & 7, key_l = id & 63;
+            const int key = j * kKeys + key_l;
+            const bool live = key < total_keys;
+            const uint8_t* src = (which ? p.v : p.k) + (live ? static_cast<size_t>(key) * row_stride + static_cast<size_t>(kvh) * kD + ch * 16 : 0);
+            cp16_zfill(base + kOffRaw + which * (kKeys * kD) + swz128(key_l, ch), src, live);
+        }
+        if (tid < kKeys) {
+            const int key = j * kKeys + tid;
+            const bool live = key < total_keys;
+            const size_t idx = live ? static_cast<size_t>(key) * p.num_kv_heads + kvh : 0;
+            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + tid * 4, p.k_scale + idx, live);
+            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + kKeys * 4 + tid * 4, p.v_scale + idx, live);
+        }
+        cp_async_commit();
+    };
+    // E4M3 -> f16 into the operand tiles: [dim block of 64][key][128 bytes, swizzled]; K and V share the form
+    // (K is consumed K-major: a row is a key; V MN-major: the 128 bytes of a row are 64 consecutive dims)
+    auto convert = [&]() {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int id = tid + i * kThreads, which = id >> 9, ch = (id >> 6) & 7, key_l = id & 63;
+            const uint4 w = *reinterpret_cast<const uint4*>(sm + kOffRaw + which * (kKeys * kD) + swz128(key_l, ch));
+            uint4 h0, h1;
+            e4m3x4_to_f16x2x2(w.x, h0.x, h0.y);
+            e4m3x4_to_f16x2x2(w.y, h0.z, h0.w);
+            e4m3x4_to_f16x2x2(w.z, h1.x, h1.y);
+            e4m3x4_to_f16x2x2(w.w, h1.z, h1.w);
+            unsigned char* const dst = sm + (which ? kOffV : kOffK) + (ch >> 2) * (kKeys * 128);
+            *reinterpret_cast<uint4*>(dst + swz128(key_l, 2 * (ch & 3))) = h0;
+            *reinterpret_cast<uint4*>(dst + swz128(key_l, 2 * (ch & 3) + 1)) = h1;
+        }
+        if (tid < kKeys) {
+            const float* const sc = reinterpret_cast<const float*>(sm + kOffRaw + 2 * kKeys * kD);
+            float* const cst = reinterpret_cast<float*>(sm + kOffCst);
+            const float lg = fmaxf(lg2f(sc[kKeys + tid]), kLgFloor);
+            cst[tid] = sc[tid] * p.scale_log2e;
+            cst[kKeys + tid] = lg;
+            cst[2 * kKeys + tid] = ex2f(-lg);
+        }
+    };
+    issue_raw(0);
+
+    // ---- Q: row tid, bf16 -> f16, [dim block][row][128 bytes, swizzled] ----
+    {
+        const __nv_bfloat16* src = p.q + (static_cast<size_t>(row_valid ? tok : 0) * p.num_q_heads + (row_valid ? qh : 0)) * kD;
+#pragma unroll
+        for (int cidx = 0; cidx < 16; ++cidx) {
+            uint4 w = make_uint4(0u, 0u, 0u, 0u);
+            if (row_valid) w = *reinterpret_cast<const uint4*>(src + cidx * 8);
+            uint4 h;
+            h.x = pack_f16x2(bf_lo(w.x), bf_hi(w.x));
+            h.y = pack_f16x2(bf_lo(w.y), bf_hi(w.y));
+            h.z = pack_f16x2(bf_lo(w.z), bf_hi(w.z));
+            h.w = pack_f16x2(bf_lo(w.w), bf_hi(w.w));
+            *reinterpret_cast<uint4*>(sm + kOffQ + (cidx >> 3) * (kRows * 128) + swz128(tid, cidx & 7)) = h;
+        }
+    }
+
+    constexpr uint32_t kIdescQK = instr_desc(kKeys, false);
+    constexpr uint32_t kIdescPV = instr_desc(kD, true);
+    float m_run = kMInit, l_run = 0.0f;
+    bool failed = false;
+
+    for (int j = 0; j < n_tiles && !failed; ++j) {
+        cp_async_wait<0>();                                      // this thread's raw chunks of tile j
+        if (j > 0) {                                             // the products of tile j-1 are done with K, V, W
+            const bool ok = pipe::mbar_wait(bar_o, (j - 1) & 1, __LINE__, p.error_word, kWaitLimit);
+            tc_fence_after();
+            if (!ok) failed = true;
+        }
+        convert();
+        if (j + 1 < n_tiles) issue_raw(j + 1);                   // this thread's chunks only: no barrier needed
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(failed)) { failed = true; break; }
+
+        // ---- S = Q K^T ----
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int s = 0; s < kD / 16; ++s) {
+                const uint32_t off = (s >> 2) * (kRows * 128) + (s & 3) * 32;
+                const uint32_t koff = (s >> 2) * (kKeys * 128) + (s & 3) * 32;
+                umma_f16(tmem_s, smem_desc(base + kOffQ + off, 16), smem_desc(base + kOffK + koff, 16), kIdescQK, s > 0);
+            }
+            umma_commit(bar_s);
+        }
+        {
+            const bool ok = pipe::mbar_wait(bar_s, j & 1, __LINE__, p.error_word, kWaitLimit);
+            tc_fence_after();
+            if (!ok) failed = true;
+        }
+
+        // ---- row tid: scores, mask, online softmax, weights ----
+        const float* const cst = reinterpret_cast<const float*>(sm + kOffCst);
+        const bool diag = j * kKeys + kKeys - 1 > qpos;
+        float sv[2][32];
+        tmem_ld32(sv[0], tmem_s + my_lane);
+        tmem_ld32(sv[1], tmem_s + my_lane + 32);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                const float4 kk = *reinterpret_cast<const float4*>(cst + 32 * h + i);
+                const float4 lg = *reinterpret_cast<const float4*>(cst + kKeys + 32 * h + i);
+                sv[h][i] = fmaf(sv[h][i], kk.x, lg.x);
+                sv[h][i + 1] = fmaf(sv[h][i + 1], kk.y, lg.y);
+                sv[h][i + 2] = fmaf(sv[h][i + 2], kk.z, lg.z);
+                sv[h][i + 3] = fmaf(sv[h][i + 3], kk.w, lg.w);
+                if (diag) {
+                    const int kpos = j * kKeys + 32 * h + i;
+                    if (kpos > qpos) sv[h][i] = -INFINITY;
+                    if (kpos + 1 > qpos) sv[h][i + 1] = -INFINITY;
+                    if (kpos + 2 > qpos) sv[h][i + 2] = -INFINITY;
+                    if (kpos + 3 > qpos) sv[h][i + 3] = -INFINITY;
+                }
+                mx = fmaxf(mx, fmaxf(fmaxf(sv[h][i], sv[h][i + 1]), fmaxf(sv[h][i + 2], sv[h][i + 3])));
+            }
+        const float m_new = fmaxf(m_run, mx);
+        const float corr = ex2f(m_run - m_new);
+        m_run = m_new;
+        float sum = 0.0f;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                uint4 w;
+                float e[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) e[u] = ex2f(sv[h][i + u] - m_new);
+                const float4 r0 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + 32 * h + i);
+                const float4 r1 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + 32 * h + i + 4);
+                sum = fmaf(e[0], r0.x, fmaf(e[1], r0.y, fmaf(e[2], r0.z, fmaf(e[3], r0.w, sum))));
+                sum = fmaf(e[4], r1.x, fmaf(e[5], r1.y, fmaf(e[6], r1.z, fmaf(e[7], r1.w, sum))));
+                w.x = pack_f16x2(e[0], e[1]);
+                w.y = pack_f16x2(e[2], e[3]);
+                w.z = pack_f16x2(e[4], e[5]);
+                w.w = pack_f16x2(e[6], e[7]);
+                *reinterpret_cast<uint4*>(sm + kOffP + swz128(tid, (32 * h + i) >> 3)) = w;
+            }
+        l_run = fmaf(l_run, corr, sum);
+        // O row rescale (the products of tile j-1 completed before this tile's conversion)
+        if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+            for (int cb = 0; cb < kD; cb += 32) {
+                float ov[32];
+                tmem_ld32(ov, tmem_o + my_lane + cb);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) ov[i] *= corr;
+                tmem_st32(tmem_o + my_lane + cb, ov);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(failed)) { failed = true; break; }
+
+        // ---- O += W V ----
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int s = 0; s < kKeys / 16; ++s)
+                umma_f16(tmem_o, smem_desc(base + kOffP + s * 32, 16), smem_desc(base + kOffV + s * 2048, kKeys * 128), kIdescPV,
+                         j > 0 || s > 0);
+            umma_commit(bar_o);
+        }
+    }
+
+    // ---- epilogue: normalise, store; every path releases the tensor memory ----
+    if (!failed && n_tiles > 0) {
+        const bool ok = pipe::mbar_wait(bar_o, (n_tiles - 1) & 1, __LINE__, p.error_word, kWaitLimit);
+        tc_fence_after();
+        if (!ok) failed = true;
+    }
+    if (!__syncthreads_or(failed) && n_tiles > 0) {
+        const float inv = 1.0f / l_run;
+        __nv_bfloat16* const dst = p.out + (static_cast<size_t>(row_valid ? tok : 0) * p.num_q_heads + (row_valid ? qh : 0)) * kD;
+#pragma unroll 1
+        for (int cb = 0; cb < kD; cb += 32) {
+            float ov[32];
+            tmem_ld32(ov, tmem_o + my_lane + cb);
+            if (row_valid) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 w;
+                    __nv_bfloat162 t;
+                    t = __floats2bfloat162_rn(ov[i] * inv, ov[i + 1] * inv); w.x = *reinterpret_cast<uint32_t*>(&t);
+                    t = __floats2bfloat162_rn(ov[i + 2] * inv, ov[i + 3] * inv); w.y = *reinterpret_cast<uint32_t*>(&t);
+                    t = __floats2bfloat162_rn(ov[i + 4] * inv, ov[i + 5] * inv); w.z = *reinterpret_cast<uint32_t*>(&t);
+                    t = __floats2bfloat162_rn(ov[i + 6] * inv, ov[i + 7] * inv); w.w = *reinterpret_cast<uint32_t*>(&t);
+                    *reinterpret_cast<uint4*>(dst + cb + i) = w;
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace tc
+
+// Launcher used by rh_flash_prefill_bf16 when the tensor-memory form is selected.
+int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const uint8_t* v, const float* k_scale,
+                            const float* v_scale, int n_new, const int* cache_len, int num_q_heads, int num_kv_heads,
+                            float scale, cudaStream_t stream, const char* fn) {
+    tc::Args a;
+    a.out = static_cast<__nv_bfloat16*>(out);
+    a.q = static_cast<const __nv_bfloat16*>(q);
+    a.k = k;
+    a.v = v;
+    a.k_scale = k_scale;
+    a.v_scale = v_scale;
+    a.cache_len = cache_len;
+    a.error_word = host::device_error_word();
+    a.n_new = n_new;
+    a.num_q_heads = num_q_heads;
+    a.num_kv_heads = num_kv_heads;
+    a.group = num_q_heads / num_kv_heads;
+    a.heads_per_cta = a.group >= 3 ? 4 : a.group;          // 3 heads ride in a 4-slot tile (one idle)
+    a.tokens_per_cta = tc::kRows / a.heads_per_cta;
+    a.head_chunks = (a.group + a.heads_per_cta - 1) / a.heads_per_cta;
+    a.scale_log2e = scale * tc::kLog2e;
+    {
+        static std::atomic<unsigned> configured{0};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const unsigned bit = 1u << (dev & 31);
+        if ((configured.load(std::memory_order_relaxed) & bit) == 0) {
+            cudaFuncSetAttribute(reinterpret_cast<const void*>(&tc::flash_prefill_tc_kernel),
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes);
+            configured.fetch_or(bit, std::memory_order_relaxed);
+        }
+    }
+    const dim3 grid(static_cast<unsigned>((n_new + a.tokens_per_cta - 1) / a.tokens_per_cta),
+                    static_cast<unsigned>(num_kv_heads * a.head_chunks));
+    RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
+    host::launch(tc::flash_prefill_tc_kernel, grid, dim3(tc::kThreads), static_cast<size_t>(tc::kSmemBytes), stream, a);
+    return host::check_launch(fn);
+}
+
+}  // namespace rh
