@@ -183,7 +183,7 @@ extern "C" int rh_tune(const char* key, int value) {
                                                          "rope_warps_per_cta", "embed_ctas_per_sm",
                                                          "elem_ctas_per_sm", "swiglu_threads",
                                                          "swiglu_rcp_steps", "rows_stages", "swiglu_stages",
-                                                         "rows_smem_h", "rows_prefetch", "swiglu_prefetch", "no_pdl", "prefill_tiles"};
+                                                         "rows_smem_h", "rows_prefetch", "swiglu_prefetch", "no_pdl", "prefill_tiles", "prefill_parts"};
     RH_REQUIRE(key != nullptr, RH_ERR_INVALID_ARG, "rh_tune: null key");
     for (int i = 0; i < host::kTuneSlots; ++i) {
         if (std::strcmp(key, kNames[i]) == 0) {

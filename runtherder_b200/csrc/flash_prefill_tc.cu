@@ -2,14 +2,16 @@
 // (tcgen05.mma, accumulators in tensor memory).  Same contract as flash_prefill.cu
 // (runtherder::kernels::flash_prefill_bf16, include/runtherder/kernels/flash_prefill.cuh:27-40).
 //
-// A CTA of 128 threads owns 128 query rows of one kv head — up to four query heads x 32 (64, 128)
-// consecutive tokens — and walks the causal key tiles of 64 keys:
+// A CTA owns 128 query rows of one kv head — up to four query heads x 32 (64, 128) consecutive tokens —
+// and walks the causal key tiles of 64 keys with 128 x kParts threads (kParts threads share a row: each
+// takes 64 / kParts keys of the row's scores and 128 / kParts columns of its output):
 //   raw E4M3 rows of the tile (cp.async, each thread its own chunks)
 //     -> f16 operand tiles in shared memory in the canonical 128-byte-swizzled layouts (exact conversion)
 //     -> S[128 x 64] = Q K^T: eight tcgen05.mma (M=128, N=64, K=16), fp32 in tensor memory
-//     -> thread t loads row t of S (tcgen05.ld 32x32b), applies the K scale, the V scale in the exponent
-//        and the causal mask, runs its online softmax without any shuffle, writes its row of weights
-//        (f16) to shared memory and rescales its row of O in tensor memory when its maximum moved
+//     -> the threads of row r load their part of S row r (tcgen05.ld 32x32b), apply the K scale, the V scale
+//        in the exponent and the causal mask, agree on the row maximum through shared memory (a named
+//        barrier per 32-row quarter), write their weights (f16) to shared memory and rescale their columns
+//        of O in tensor memory when the running maximum moved
 //     -> O[128 x 128] += W V: four tcgen05.mma (M=128, N=128, K=16), V read MN-major as stored.
 // One elected thread issues the products; completion comes back through mbarriers (tcgen05.commit).
 // Every mbarrier wait is bounded and agreed on by the whole CTA (__syncthreads_or), and every path out
@@ -29,7 +31,6 @@ namespace tc {
 constexpr int kD = 128;          // head_dim
 constexpr int kKeys = 64;        // keys per tile (N of the first product, K of the second)
 constexpr int kRows = 128;       // query rows per CTA (M)
-constexpr int kThreads = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMInit = -1.0e30f;
 constexpr float kLgFloor = -100.0f;
@@ -43,7 +44,8 @@ constexpr int kOffV = kOffK + 2 * kKeys * 128;  // [2 dim blocks][64 keys][128 B
 constexpr int kOffP = kOffV + 2 * kKeys * 128;  // [128 rows][128 B]                 16 KB
 constexpr int kOffRaw = kOffP + kRows * 128;    // raw K, raw V (8 KB each), 64 + 64 scales
 constexpr int kOffCst = kOffRaw + 2 * kKeys * kD + 2 * kKeys * 4;   // ksl[64], lgv[64], rvs[64]
-constexpr int kOffBar = kOffCst + 3 * kKeys * 4;                    // two mbarriers, the tmem base
+constexpr int kOffXch = kOffCst + 3 * kKeys * 4;                    // row maxima / sums exchanged between a row's threads: [4][128]
+constexpr int kOffBar = kOffXch + 4 * kRows * 4;                    // two mbarriers, the tmem base
 constexpr int kSmemBytes = kOffBar + 32 + 1024;                     // + slack for the alignment
 
 struct Args {
@@ -123,7 +125,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pipe::smem_u32(bar)) : "memory");
 }
 // 32 consecutive fp32 columns of this thread's tensor-memory lane
-__device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t addr) {
+__device__ __forceinline__ void tmem_ld32(float* v, uint32_t addr) {
     uint32_t r[32];
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -139,7 +141,7 @@ __device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t addr) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const float* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -155,26 +157,57 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
           "r"(__float_as_uint(v[31]))
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(float* v, uint32_t addr) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <int kN>
+__device__ __forceinline__ void tmem_ld(float* v, uint32_t addr) {
+    static_assert(kN == 16 || kN == 32 || kN == 64, "columns per thread");
+    if constexpr (kN == 16) {
+        tmem_ld16(v, addr);
+    } else {
+#pragma unroll
+        for (int c = 0; c < kN; c += 32) tmem_ld32(v + c, addr + c);
+    }
+}
+// barrier among the `count` threads that share named barrier `id`
+__device__ __forceinline__ void named_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 // byte offset of 16-byte chunk `chunk` (0..7) of 128-byte row `row`, swizzled with the row
 __device__ __forceinline__ int swz128(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
-// grid (token tiles, num_kv_heads * head_chunks), 128 threads.
-__global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Args p) {
+// grid (token tiles, num_kv_heads * head_chunks), 128 * kParts threads.
+template <int kParts>
+__global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const Args p) {
+    constexpr int kThreads = 128 * kParts;
+    constexpr int kC = kKeys / kParts;       // score columns per thread
+    constexpr int kOC = kD / kParts;         // output columns per thread
     extern __shared__ unsigned char raw_smem[];
     const uint32_t base = (pipe::smem_u32(raw_smem) + 1023u) & ~1023u;          // shared-space address, 1 KB aligned
     unsigned char* const sm = raw_smem + (base - pipe::smem_u32(raw_smem));     // the same place, generic pointer
     uint64_t* const bar_s = reinterpret_cast<uint64_t*>(sm + kOffBar);
     uint64_t* const bar_o = bar_s + 1;
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(sm + kOffBar + 16);
+    float* const xch = reinterpret_cast<float*>(sm + kOffXch);
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    const int row = tid & (kRows - 1), part = tid >> 7;     // warp w reaches tensor-memory lanes 32 (w % 4) ..
     const int kvh = blockIdx.y / p.head_chunks;
     const int chunk = blockIdx.y - kvh * p.head_chunks;
     const int tile = gridDim.x - 1 - blockIdx.x;            // long (late) token tiles first
     const int tok0 = tile * p.tokens_per_cta;
-    // row tid = (head slot tid / tokens_per_cta, token tid % tokens_per_cta)
-    const int head_slot = tid / p.tokens_per_cta;
-    const int tok = tok0 + (tid - head_slot * p.tokens_per_cta);
+    // row = (head slot row / tokens_per_cta, token row % tokens_per_cta)
+    const int head_slot = row / p.tokens_per_cta;
+    const int tok = tok0 + (row - head_slot * p.tokens_per_cta);
     const int head_in_group = chunk * p.heads_per_cta + head_slot;
     const bool row_valid = head_in_group < p.group && tok < p.n_new;
     const int qh = kvh * p.group + head_in_group;
@@ -193,8 +226,8 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Arg
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + kKeys;                 // column offsets
-    const uint32_t my_lane = static_cast<uint32_t>(32 * warp) << 16;     // this warp's quarter of the 128 lanes
+    const uint32_t tmem_s = tmem, tmem_o = tmem + kKeys;                       // column offsets
+    const uint32_t my_lane = static_cast<uint32_t>(32 * (warp & 3)) << 16;     // this warp's quarter of the 128 lanes
 
     pdl_enter();
     const int clen = *p.cache_len;
@@ -203,11 +236,11 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Arg
     const int n_tiles = min((total_keys + kKeys - 1) / kKeys, (clen + last_tok) / kKeys + 1);
     const int qpos = clen + tok;
 
-    // ---- raw tile copies: thread t owns chunks t, t+128, ... (eight consecutive keys per quarter-warp) ----
+    // ---- raw tile copies: thread t owns chunks t, t + kThreads, ... (eight consecutive keys per quarter-warp) ----
     const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kD;
     auto issue_raw = [&](int j) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 1024 / kThreads; ++i) {
             const int id = tid + i * kThreads, which = id >> 9, ch = (id >> 6) & 7, key_l = id & 63;
             const int key = j * kKeys + key_l;
             const bool live = key < total_keys;
@@ -227,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Arg
     // (K is consumed K-major: a row is a key; V MN-major: the 128 bytes of a row are 64 consecutive dims)
     auto convert = [&]() {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 1024 / kThreads; ++i) {
             const int id = tid + i * kThreads, which = id >> 9, ch = (id >> 6) & 7, key_l = id & 63;
             const uint4 w = *reinterpret_cast<const uint4*>(sm + kOffRaw + which * (kKeys * kD) + swz128(key_l, ch));
             uint4 h0, h1;
@@ -250,11 +283,12 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Arg
     };
     issue_raw(0);
 
-    // ---- Q: row tid, bf16 -> f16, [dim block][row][128 bytes, swizzled] ----
+    // ---- Q: row `row`, this thread's 16 / kParts chunks, bf16 -> f16, [dim block][row][128 bytes, swizzled] ----
     {
         const __nv_bfloat16* src = p.q + (static_cast<size_t>(row_valid ? tok : 0) * p.num_q_heads + (row_valid ? qh : 0)) * kD;
 #pragma unroll
-        for (int cidx = 0; cidx < 16; ++cidx) {
+        for (int c = 0; c < 16 / kParts; ++c) {
+            const int cidx = part * (16 / kParts) + c;
             uint4 w = make_uint4(0u, 0u, 0u, 0u);
             if (row_valid) w = *reinterpret_cast<const uint4*>(src + cidx * 8);
             uint4 h;
@@ -262,13 +296,13 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Arg
             h.y = pack_f16x2(bf_lo(w.y), bf_hi(w.y));
             h.z = pack_f16x2(bf_lo(w.z), bf_hi(w.z));
             h.w = pack_f16x2(bf_lo(w.w), bf_hi(w.w));
-            *reinterpret_cast<uint4*>(sm + kOffQ + (cidx >> 3) * (kRows * 128) + swz128(tid, cidx & 7)) = h;
+            *reinterpret_cast<uint4*>(sm + kOffQ + (cidx >> 3) * (kRows * 128) + swz128(row, cidx & 7)) = h;
         }
     }
 
     constexpr uint32_t kIdescQK = instr_desc(kKeys, false);
     constexpr uint32_t kIdescPV = instr_desc(kD, true);
-    float m_run = kMInit, l_run = 0.0f;
+    float m_run = kMInit, l_run = 0.0f;      // m_run is the same in all threads of a row; l_run is this thread's part
     bool failed = false;
 
     for (int j = 0; j < n_tiles && !failed; ++j) {
@@ -301,64 +335,70 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Arg
             if (!ok) failed = true;
         }
 
-        // ---- row tid: scores, mask, online softmax, weights ----
-        const float* const cst = reinterpret_cast<const float*>(sm + kOffCst);
+        // ---- this thread's kC scores of its row: scales, mask, maximum ----
+        const float* const cst = reinterpret_cast<const float*>(sm + kOffCst) + part * kC;
+        const int key0 = j * kKeys + part * kC;
         const bool diag = j * kKeys + kKeys - 1 > qpos;
-        float sv[2][32];
-        tmem_ld32(sv[0], tmem_s + my_lane);
-        tmem_ld32(sv[1], tmem_s + my_lane + 32);
+        float sv[kC];
+        tmem_ld<kC>(sv, tmem_s + my_lane + part * kC);
         float mx = -INFINITY;
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                const float4 kk = *reinterpret_cast<const float4*>(cst + 32 * h + i);
-                const float4 lg = *reinterpret_cast<const float4*>(cst + kKeys + 32 * h + i);
-                sv[h][i] = fmaf(sv[h][i], kk.x, lg.x);
-                sv[h][i + 1] = fmaf(sv[h][i + 1], kk.y, lg.y);
-                sv[h][i + 2] = fmaf(sv[h][i + 2], kk.z, lg.z);
-                sv[h][i + 3] = fmaf(sv[h][i + 3], kk.w, lg.w);
-                if (diag) {
-                    const int kpos = j * kKeys + 32 * h + i;
-                    if (kpos > qpos) sv[h][i] = -INFINITY;
-                    if (kpos + 1 > qpos) sv[h][i + 1] = -INFINITY;
-                    if (kpos + 2 > qpos) sv[h][i + 2] = -INFINITY;
-                    if (kpos + 3 > qpos) sv[h][i + 3] = -INFINITY;
-                }
-                mx = fmaxf(mx, fmaxf(fmaxf(sv[h][i], sv[h][i + 1]), fmaxf(sv[h][i + 2], sv[h][i + 3])));
+        for (int i = 0; i < kC; i += 4) {
+            const float4 kk = *reinterpret_cast<const float4*>(cst + i);
+            const float4 lg = *reinterpret_cast<const float4*>(cst + kKeys + i);
+            sv[i] = fmaf(sv[i], kk.x, lg.x);
+            sv[i + 1] = fmaf(sv[i + 1], kk.y, lg.y);
+            sv[i + 2] = fmaf(sv[i + 2], kk.z, lg.z);
+            sv[i + 3] = fmaf(sv[i + 3], kk.w, lg.w);
+            if (diag) {
+                const int kpos = key0 + i;
+                if (kpos > qpos) sv[i] = -INFINITY;
+                if (kpos + 1 > qpos) sv[i + 1] = -INFINITY;
+                if (kpos + 2 > qpos) sv[i + 2] = -INFINITY;
+                if (kpos + 3 > qpos) sv[i + 3] = -INFINITY;
             }
+            mx = fmaxf(mx, fmaxf(fmaxf(sv[i], sv[i + 1]), fmaxf(sv[i + 2], sv[i + 3])));
+        }
+        if constexpr (kParts > 1) {          // the row's threads sit in warps w, w + 4, ...: one named barrier per quarter
+            xch[part * kRows + row] = mx;
+            named_sync(1 + (warp & 3), 32 * kParts);
+#pragma unroll
+            for (int q = 0; q < kParts; ++q) mx = fmaxf(mx, xch[q * kRows + row]);
+        }
+        // The reference follows the maximum exactly: the largest weight of a row is then exactly 1 in f16,
+        // so a row dominated by one key keeps its weight-to-sum ratio free of f16 rounding.  (A reference
+        // that lags the maximum by a threshold saves most rescales of O but rounds the dominant weight:
+        // measured, two-ulp outputs on inputs with widely spread V scales.)
         const float m_new = fmaxf(m_run, mx);
         const float corr = ex2f(m_run - m_new);
         m_run = m_new;
         float sum = 0.0f;
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int i = 0; i < kC; i += 8) {
+            uint4 w;
+            float e[8];
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-                uint4 w;
-                float e[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) e[u] = ex2f(sv[h][i + u] - m_new);
-                const float4 r0 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + 32 * h + i);
-                const float4 r1 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + 32 * h + i + 4);
-                sum = fmaf(e[0], r0.x, fmaf(e[1], r0.y, fmaf(e[2], r0.z, fmaf(e[3], r0.w, sum))));
-                sum = fmaf(e[4], r1.x, fmaf(e[5], r1.y, fmaf(e[6], r1.z, fmaf(e[7], r1.w, sum))));
-                w.x = pack_f16x2(e[0], e[1]);
-                w.y = pack_f16x2(e[2], e[3]);
-                w.z = pack_f16x2(e[4], e[5]);
-                w.w = pack_f16x2(e[6], e[7]);
-                *reinterpret_cast<uint4*>(sm + kOffP + swz128(tid, (32 * h + i) >> 3)) = w;
-            }
+            for (int u = 0; u < 8; ++u) e[u] = ex2f(sv[i + u] - m_new);
+            const float4 r0 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + i);
+            const float4 r1 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + i + 4);
+            sum = fmaf(e[0], r0.x, fmaf(e[1], r0.y, fmaf(e[2], r0.z, fmaf(e[3], r0.w, sum))));
+            sum = fmaf(e[4], r1.x, fmaf(e[5], r1.y, fmaf(e[6], r1.z, fmaf(e[7], r1.w, sum))));
+            w.x = pack_f16x2(e[0], e[1]);
+            w.y = pack_f16x2(e[2], e[3]);
+            w.z = pack_f16x2(e[4], e[5]);
+            w.w = pack_f16x2(e[6], e[7]);
+            *reinterpret_cast<uint4*>(sm + kOffP + swz128(row, (part * kC + i) >> 3)) = w;
+        }
         l_run = fmaf(l_run, corr, sum);
-        // O row rescale (the products of tile j-1 completed before this tile's conversion)
+        // this thread's columns of the O row (the products of tile j-1 completed before this tile's conversion)
         if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-            for (int cb = 0; cb < kD; cb += 32) {
+            for (int cb = 0; cb < kOC; cb += 32) {
                 float ov[32];
-                tmem_ld32(ov, tmem_o + my_lane + cb);
+                tmem_ld32(ov, tmem_o + my_lane + part * kOC + cb);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) ov[i] *= corr;
-                tmem_st32(tmem_o + my_lane + cb, ov);
+                tmem_st32(tmem_o + my_lane + part * kOC + cb, ov);
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
@@ -383,13 +423,20 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_tc_kernel(const Arg
         tc_fence_after();
         if (!ok) failed = true;
     }
+    if constexpr (kParts > 1) xch[part * kRows + row] = l_run;     // last read of xch was before the loop's final barrier
     if (!__syncthreads_or(failed) && n_tiles > 0) {
-        const float inv = 1.0f / l_run;
-        __nv_bfloat16* const dst = p.out + (static_cast<size_t>(row_valid ? tok : 0) * p.num_q_heads + (row_valid ? qh : 0)) * kD;
+        float l_row = l_run;
+        if constexpr (kParts > 1) {
+            l_row = 0.0f;
+#pragma unroll
+            for (int q = 0; q < kParts; ++q) l_row += xch[q * kRows + row];
+        }
+        const float inv = 1.0f / l_row;
+        __nv_bfloat16* const dst = p.out + (static_cast<size_t>(row_valid ? tok : 0) * p.num_q_heads + (row_valid ? qh : 0)) * kD + part * kOC;
 #pragma unroll 1
-        for (int cb = 0; cb < kD; cb += 32) {
+        for (int cb = 0; cb < kOC; cb += 32) {
             float ov[32];
-            tmem_ld32(ov, tmem_o + my_lane + cb);
+            tmem_ld32(ov, tmem_o + my_lane + part * kOC + cb);
             if (row_valid) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
@@ -435,21 +482,25 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     a.tokens_per_cta = tc::kRows / a.heads_per_cta;
     a.head_chunks = (a.group + a.heads_per_cta - 1) / a.heads_per_cta;
     a.scale_log2e = scale * tc::kLog2e;
-    {
-        static std::atomic<unsigned> configured{0};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        const unsigned bit = 1u << (dev & 31);
-        if ((configured.load(std::memory_order_relaxed) & bit) == 0) {
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(&tc::flash_prefill_tc_kernel),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes);
-            configured.fetch_or(bit, std::memory_order_relaxed);
-        }
-    }
     const dim3 grid(static_cast<unsigned>((n_new + a.tokens_per_cta - 1) / a.tokens_per_cta),
                     static_cast<unsigned>(num_kv_heads * a.head_chunks));
     RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
-    host::launch(tc::flash_prefill_tc_kernel, grid, dim3(tc::kThreads), static_cast<size_t>(tc::kSmemBytes), stream, a);
+    const int parts = host::tuning(host::kPrefillParts);
+    auto go = [&](auto kernel, int threads) {
+        static std::atomic<unsigned> configured[3];      // per kernel form: the devices already set up
+        std::atomic<unsigned>& done = configured[threads >> 8];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        const unsigned bit = 1u << (dev & 31);
+        if ((done.load(std::memory_order_relaxed) & bit) == 0) {
+            cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes);
+            done.fetch_or(bit, std::memory_order_relaxed);
+        }
+        host::launch(kernel, grid, dim3(threads), static_cast<size_t>(tc::kSmemBytes), stream, a);
+    };
+    if (parts == 1) go(tc::flash_prefill_tc_kernel<1>, 128);
+    else if (parts == 4) go(tc::flash_prefill_tc_kernel<4>, 512);
+    else go(tc::flash_prefill_tc_kernel<2>, 256);
     return host::check_launch(fn);
 }
 

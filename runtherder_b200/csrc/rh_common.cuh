@@ -290,7 +290,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kSwigluThreads,
                 kSwigluRcpSteps, kRowsStages, kSwigluStages, kRowsSmemH, kRowsPrefetch,
-                kSwigluPrefetch, kNoPdl, kPrefillTiles, kTuneSlots };
+                kSwigluPrefetch, kNoPdl, kPrefillTiles, kPrefillParts, kTuneSlots };
 
 // Launches `kernel` with the programmatic-stream-serialization attribute (unless rh_tune("no_pdl", 1)):
 // the kernel may be scheduled while the previous kernel of `stream` drains; it orders itself with

@@ -93,12 +93,17 @@ def test_flash_prefill_matches_exact_attention_and_reference(orc, ref, n_new, ca
     cl = torch.tensor([cache_len], dtype=torch.int32, device="cuda")
     outs = {}
     try:
-        for tiles in (1, 2, 3):    # 16 or 32 query rows per warp (mma.sync), 128 rows per CTA in tensor memory (tcgen05)
+        # 16 or 32 query rows per warp (mma.sync); 128 rows per CTA in tensor memory (tcgen05) with 1, 2 or 4
+        # threads sharing a row
+        for tiles, parts in ((1, 0), (2, 0), (3, 1), (3, 2), (3, 4)):
             K.tune("prefill_tiles", tiles)
-            outs[tiles] = torch.full((n_new, Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
-            K.flash_prefill_bf16(outs[tiles], q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
+            K.tune("prefill_parts", parts)
+            key = tiles if tiles < 3 else 10 * tiles + parts
+            outs[key] = torch.full((n_new, Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+            K.flash_prefill_bf16(outs[key], q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
     finally:
         K.tune("prefill_tiles", 0)
+        K.tune("prefill_parts", 0)
     out = outs[1]
     out_naive, out_flash = torch.empty_like(out), torch.empty_like(out)
     ref.attention_causal_bf16(out_naive, q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
@@ -107,7 +112,8 @@ def test_flash_prefill_matches_exact_attention_and_reference(orc, ref, n_new, ca
     exact_bits, exact = orc.attention_causal_fp8(to_np(q), to_np(kc), to_np(vc), to_np(ks), to_np(vs), cache_len, scale)
     check(outs[1], exact_bits, exact, "this library, 16 rows per warp")
     check(outs[2], exact_bits, exact, "this library, 32 rows per warp")
-    check(outs[3], exact_bits, exact, "this library, tensor-memory form")
+    for parts in (1, 2, 4):
+        check(outs[30 + parts], exact_bits, exact, f"this library, tensor-memory form, {parts} thread(s) per row")
     check(out_naive, exact_bits, exact, "reference naive kernel", significance=64)
     a, b = out_naive.float().flatten(), out.float().flatten()
     if flavour != "spread":
