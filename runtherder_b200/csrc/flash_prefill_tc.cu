@@ -35,6 +35,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMInit = -1.0e30f;
 constexpr float kLgFloor = -100.0f;
 constexpr int kTmemCols = 256;   // S: 64 columns, O: 128 columns; allocations are powers of two
+constexpr uint32_t kSuspendNs = 20000;   // longest hardware sleep per mbarrier try
 constexpr int kWaitLimit = 1 << 16;   // polls; each try_wait already blocks for a while in hardware
 
 // shared-memory map, relative to a 1024-byte aligned base
@@ -93,6 +94,24 @@ __device__ __forceinline__ void cp16_zfill(uint32_t dst, const void* src, bool v
 __device__ __forceinline__ void cp4_zfill(uint32_t dst, const void* src, bool valid) {
     const int bytes = valid ? 4 : 0;
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+// Bounded wait on an mbarrier phase.  The suspend-time hint lets a waiting thread sleep in hardware up to
+// that long per try instead of polling, so waiting warps leave the issue slots to the warps with work.
+__device__ __forceinline__ bool mbar_wait_quiet(uint64_t* bar, uint32_t parity, int where, int* error_word) {
+    const uint32_t addr = pipe::smem_u32(bar);
+    for (int i = 0; i < kWaitLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity), "r"(kSuspendNs)
+            : "memory");
+        if (ok != 0) return true;
+    }
+    if (error_word != nullptr) atomicCAS(error_word, 0, (where << 8) | 1);
+    return false;
 }
 // generic-proxy writes to shared memory -> visible to the tensor core's (async proxy) reads
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -236,42 +255,73 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
     const int n_tiles = min((total_keys + kKeys - 1) / kKeys, (clen + last_tok) / kKeys + 1);
     const int qpos = clen + tok;
 
-    // ---- raw tile copies: thread t owns chunks t, t + kThreads, ... (eight consecutive keys per quarter-warp) ----
+    // ---- raw tile copies and conversion: thread t owns key t % 64 and the 16-byte chunks c0, c0 + kStep, ...
+    //      of its K row and of its V row (eight consecutive keys per quarter-warp: conflict-free both ways).
+    //      Every shared-memory offset is fixed per thread; the global pointers advance by one tile per step.
+    constexpr uint32_t kIdescQK = instr_desc(kKeys, false);
+    constexpr uint32_t kIdescPV = instr_desc(kD, true);
+    constexpr int kStep = kThreads / 64;     // chunk stride between this thread's chunks of a row
+    constexpr int kNch = 8 / kStep;          // chunks per row and matrix
+    const int key_l = tid & 63, c0 = tid >> 6;
     const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kD;
-    auto issue_raw = [&](int j) {
+    const size_t head_off = static_cast<size_t>(key_l) * row_stride + static_cast<size_t>(kvh) * kD + c0 * 16;
+    const uint8_t* gk = p.k + head_off;
+    const uint8_t* gv = p.v + head_off;
+    const size_t tile_bytes = static_cast<size_t>(kKeys) * row_stride;
+    const float* gks = p.k_scale + static_cast<size_t>(key_l) * p.num_kv_heads + kvh;
+    const float* gvs = p.v_scale + static_cast<size_t>(key_l) * p.num_kv_heads + kvh;
+    const size_t tile_scales = static_cast<size_t>(kKeys) * p.num_kv_heads;
+    uint32_t raw_off[kNch], dst_off[kNch];
 #pragma unroll
-        for (int i = 0; i < 1024 / kThreads; ++i) {
-            const int id = tid + i * kThreads, which = id >> 9, ch = (id >> 6) & 7, key_l = id & 63;
-            const int key = j * kKeys + key_l;
-            const bool live = key < total_keys;
-            const uint8_t* src = (which ? p.v : p.k) + (live ? static_cast<size_t>(key) * row_stride + static_cast<size_t>(kvh) * kD + ch * 16 : 0);
-            cp16_zfill(base + kOffRaw + which * (kKeys * kD) + swz128(key_l, ch), src, live);
-        }
+    for (int t = 0; t < kNch; ++t) {
+        const int ch = c0 + t * kStep;
+        raw_off[t] = kOffRaw + swz128(key_l, ch);
+        dst_off[t] = (ch >> 2) * (kKeys * 128) + swz128(key_l, 2 * (ch & 3));      // the second half sits at ^ 16
+    }
+    // K rows (with both scale vectors) and V rows travel as separate cp.async groups, issued in the order
+    // K0 V0 K1 V1 ...: a wait that leaves one group pending always covers the tile part needed next.
+    int next_key_k = key_l, next_key_v = key_l;          // this thread's key in the tile the next issue fetches
+    auto issue_k = [&]() {
+        const bool live = next_key_k < total_keys;
+#pragma unroll
+        for (int t = 0; t < kNch; ++t) cp16_zfill(base + raw_off[t], live ? gk + t * kStep * 16 : p.k, live);
         if (tid < kKeys) {
-            const int key = j * kKeys + tid;
-            const bool live = key < total_keys;
-            const size_t idx = live ? static_cast<size_t>(key) * p.num_kv_heads + kvh : 0;
-            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + tid * 4, p.k_scale + idx, live);
-            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + kKeys * 4 + tid * 4, p.v_scale + idx, live);
+            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + tid * 4, live ? gks : p.k_scale, live);
+            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + kKeys * 4 + tid * 4, live ? gvs : p.v_scale, live);
         }
         cp_async_commit();
+        gk += tile_bytes;
+        gks += tile_scales;
+        gvs += tile_scales;
+        next_key_k += kKeys;
+    };
+    auto issue_v = [&]() {
+        const bool live = next_key_v < total_keys;
+#pragma unroll
+        for (int t = 0; t < kNch; ++t) cp16_zfill(base + raw_off[t] + kKeys * kD, live ? gv + t * kStep * 16 : p.v, live);
+        cp_async_commit();
+        gv += tile_bytes;
+        next_key_v += kKeys;
     };
     // E4M3 -> f16 into the operand tiles: [dim block of 64][key][128 bytes, swizzled]; K and V share the form
     // (K is consumed K-major: a row is a key; V MN-major: the 128 bytes of a row are 64 consecutive dims)
-    auto convert = [&]() {
+    auto convert_rows = [&](int which) {
 #pragma unroll
-        for (int i = 0; i < 1024 / kThreads; ++i) {
-            const int id = tid + i * kThreads, which = id >> 9, ch = (id >> 6) & 7, key_l = id & 63;
-            const uint4 w = *reinterpret_cast<const uint4*>(sm + kOffRaw + which * (kKeys * kD) + swz128(key_l, ch));
+        for (int t = 0; t < kNch; ++t) {
+            const uint4 w = *reinterpret_cast<const uint4*>(sm + raw_off[t] + which * (kKeys * kD));
             uint4 h0, h1;
             e4m3x4_to_f16x2x2(w.x, h0.x, h0.y);
             e4m3x4_to_f16x2x2(w.y, h0.z, h0.w);
             e4m3x4_to_f16x2x2(w.z, h1.x, h1.y);
             e4m3x4_to_f16x2x2(w.w, h1.z, h1.w);
-            unsigned char* const dst = sm + (which ? kOffV : kOffK) + (ch >> 2) * (kKeys * 128);
-            *reinterpret_cast<uint4*>(dst + swz128(key_l, 2 * (ch & 3))) = h0;
-            *reinterpret_cast<uint4*>(dst + swz128(key_l, 2 * (ch & 3) + 1)) = h1;
+            unsigned char* const dst = sm + (which ? kOffV : kOffK) + dst_off[t];
+            *reinterpret_cast<uint4*>(dst) = h0;
+            *reinterpret_cast<uint4*>(reinterpret_cast<uintptr_t>(dst) ^ 16) = h1;
         }
+    };
+    // K rows plus the per-key constants of the tile: K scale x softmax scale x log2(e), log2 of the V scale, its inverse
+    auto convert_k = [&]() {
+        convert_rows(0);
         if (tid < kKeys) {
             const float* const sc = reinterpret_cast<const float*>(sm + kOffRaw + 2 * kKeys * kD);
             float* const cst = reinterpret_cast<float*>(sm + kOffCst);
@@ -281,7 +331,18 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             cst[2 * kKeys + tid] = ex2f(-lg);
         }
     };
-    issue_raw(0);
+    auto issue_qk = [&]() {                               // S = Q K^T: eight products of depth 16
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < kD / 16; ++s) {
+            const uint32_t off = (s >> 2) * (kRows * 128) + (s & 3) * 32;
+            const uint32_t koff = (s >> 2) * (kKeys * 128) + (s & 3) * 32;
+            umma_f16(tmem_s, smem_desc(base + kOffQ + off, 16), smem_desc(base + kOffK + koff, 16), kIdescQK, s > 0);
+        }
+        umma_commit(bar_s);
+    };
+    issue_k();
+    issue_v();
 
     // ---- Q: row `row`, this thread's 16 / kParts chunks, bf16 -> f16, [dim block][row][128 bytes, swizzled] ----
     {
@@ -300,37 +361,26 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
         }
     }
 
-    constexpr uint32_t kIdescQK = instr_desc(kKeys, false);
-    constexpr uint32_t kIdescPV = instr_desc(kD, true);
     float m_run = kMInit, l_run = 0.0f;      // m_run is the same in all threads of a row; l_run is this thread's part
     bool failed = false;
 
-    for (int j = 0; j < n_tiles && !failed; ++j) {
-        cp_async_wait<0>();                                      // this thread's raw chunks of tile j
-        if (j > 0) {                                             // the products of tile j-1 are done with K, V, W
-            const bool ok = pipe::mbar_wait(bar_o, (j - 1) & 1, __LINE__, p.error_word, kWaitLimit);
-            tc_fence_after();
-            if (!ok) failed = true;
-        }
-        convert();
-        if (j + 1 < n_tiles) issue_raw(j + 1);                   // this thread's chunks only: no barrier needed
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(failed)) { failed = true; break; }
+    // ---- prologue: K of tile 0 converted, S_0 = Q K_0^T under way, V of tile 0 converted meanwhile ----
+    cp_async_wait<1>();                                          // K rows and scales of tile 0 (V rows may be pending)
+    convert_k();
+    issue_k();                                                   // tile 1 (an empty group past the last tile)
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) issue_qk();
+    cp_async_wait<1>();                                          // V rows of tile 0
+    convert_rows(1);
+    issue_v();
 
-        // ---- S = Q K^T ----
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int s = 0; s < kD / 16; ++s) {
-                const uint32_t off = (s >> 2) * (kRows * 128) + (s & 3) * 32;
-                const uint32_t koff = (s >> 2) * (kKeys * 128) + (s & 3) * 32;
-                umma_f16(tmem_s, smem_desc(base + kOffQ + off, 16), smem_desc(base + kOffK + koff, 16), kIdescQK, s > 0);
-            }
-            umma_commit(bar_s);
-        }
+    // Steady state of tile j.  The tensor core works on O += W_j V_j while the threads convert K of tile j+1,
+    // and on S_{j+1} while they convert V of tile j+1; the threads' softmax of tile j follows the wait for S_j.
+    for (int j = 0; j < n_tiles; ++j) {          // leaves early only through the CTA-wide votes below
         {
-            const bool ok = pipe::mbar_wait(bar_s, j & 1, __LINE__, p.error_word, kWaitLimit);
+            const bool ok = mbar_wait_quiet(bar_s, j & 1, __LINE__, p.error_word);
             tc_fence_after();
             if (!ok) failed = true;
         }
@@ -350,15 +400,14 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             sv[i + 1] = fmaf(sv[i + 1], kk.y, lg.y);
             sv[i + 2] = fmaf(sv[i + 2], kk.z, lg.z);
             sv[i + 3] = fmaf(sv[i + 3], kk.w, lg.w);
-            if (diag) {
-                const int kpos = key0 + i;
-                if (kpos > qpos) sv[i] = -INFINITY;
-                if (kpos + 1 > qpos) sv[i + 1] = -INFINITY;
-                if (kpos + 2 > qpos) sv[i + 2] = -INFINITY;
-                if (kpos + 3 > qpos) sv[i + 3] = -INFINITY;
-            }
-            mx = fmaxf(mx, fmaxf(fmaxf(sv[i], sv[i + 1]), fmaxf(sv[i + 2], sv[i + 3])));
         }
+        if (diag) {                          // the one or two tiles that straddle the diagonal
+#pragma unroll
+            for (int i = 0; i < kC; ++i)
+                if (key0 + i > qpos) sv[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < kC; i += 4) mx = fmaxf(mx, fmaxf(fmaxf(sv[i], sv[i + 1]), fmaxf(sv[i + 2], sv[i + 3])));
         if constexpr (kParts > 1) {          // the row's threads sit in warps w, w + 4, ...: one named barrier per quarter
             xch[part * kRows + row] = mx;
             named_sync(1 + (warp & 3), 32 * kParts);
@@ -372,7 +421,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
         const float m_new = fmaxf(m_run, mx);
         const float corr = ex2f(m_run - m_new);
         m_run = m_new;
-        float sum = 0.0f;
+        float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};      // independent chains
 #pragma unroll
         for (int i = 0; i < kC; i += 8) {
             uint4 w;
@@ -381,16 +430,18 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             for (int u = 0; u < 8; ++u) e[u] = ex2f(sv[i + u] - m_new);
             const float4 r0 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + i);
             const float4 r1 = *reinterpret_cast<const float4*>(cst + 2 * kKeys + i + 4);
-            sum = fmaf(e[0], r0.x, fmaf(e[1], r0.y, fmaf(e[2], r0.z, fmaf(e[3], r0.w, sum))));
-            sum = fmaf(e[4], r1.x, fmaf(e[5], r1.y, fmaf(e[6], r1.z, fmaf(e[7], r1.w, sum))));
+            sum4[0] = fmaf(e[0], r0.x, fmaf(e[4], r1.x, sum4[0]));
+            sum4[1] = fmaf(e[1], r0.y, fmaf(e[5], r1.y, sum4[1]));
+            sum4[2] = fmaf(e[2], r0.z, fmaf(e[6], r1.z, sum4[2]));
+            sum4[3] = fmaf(e[3], r0.w, fmaf(e[7], r1.w, sum4[3]));
             w.x = pack_f16x2(e[0], e[1]);
             w.y = pack_f16x2(e[2], e[3]);
             w.z = pack_f16x2(e[4], e[5]);
             w.w = pack_f16x2(e[6], e[7]);
             *reinterpret_cast<uint4*>(sm + kOffP + swz128(row, (part * kC + i) >> 3)) = w;
         }
-        l_run = fmaf(l_run, corr, sum);
-        // this thread's columns of the O row (the products of tile j-1 completed before this tile's conversion)
+        l_run = fmaf(l_run, corr, (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        // this thread's columns of the O row (O += W_{j-1} V_{j-1} completed before V of this tile was converted)
         if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
             for (int cb = 0; cb < kOC; cb += 32) {
@@ -406,7 +457,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
         tc_fence_before();
         if (__syncthreads_or(failed)) { failed = true; break; }
 
-        // ---- O += W V ----
+        // ---- O += W_j V_j ----
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
@@ -415,11 +466,28 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
                          j > 0 || s > 0);
             umma_commit(bar_o);
         }
+        if (j + 1 < n_tiles) {
+            // K of tile j+1: the K tile is free (S_j is complete), the product above runs meanwhile
+            cp_async_wait<1>();
+            convert_k();
+            issue_k();
+            fence_async_smem();
+            tc_fence_before();
+            if (__syncthreads_or(failed)) { failed = true; break; }
+            if (tid == 0) issue_qk();                            // every thread has read S_j: its columns are free
+            // V of tile j+1 once O += W_j V_j is complete; S_{j+1} runs meanwhile
+            const bool ok = mbar_wait_quiet(bar_o, j & 1, __LINE__, p.error_word);
+            tc_fence_after();
+            if (!ok) failed = true;
+            cp_async_wait<1>();
+            convert_rows(1);
+            issue_v();
+        }
     }
 
     // ---- epilogue: normalise, store; every path releases the tensor memory ----
     if (!failed && n_tiles > 0) {
-        const bool ok = pipe::mbar_wait(bar_o, (n_tiles - 1) & 1, __LINE__, p.error_word, kWaitLimit);
+        const bool ok = mbar_wait_quiet(bar_o, (n_tiles - 1) & 1, __LINE__, p.error_word);
         tc_fence_after();
         if (!ok) failed = true;
     }
