@@ -253,8 +253,9 @@ int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host);
  * "swiglu_stages" (depth of the bulk-copy staging ring, 1 = direct loads), "no_pdl" (1 = launch
  * without the programmatic-dependent-launch attribute; by default each kernel may be scheduled
  * while the previous kernel of its stream drains and orders itself on the device before its first
- * memory access, so stream semantics are unchanged), "prefill_tiles" (1|2: 16-row tiles per warp of the
- * prefill attention kernel; default by problem size); value <= 0 restores the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
+ * memory access, so stream semantics are unchanged), "prefill_tiles" (1|2: the mma.sync forms of the prefill
+ * attention kernel with one or two 16-row tiles per warp; default: the tcgen05 form with S and O in tensor
+ * memory), "prefill_parts" (1|2|4 threads share a query row of the tcgen05 form; default 2); value <= 0 restores the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
 int rh_tune(const char* key, int value);
 
 #ifdef __cplusplus

@@ -457,8 +457,10 @@ extern "C" int rh_flash_prefill_bf16(void* out, const void* q, const uint8_t* k,
     // Two 16-row tiles per warp halve the shared-memory reads per product (one CTA per SM, 255 registers);
     // short prompts do not fill the GPU with such CTAs and take the one-tile form (two CTAs per SM).
     const long long ctas_wide = static_cast<long long>((n_new + 32 * a.subs - 1) / (32 * a.subs)) * num_kv_heads * a.head_chunks;
+    // Default: the tcgen05 form (flash_prefill_tc.cu; it stores 16-byte pieces of `out`).  "prefill_tiles" 1 or 2,
+    // or an `out` that is only 4-byte aligned, selects the mma.sync forms below.
     const int pick = host::tuning(host::kPrefillTiles);
-    if (pick == 3)
+    if (pick != 1 && pick != 2 && host::aligned16(out))
         return launch_flash_prefill_tc(out, q, k, v, k_scale, v_scale, n_new, cache_len, num_q_heads, num_kv_heads, scale,
                                        static_cast<cudaStream_t>(stream), fn);
     const bool wide = pick == 2 || (pick != 1 && ctas_wide >= 2LL * host::num_sms());

@@ -145,6 +145,24 @@ def test_prefill_then_decode_agree_on_the_last_token(orc):
     check(dec, bits, exact, "decode", significance=64)
 
 
+def test_output_that_is_only_four_byte_aligned(orc):
+    """The reference asks nothing of `out` beyond bf16 pairs; the tensor-memory form stores 16-byte pieces, so such
+    a call takes the mma.sync form and must land on the same exact values."""
+    from runtherder_b200 import kernels as K
+    n_new, cache_len, Hq, Hkv, D = 70, 9, 8, 2, 128
+    q, kc, ks, vc, vs = make_case(n_new, cache_len, Hq, Hkv, D, seed=21, q_mul=2.0, dist="normal")
+    scale = 1.0 / math.sqrt(D)
+    cl = torch.tensor([cache_len], dtype=torch.int32, device="cuda")
+    backing = torch.zeros(n_new * Hq * D + 8, dtype=torch.bfloat16, device="cuda")
+    out = backing[2:2 + n_new * Hq * D].view(n_new, Hq, D)
+    assert out.data_ptr() % 16 == 4
+    K.flash_prefill_bf16(out, q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
+    torch.cuda.synchronize()
+    bits, exact = orc.attention_causal_fp8(to_np(q), to_np(kc), to_np(vc), to_np(ks), to_np(vs), cache_len, scale)
+    check(out.contiguous(), bits, exact, "four-byte aligned output")
+    assert float(backing[:2].float().abs().max()) == 0.0 and float(backing[-6:].float().abs().max()) == 0.0
+
+
 def test_cache_len_is_read_on_the_device_and_arguments_are_checked():
     from runtherder_b200 import _lib
     from runtherder_b200 import kernels as K
