@@ -79,6 +79,9 @@ MORE_CASES = [
     (97, 1, 16, 1),       # sixteen heads on one kv head: two head chunks
     (129, 0, 2, 2),       # no grouping: eight 16-token sub-tiles per CTA
     (1, 77, 8, 2),        # a single token (the decode shape through the prefill entry)
+    (97, 31, 8, 4),       # two heads per kv head: 64 tokens x 2 heads per 128-row tile
+    (70, 200, 16, 2),     # eight heads per kv head: two head chunks of four
+    (33, 5, 10, 2),       # five heads per kv head: a full chunk and a chunk with one live head slot
 ]
 
 
@@ -143,6 +146,41 @@ def test_prefill_then_decode_agree_on_the_last_token(orc):
                                            cache_len + n_new - 1, scale)
     check(out[n_new - 1], bits, exact, "prefill, last token")
     check(dec, bits, exact, "decode", significance=64)
+
+
+def test_full_size_prefill_properties(orc):
+    """The prefill configuration's full size (8192 tokens, 32/8 heads): (a) the tensor-memory form and the
+    mma.sync form land within two ulp-at-row-max of each other everywhere, (b) sampled tokens match the exact
+    value, (c) a chunked prefill of the tail (different row-to-CTA grouping, `*cache_len` > 0) reproduces the
+    same rows of the whole prefill bit for bit."""
+    from runtherder_b200 import kernels as K
+    T, Hq, Hkv, D = 8192, 32, 8, 128
+    q, kc, ks, vc, vs = make_case(T, 0, Hq, Hkv, D, seed=77, q_mul=3.0, dist="normal")
+    scale = 1.0 / math.sqrt(D)
+    zero = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out_tc = torch.empty(T, Hq, D, dtype=torch.bfloat16, device="cuda")
+    out_mma = torch.empty_like(out_tc)
+    K.flash_prefill_bf16(out_tc, q, kc, vc, ks, vs, T, zero, Hq, Hkv, D, scale)
+    try:
+        K.tune("prefill_tiles", 2)
+        K.flash_prefill_bf16(out_mma, q, kc, vc, ks, vs, T, zero, Hq, Hkv, D, scale)
+    finally:
+        K.tune("prefill_tiles", 0)
+    torch.cuda.synchronize()
+    a, b = out_tc.float(), out_mma.float()
+    assert bool(torch.isfinite(a).all())
+    rowmax = b.abs().amax(dim=-1, keepdim=True)
+    assert float(((a - b).abs() / rowmax).max()) <= 2 * ROWMAX_TOL
+    for t0, n in ((0, 3), (62, 4), (4094, 4), (T - 4, 4)):
+        bits, exact = orc.attention_causal_fp8(to_np(q[t0:t0 + n].contiguous()), to_np(kc[:t0 + n]), to_np(vc[:t0 + n]),
+                                               to_np(ks[:t0 + n]), to_np(vs[:t0 + n]), t0, scale)
+        check(out_tc[t0:t0 + n].contiguous(), bits, exact, f"tokens {t0}..{t0 + n - 1} of {T}")
+    t0 = 4100                                   # not a multiple of the token tile: rows regroup
+    cl = torch.tensor([t0], dtype=torch.int32, device="cuda")
+    tail = torch.empty(T - t0, Hq, D, dtype=torch.bfloat16, device="cuda")
+    K.flash_prefill_bf16(tail, q[t0:].contiguous(), kc, vc, ks, vs, T - t0, cl, Hq, Hkv, D, scale)
+    torch.cuda.synchronize()
+    assert torch.equal(tail.view(torch.int16), out_tc[t0:].view(torch.int16))
 
 
 def test_output_that_is_only_four_byte_aligned(orc):
