@@ -10,9 +10,10 @@
 //     -> S[128 x 64] = Q K^T: eight tcgen05.mma (M=128, N=64, K=16), fp32 in tensor memory
 //     -> the threads of row r load their part of S row r (tcgen05.ld 32x32b), apply the K scale, the V scale
 //        in the exponent and the causal mask, agree on the row maximum through shared memory (a named
-//        barrier per 32-row quarter), write their weights (f16) to shared memory and rescale their columns
-//        of O in tensor memory when the running maximum moved
-//     -> O[128 x 128] += W V: four tcgen05.mma (M=128, N=128, K=16), V read MN-major as stored.
+//        barrier per 32-row quarter), store their weights as f16 pairs into tensor memory (tcgen05.st) and
+//        rescale their columns of O in tensor memory when the running maximum moved
+//     -> O[128 x 128] += W V: four tcgen05.mma (M=128, N=128, K=16) with W read from tensor memory and V
+//        read MN-major from shared memory exactly as the cache stores it.
 // One elected thread issues the products; completion comes back through mbarriers (tcgen05.commit).
 // Every mbarrier wait is bounded and agreed on by the whole CTA (__syncthreads_or), and every path out
 // of the kernel releases the tensor memory it allocated.
@@ -34,7 +35,7 @@ constexpr int kRows = 128;       // query rows per CTA (M)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMInit = -1.0e30f;
 constexpr float kLgFloor = -100.0f;
-constexpr int kTmemCols = 256;   // S: 64 columns, O: 128 columns; allocations are powers of two
+constexpr int kTmemCols = 256;   // S: 64 columns, O: 128, W (f16 pairs): 32; allocations are powers of two
 constexpr uint32_t kSuspendNs = 20000;   // longest hardware sleep per mbarrier try
 constexpr int kWaitLimit = 1 << 16;   // polls; each try_wait already blocks for a while in hardware
 
@@ -42,8 +43,7 @@ constexpr int kWaitLimit = 1 << 16;   // polls; each try_wait already blocks for
 constexpr int kOffQ = 0;                        // [2 dim blocks][128 rows][128 B]   32 KB
 constexpr int kOffK = kOffQ + 2 * kRows * 128;  // [2 dim blocks][64 keys][128 B]    16 KB
 constexpr int kOffV = kOffK + 2 * kKeys * 128;  // [2 dim blocks][64 keys][128 B]    16 KB (read MN-major)
-constexpr int kOffP = kOffV + 2 * kKeys * 128;  // [128 rows][128 B]                 16 KB
-constexpr int kOffRaw = kOffP + kRows * 128;    // raw K, raw V (8 KB each), 64 + 64 scales
+constexpr int kOffRaw = kOffV + 2 * kKeys * 128;   // raw K, raw V (8 KB each), 64 + 64 scales
 constexpr int kOffCst = kOffRaw + 2 * kKeys * kD + 2 * kKeys * 4;   // ksl[64], lgv[64], rvs[64]
 constexpr int kOffXch = kOffCst + 3 * kKeys * 4;                    // row maxima / sums exchanged between a row's threads: [4][128]
 constexpr int kOffBar = kOffXch + 4 * kRows * 4;                    // two mbarriers, the tmem base
@@ -140,6 +140,14 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
         : "memory");
 }
+// the same product with the A operand in tensor memory (row = lane, two f16 values per 32-bit column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pipe::smem_u32(bar)) : "memory");
 }
@@ -188,6 +196,22 @@ __device__ __forceinline__ void tmem_ld16(float* v, uint32_t addr) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// kN consecutive 32-bit columns of this thread's lane, from registers
+template <int kN>
+__device__ __forceinline__ void tmem_st_words(uint32_t addr, const uint32_t* w) {
+    static_assert(kN == 8 || kN == 16 || kN == 32, "columns per thread");
+    if constexpr (kN == 8) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                     ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+    } else if constexpr (kN == 16) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                     ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
+                       "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
+    } else {
+        tmem_st_words<16>(addr, w);
+        tmem_st_words<16>(addr + 16, w + 16);
+    }
 }
 template <int kN>
 __device__ __forceinline__ void tmem_ld(float* v, uint32_t addr) {
@@ -245,7 +269,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + kKeys;                       // column offsets
+    const uint32_t tmem_s = tmem, tmem_o = tmem + kKeys, tmem_w = tmem + kKeys + kD;   // column offsets
     const uint32_t my_lane = static_cast<uint32_t>(32 * (warp & 3)) << 16;     // this warp's quarter of the 128 lanes
 
     pdl_enter();
@@ -422,9 +446,9 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
         const float corr = ex2f(m_run - m_new);
         m_run = m_new;
         float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};      // independent chains
+        uint32_t wv[kC / 2];                           // this thread's weights, two f16 per word
 #pragma unroll
         for (int i = 0; i < kC; i += 8) {
-            uint4 w;
             float e[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) e[u] = ex2f(sv[i + u] - m_new);
@@ -434,12 +458,13 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             sum4[1] = fmaf(e[1], r0.y, fmaf(e[5], r1.y, sum4[1]));
             sum4[2] = fmaf(e[2], r0.z, fmaf(e[6], r1.z, sum4[2]));
             sum4[3] = fmaf(e[3], r0.w, fmaf(e[7], r1.w, sum4[3]));
-            w.x = pack_f16x2(e[0], e[1]);
-            w.y = pack_f16x2(e[2], e[3]);
-            w.z = pack_f16x2(e[4], e[5]);
-            w.w = pack_f16x2(e[6], e[7]);
-            *reinterpret_cast<uint4*>(sm + kOffP + swz128(row, (part * kC + i) >> 3)) = w;
+            wv[i / 2] = pack_f16x2(e[0], e[1]);
+            wv[i / 2 + 1] = pack_f16x2(e[2], e[3]);
+            wv[i / 2 + 2] = pack_f16x2(e[4], e[5]);
+            wv[i / 2 + 3] = pack_f16x2(e[6], e[7]);
         }
+        // W stays in tensor memory as the A operand of O += W V (O += W_{j-1} V_{j-1} has completed: see below)
+        tmem_st_words<kC / 2>(tmem_w + my_lane + part * (kC / 2), wv);
         l_run = fmaf(l_run, corr, (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         // this thread's columns of the O row (O += W_{j-1} V_{j-1} completed before V of this tile was converted)
         if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
@@ -451,8 +476,8 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
                 for (int i = 0; i < 32; ++i) ov[i] *= corr;
                 tmem_st32(tmem_o + my_lane + part * kOC + cb, ov);
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         fence_async_smem();
         tc_fence_before();
         if (__syncthreads_or(failed)) { failed = true; break; }
@@ -462,8 +487,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             tc_fence_after();
 #pragma unroll
             for (int s = 0; s < kKeys / 16; ++s)
-                umma_f16(tmem_o, smem_desc(base + kOffP + s * 32, 16), smem_desc(base + kOffV + s * 2048, kKeys * 128), kIdescPV,
-                         j > 0 || s > 0);
+                umma_f16_ts(tmem_o, tmem_w + s * 8, smem_desc(base + kOffV + s * 2048, kKeys * 128), kIdescPV, j > 0 || s > 0);
             umma_commit(bar_o);
         }
         if (j + 1 < n_tiles) {
@@ -553,7 +577,10 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     const dim3 grid(static_cast<unsigned>((n_new + a.tokens_per_cta - 1) / a.tokens_per_cta),
                     static_cast<unsigned>(num_kv_heads * a.head_chunks));
     RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
-    const int parts = host::tuning(host::kPrefillParts);
+    // "prefill_parts" 1|2|4; +20 pads the shared-memory request so that one CTA fits per SM (a measuring aid)
+    const int knob = host::tuning(host::kPrefillParts);
+    const int parts = knob >= 20 ? knob - 20 : knob;
+    const size_t smem = knob >= 20 ? 120u * 1024u : static_cast<size_t>(tc::kSmemBytes);
     auto go = [&](auto kernel, int threads) {
         static std::atomic<unsigned> configured[3];      // per kernel form: the devices already set up
         std::atomic<unsigned>& done = configured[threads >> 8];
@@ -561,10 +588,10 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
         cudaGetDevice(&dev);
         const unsigned bit = 1u << (dev & 31);
         if ((done.load(std::memory_order_relaxed) & bit) == 0) {
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes);
+            cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
             done.fetch_or(bit, std::memory_order_relaxed);
         }
-        host::launch(kernel, grid, dim3(threads), static_cast<size_t>(tc::kSmemBytes), stream, a);
+        host::launch(kernel, grid, dim3(threads), smem, stream, a);
     };
     if (parts == 1) go(tc::flash_prefill_tc_kernel<1>, 128);
     else if (parts == 4) go(tc::flash_prefill_tc_kernel<4>, 512);
