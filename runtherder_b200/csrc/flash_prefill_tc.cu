@@ -35,13 +35,13 @@ constexpr int kRows = 128;       // query rows per CTA (M)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMInit = -1.0e30f;
 constexpr float kLgFloor = -100.0f;
-constexpr int kTmemCols = 256;   // S: 64 columns, O: 128, W (f16 pairs): 32; allocations are powers of two
+constexpr int kTmemCols = 256;   // S: 64 columns, O: 128, W (f16 pairs): 32, upper half of Q (f16 pairs): 32
 constexpr uint32_t kSuspendNs = 20000;   // longest hardware sleep per mbarrier try
 constexpr int kWaitLimit = 1 << 16;   // polls; each try_wait already blocks for a while in hardware
 
 // shared-memory map, relative to a 1024-byte aligned base
-constexpr int kOffQ = 0;                        // [2 dim blocks][128 rows][128 B]   32 KB
-constexpr int kOffK = kOffQ + 2 * kRows * 128;  // [2 dim blocks][64 keys][128 B]    16 KB
+constexpr int kOffQ = 0;                        // [128 rows][128 B]: dims 0..63 of Q (dims 64..127 live in tensor memory)  16 KB
+constexpr int kOffK = kOffQ + kRows * 128;      // [2 dim blocks][64 keys][128 B]    16 KB
 constexpr int kOffV = kOffK + 2 * kKeys * 128;  // [2 dim blocks][64 keys][128 B]    16 KB (read MN-major)
 constexpr int kOffRaw = kOffV + 2 * kKeys * 128;   // raw K, raw V (8 KB each), 64 + 64 scales
 constexpr int kOffCst = kOffRaw + 2 * kKeys * kD + 2 * kKeys * 4;   // ksl[64], lgv[64], rvs[64]
@@ -270,6 +270,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_s = tmem, tmem_o = tmem + kKeys, tmem_w = tmem + kKeys + kD;   // column offsets
+    const uint32_t tmem_q = tmem_w + kKeys / 2;
     const uint32_t my_lane = static_cast<uint32_t>(32 * (warp & 3)) << 16;     // this warp's quarter of the 128 lanes
 
     pdl_enter();
@@ -358,22 +359,22 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
     auto issue_qk = [&]() {                               // S = Q K^T: eight products of depth 16
         tc_fence_after();
 #pragma unroll
-        for (int s = 0; s < kD / 16; ++s) {
-            const uint32_t off = (s >> 2) * (kRows * 128) + (s & 3) * 32;
-            const uint32_t koff = (s >> 2) * (kKeys * 128) + (s & 3) * 32;
-            umma_f16(tmem_s, smem_desc(base + kOffQ + off, 16), smem_desc(base + kOffK + koff, 16), kIdescQK, s > 0);
-        }
+        for (int s = 0; s < 4; ++s)       // dims 0..63: both operands from shared memory
+            umma_f16(tmem_s, smem_desc(base + kOffQ + s * 32, 16), smem_desc(base + kOffK + s * 32, 16), kIdescQK, s > 0);
+#pragma unroll
+        for (int s = 0; s < 4; ++s)       // dims 64..127: Q from tensor memory
+            umma_f16_ts(tmem_s, tmem_q + s * 8, smem_desc(base + kOffK + kKeys * 128 + s * 32, 16), kIdescQK, true);
         umma_commit(bar_s);
     };
     issue_k();
     issue_v();
 
-    // ---- Q: row `row`, this thread's 16 / kParts chunks, bf16 -> f16, [dim block][row][128 bytes, swizzled] ----
+    // ---- Q: row `row`, bf16 -> f16.  Dims 0..63 go to shared memory ([row][128 bytes, swizzled]), dims 64..127 to
+    //      tensor memory (row = lane, two f16 per column) as the A operand of the second half of S = Q K^T.
+    //      kParts threads share the row's 16 chunks of 8 dims; `part` is uniform in a warp. ----
     {
         const __nv_bfloat16* src = p.q + (static_cast<size_t>(row_valid ? tok : 0) * p.num_q_heads + (row_valid ? qh : 0)) * kD;
-#pragma unroll
-        for (int c = 0; c < 16 / kParts; ++c) {
-            const int cidx = part * (16 / kParts) + c;
+        auto load_chunk = [&](int cidx) {
             uint4 w = make_uint4(0u, 0u, 0u, 0u);
             if (row_valid) w = *reinterpret_cast<const uint4*>(src + cidx * 8);
             uint4 h;
@@ -381,7 +382,29 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             h.y = pack_f16x2(bf_lo(w.y), bf_hi(w.y));
             h.z = pack_f16x2(bf_lo(w.z), bf_hi(w.z));
             h.w = pack_f16x2(bf_lo(w.w), bf_hi(w.w));
-            *reinterpret_cast<uint4*>(sm + kOffQ + (cidx >> 3) * (kRows * 128) + swz128(row, cidx & 7)) = h;
+            return h;
+        };
+        constexpr int kPer = kParts == 1 ? 8 : 16 / kParts;     // chunks per thread and half
+        if (kParts == 1 || part < kParts / 2) {
+#pragma unroll
+            for (int c = 0; c < kPer; ++c) {
+                const int cidx = (kParts == 1 ? 0 : part * kPer) + c;
+                *reinterpret_cast<uint4*>(sm + kOffQ + swz128(row, cidx)) = load_chunk(cidx);
+            }
+        }
+        if (kParts == 1 || part >= kParts / 2) {
+            uint32_t qw[4 * kPer];
+            const int first = kParts == 1 ? 0 : (part - kParts / 2) * kPer;     // chunk within the upper half
+#pragma unroll
+            for (int c = 0; c < kPer; ++c) {
+                const uint4 h = load_chunk(8 + first + c);
+                qw[4 * c] = h.x;
+                qw[4 * c + 1] = h.y;
+                qw[4 * c + 2] = h.z;
+                qw[4 * c + 3] = h.w;
+            }
+            tmem_st_words<4 * kPer>(tmem_q + my_lane + 4 * first, qw);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
     }
 
