@@ -11,7 +11,12 @@ RoPE + FP8 KV append, SwiGLU + INT8 quantisation.  With N GPUs the rows are spli
 blocks (strong scaling, no collective on the data path).
 
 value  = algorithmic HBM bytes of a step / device time of the step, whole job (GB/s), inputs resident.
+         The K-step region (no event, no host work between launches) is timed `--repeats` times, each
+         bracketed by a barrier and a synchronise; ms_per_step is the median region, the spread is reported.
+ops    = per-kernel times from a separate, un-timed pass with an event after every launch.
 e2e    = the same bytes / wall time of a step driven from pinned HOST buffers (H2D + kernels + D2H).
+verify = (N > 1) rows around every shard boundary, gathered over NCCL from the GPUs that own them and
+         compared bit for bit with the same rows computed on rank 0 alone; outside the timed region.
 Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
@@ -32,10 +37,22 @@ sys.path.insert(0, str(ROOT))
 METRIC = "fused-layer-op HBM GB/s"
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per token row of each step kernel, from the ncu capture
-# summarised in profiles/c4_step_kernels_ncu_16384rows.md (16384-row case; rows are independent units,
-# so a launch's traffic is this figure times its rows).
-DRAM_TRAFFIC_BYTES_PER_ROW = {"embedding": 12878, "norm_quant": 26223, "rope_kv": 19303, "swiglu_quant": 70921}
+
+
+def dram_traffic_per_row(kernel: str, rows: int):
+    """dram__bytes_read.sum + dram__bytes_write.sum per token row of a step kernel, from the ncu captures listed
+    in profiles/dram_traffic.json (one entry per (kernel, rows) actually captured).  Rows are independent units,
+    so a launch's traffic is the per-row figure of the nearest captured row count times its rows; None when the
+    kernel was never captured."""
+    f = ROOT / "profiles" / "dram_traffic.json"
+    try:
+        entries = [e for e in json.loads(f.read_text())["captures"] if e["kernel"] == kernel]
+    except Exception:
+        return None
+    if not entries:
+        return None
+    best = min(entries, key=lambda e: abs(e["rows"] - rows))
+    return (best["dram_bytes_read"] + best["dram_bytes_write"]) / best["rows"]
 
 
 def parse_args():
@@ -49,6 +66,9 @@ def parse_args():
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-cpu", action="store_true")
     p.add_argument("--no-refcuda", action="store_true")
+    p.add_argument("--no-secondary", action="store_true", help="skip the attention timings appended to the sweep line")
+    p.add_argument("--no-verify", action="store_true", help="N > 1: skip the cross-GPU check of the shard boundaries")
+    p.add_argument("--repeats", type=int, default=5, help="how many times the K-step region is timed (median reported)")
     p.add_argument("--cpu-seconds", type=float, default=15.0)
     p.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
                    help="layer-chain configs: replay the forward from a CUDA graph (auto: on for the decode config)")
@@ -156,8 +176,7 @@ def cpu_rows_per_second(cfg, total_rows: int, threads: int):
     import numpy as np
     sys.path.insert(0, str(ROOT / "tests"))
     from oracle_lib import Oracle, load_ref_host, ptr
-    from runtherder_b200 import synth
-    from runtherder_b200.rope_tables import inv_freq_for
+    from runtherder_b200 import synth_spec as synth      # numpy only: this arm never loads the CUDA library
 
     orc = Oracle()
     ref = load_ref_host()
@@ -197,7 +216,10 @@ def cpu_rows_per_second(cfg, total_rows: int, threads: int):
             ref.refhost_swiglu(ptr(act), ptr(gate), ptr(up), n * I)
         else:
             pos = np.arange(cfg.start_pos + b, cfg.start_pos + e, dtype=np.int32)
-            inv = inv_freq_for(cfg)
+            rs = cfg.rope_scaling
+            inv = (orc.inv_freq_plain(D, cfg.rope_theta) if rs is None else
+                   orc.inv_freq_llama3(D, cfg.rope_theta, rs.factor, rs.low_freq_factor, rs.high_freq_factor,
+                                       rs.original_max_position_embeddings))
             orc.rope_table(q, pos, inv)
             k = orc.rope_table(k, pos, inv)
             orc.quant_kv(k.reshape(n * Hkv, D))
@@ -234,7 +256,9 @@ def cpu_baseline(cfg, seconds: float):
                               "sample": f"{one_rows} rows on one thread"},
             "sample": f"{rows} of {cfg.tokens} token rows of the same four ops, row-parallel over {threads} host "
                       f"threads; {'reference test helpers (double precision) for norm, RoPE, FP8 KV, SwiGLU; ' if kind == 'reference' else ''}"
-                      f"oracle port for INT8 quantisation and the gather (the reference has no host code for them)"}
+                      f"oracle port for INT8 quantisation and the gather (the reference has no host code for them); "
+                      f"{'RoPE through the plain-theta table its host helper builds (no llama3 rescaling), ' if kind == 'reference' else ''}"
+                      f"gather from a 4096-row window of the table"}
 
 
 def run_reference_arm(args, cfg):
@@ -259,7 +283,8 @@ def run_reference_arm(args, cfg):
     ms = total / args.steps * 1e3
     value = rows * per_row / (total / args.steps) / 1e9
     sample = (f"each step = {rows} of {cfg.tokens} token rows through the four ops on {threads} host threads "
-              f"(reference test helpers where the reference has host code, oracle port for INT8 quantisation and gather)")
+              f"(reference test helpers where the reference has host code, oracle port for INT8 quantisation and gather; "
+              f"RoPE through the plain-theta table the reference's host helper builds, gather from a 4096-row window of the table)")
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f64",
@@ -342,10 +367,7 @@ def main():
 
     for _ in range(max(args.warmup, 3)):
         step()
-    # ---- timed region: K steps, an event after every launch so each kernel's duration is known ----
     K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
-    launches = 0
     # The timed loop calls the C ABI directly with pre-resolved device pointers (the Python mirror in
     # runtherder_b200.kernels adds ~10 us of argument checking per call, which matters once a GPU's share
     # of a step shrinks to ~200 us at 8 GPUs).
@@ -363,29 +385,50 @@ def main():
                             P(outs["v_scale"]), P(outs["at_pos"]), rows, cfg.q_heads, cfg.kv_heads, cfg.head_dim, sp)),
         (L.rh_swiglu_quant_int8, (P(outs["q_mlp"]), P(outs["s_mlp"]), None, P(ins["gate"]), P(ins["up"]), rows, cfg.inter, sp)),
     ]
+    # ---- timed regions: K steps each, nothing but the four launches per step between the two events, so the
+    # kernels keep their programmatic-dependent-launch overlap; a barrier and a synchronise on both sides ----
     status = 0
-    barrier()
+    launches = 0
+    region_ms = []
+    t_enqueue = 0.0
     with ClockSampler(local_rank) as clocks:
-        t_enqueue = time.perf_counter()
-        for s in range(K):
-            e = ev[s]
-            e[0].record()
-            for j, (fn, fargs) in enumerate(calls):
-                status |= fn(*fargs)
-                e[j + 1].record()
-            launches += 4
-        t_enqueue = time.perf_counter() - t_enqueue
-        torch.cuda.synchronize()
+        for _ in range(max(1, args.repeats)):
+            first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            t0 = time.perf_counter()
+            first.record()
+            for _s in range(K):
+                for fn, fargs in calls:
+                    status |= fn(*fargs)
+            last.record()
+            t_enqueue += time.perf_counter() - t0
+            torch.cuda.synchronize()
+            barrier()
+            region_ms.append(max_over_ranks(first.elapsed_time(last)))
+            launches += 4 * K
     if status != 0:
         raise SystemExit("a kernel call failed: " + L.rh_last_error_string().decode())
-    elapsed_ms = ev[0][0].elapsed_time(ev[K - 1][4])
+    per_step = sorted(ms / K for ms in region_ms)
+    ms_per_step = statistics.median(per_step)
+    spread = {"repeats": len(per_step), "ms_per_step_all": [round(ms / K, 4) for ms in region_ms],
+              "min": round(per_step[0], 4), "max": round(per_step[-1], 4),
+              "iqr": round(per_step[(3 * len(per_step)) // 4] - per_step[len(per_step) // 4], 4)}
+
+    # ---- per-kernel pass (not part of the timed regions): an event after every launch ----
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
     barrier()
-    elapsed_ms = max_over_ranks(elapsed_ms)
-    op_ms = [statistics.mean(ev[s][j].elapsed_time(ev[s][j + 1]) for s in range(K)) for j in range(4)]
+    for s_ in range(K):
+        e_ = ev[s_]
+        e_[0].record()
+        for j, (fn, fargs) in enumerate(calls):
+            status |= fn(*fargs)
+            e_[j + 1].record()
+    torch.cuda.synchronize()
+    barrier()
+    op_ms = [statistics.median(ev[s_][j].elapsed_time(ev[s_][j + 1]) for s_ in range(K)) for j in range(4)]
     op_ms = [max_over_ranks(m) for m in op_ms]
 
     peak, peak_kind = measured_peak()
-    ms_per_step = elapsed_ms / K
     total_bytes = T * per_row
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
     op_table = {}
@@ -397,11 +440,12 @@ def main():
     dom = max(range(4), key=lambda j: op_ms[j])
     dom_name, dom_bpr = ops[dom]
     achieved = rows * dom_bpr / (op_ms[dom] * 1e-3) / 1e9
-    traffic = DRAM_TRAFFIC_BYTES_PER_ROW.get(dom_name)
-    traffic = None if traffic is None or args.config != "c4" else traffic * rows
+    traffic = dram_traffic_per_row(dom_name, rows) if args.config == "c4" else None
+    traffic = None if traffic is None else int(traffic * rows)
     roofline = {"bound": "hbm", "kernel": dom_name, "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": traffic,
-                "algorithmic_bytes_per_launch": rows * dom_bpr}
+                "algorithmic_bytes_per_launch": rows * dom_bpr,
+                "timing": "median launch duration of the per-kernel pass (an event after every launch), separate from the timed regions"}
 
     line = {"metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
@@ -409,9 +453,13 @@ def main():
             "data": "synthetic", "token_rows_per_s": round(T / (ms_per_step * 1e-3), 1),
             "frac_of_hbm_peak": {peak_kind: round(value / (peak * world), 4),
                                  "nominal_8TBs": round(value / (NOMINAL_HBM_GBS * world), 4)},
-            "config": sweep_config(cfg, world, rows),
+            "config": sweep_config(cfg, world, rows), "timed_regions": spread,
             "ops": op_table, "roofline": roofline, "gpu_launches": launches, "clocks": clocks.summary(),
-            "host_enqueue_us_per_step": round(t_enqueue / K * 1e6, 1)}
+            "host_enqueue_us_per_step": round(t_enqueue / (K * max(1, args.repeats)) * 1e6, 1)}
+
+    # ---- N > 1: the shards' bytes against the same rows computed on rank 0 alone ----
+    if world > 1 and not args.no_verify:
+        line["verify"] = verify_shards(cfg, ins, outs, b, rows, world, rank, dev, calls)
 
     # ---- the reference's own CUDA kernels on the same buffers (rank 0, N=1) ----
     if world == 1 and not args.no_refcuda:
@@ -427,11 +475,77 @@ def main():
 
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(cfg, args.cpu_seconds)
+    # ---- secondary: the attention kernels over the FP8 cache (the consumers of this path's bytes), N = 1 ----
+    if world == 1 and not args.no_secondary and args.config == "c4" and not args.rows:
+        del ins, outs
+        torch.cuda.empty_cache()
+        line["secondary"] = secondary_attention(args, dev)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def secondary_attention(args, dev):
+    """Short timings of the two attention kernels on their own configurations, appended to the sweep line so
+    that one bench run records them: causal prefill on the Qwen3-8B prefill shape (TFLOP/s) and the split-KV
+    decode at depth 8196 inside a 28-layer CUDA graph (us per call).  Not part of the headline metric."""
+    import copy
+    from runtherder_b200.configs import CONFIGS
+    sub = copy.copy(args)
+    sub.steps, sub.warmup, sub.no_refcuda, sub.no_cpu, sub.depth = 10, 3, True, True, 0
+    out = {}
+    for key, cfg_name, fn in (("prefill_c3", "c3", run_prefill_attention), ("decode_c2", "c2", run_decode_attention)):
+        try:
+            ln = fn(sub, CONFIGS[cfg_name], dev, emit=False)
+            out[key] = {k: ln[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "config", "roofline", "gpu_launches")
+                        if k in ln}
+            if "us_per_call" in ln:
+                out[key]["us_per_call"] = ln["us_per_call"]
+        except Exception as exc:
+            out[key] = {"unavailable": str(exc)[:200]}
+    return out
+
+
+def verify_shards(cfg, ins, outs, begin, rows, world, rank, dev, calls):
+    """After an N-GPU run: for a window of rows around every shard boundary (and the first and last rows),
+    gather each output's rows over NCCL from the ranks that own them and compare them, bit for bit, with
+    the same rows computed by rank 0 alone from freshly generated inputs.  The rotated q is produced in
+    place (and therefore re-rotated by every step), so its comparison uses a fresh single pass on every
+    rank; all other outputs are the timed buffers themselves."""
+    import torch
+    from runtherder_b200 import host_path, layer_ops, synth
+    from runtherder_b200.sharding import boundary_windows, gather_window
+    T = cfg.tokens
+    names = ["emb", "h_attn", "q_attn_in", "s_attn_in", "k_cache", "k_scale", "v_cache", "v_scale", "q_mlp", "s_mlp"]
+    weights = {k: ins[k] for k in ("g_attn", "inv_freq", "table")}
+    ok, checked_rows, bad = True, 0, []
+    # a fresh single pass over this rank's rows for the in-place output
+    q_fresh = synth.make_inputs(cfg, rows=rows, row_offset=begin, device=dev, with_table=False)
+    q_fresh.update(weights)
+    scratch = layer_ops.alloc_outputs(cfg, rows, device=dev, slots=rows)
+    host_path.sweep_step(cfg, q_fresh, scratch)
+    torch.cuda.synchronize()
+    local = {n: outs[n] for n in names}
+    local["q_rot"] = q_fresh["q"]
+    for lo, hi in boundary_windows(T, world, half_width=64):
+        gathered = {n: gather_window(t, T, lo, hi) for n, t in local.items()}
+        if rank == 0:
+            one = synth.make_inputs(cfg, rows=hi - lo, row_offset=lo, device=dev, with_table=False)
+            one.update(weights)
+            ref = layer_ops.alloc_outputs(cfg, hi - lo, device=dev, slots=hi - lo)
+            host_path.sweep_step(cfg, one, ref)
+            torch.cuda.synchronize()
+            ref["q_rot"] = one["q"]
+            for n, g in gathered.items():
+                same = torch.equal(g.contiguous().view(torch.uint8), ref[n].contiguous().view(torch.uint8))
+                if not same:
+                    ok = False
+                    bad.append(f"{n}[{lo}:{hi}]")
+            checked_rows += hi - lo
+    return {"ok": ok, "rows": checked_rows, "outputs": list(local.keys()), "mismatches": bad[:8],
+            "how": "rows around every shard boundary gathered over NCCL from their owners vs the same rows computed on rank 0 alone, bitwise"}
 
 
 def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
@@ -545,7 +659,7 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
         print(json.dumps(line), flush=True)
 
 
-def run_decode_attention(args, cfg, dev):
+def run_decode_attention(args, cfg, dev, emit=True):
     """Secondary measurement: one decode step's attention per layer — rh_flash_decode_split_bf16 over a
     seeded FP8 cache of `depth` keys, one distinct cache per layer (28 x 16.8 MB at the decode config, more
     than L2), replayed as one CUDA graph like the reference's decode loop.  Algorithmic bytes per call: the K
@@ -644,7 +758,9 @@ def run_decode_attention(args, cfg, dev):
                                     "sample": f"one call ({depth} keys, {Hq} heads) of the double-precision oracle, {dt:.2f} s"}
         except Exception as exc:
             line["cpu_baseline"] = {"unavailable": str(exc)[:200]}
-    print(json.dumps(line), flush=True)
+    if emit:
+        print(json.dumps(line), flush=True)
+    return line
 
 
 def measured_tensor_peak():
@@ -657,7 +773,7 @@ def measured_tensor_peak():
     return 1590.0, "fallback"
 
 
-def run_prefill_attention(args, cfg, dev):
+def run_prefill_attention(args, cfg, dev, emit=True):
     """Secondary measurement: the causal prefill attention of one layer — rh_flash_prefill_bf16 on `tokens` new
     tokens over an (initially empty) FP8 cache, a few distinct q/cache sets used in turn.  FLOPs per call:
     4 * head_dim * q_heads * T (T + 1) / 2 (both products, causal half)."""
@@ -747,7 +863,9 @@ def run_prefill_attention(args, cfg, dev):
                                     "sample": f"the last {n_s} of {T} tokens through the double-precision oracle, {dt:.2f} s"}
         except Exception as exc:
             line["cpu_baseline"] = {"unavailable": str(exc)[:200]}
-    print(json.dumps(line), flush=True)
+    if emit:
+        print(json.dumps(line), flush=True)
+    return line
 
 
 def chain_roofline(cfg, i, o, rows, peak, peak_kind):

@@ -43,6 +43,16 @@ typedef enum rh_status {
 #define RH_MAX_HEAD_DIM 256  /* reference: rope.cu:12 */
 
 int rh_version(void);
+
+/* Optional one-time preparation of `device` (host-side; may be called from any thread, any number of
+ * times): loads the code of every kernel of this library onto the device, opts the kernels that need it
+ * in to their dynamic shared memory, caches the occupancy figures their grids are sized with, the SM
+ * count and the address of the device error word.  After it, no launch on that device has first-use work
+ * left, so even the very first call of an entry point may happen inside stream capture.  Without it each
+ * kernel does the same work on its first launch per device (harmless outside capture: the reference runs
+ * its first decode step eagerly, src/engine/generator.cu:54-58).  The current device is left unchanged.
+ * No counterpart in the reference (its kernels need no set-up). */
+int rh_init(int device);
 const char* rh_status_string(int status);
 const char* rh_last_error_string(void);
 
@@ -59,6 +69,15 @@ int rh_rmsnorm_bf16(void* y, const void* x, const void* g, int num_tokens, int h
  * Replaces rmsnorm_add_bf16_forward (rmsnorm.cuh:36-45, rmsnorm.cu:226-238). */
 int rh_rmsnorm_add_bf16(void* y, void* h_out, const void* x, const void* residual, const void* g,
                         int num_tokens, int hidden_dim, float eps, void* stream);
+
+/* The forward pass's final norm when only the last token feeds lm_head: y_last[hidden_dim] is row
+ * num_tokens-1 of what rh_rmsnorm_add_bf16 would write to y for x, residual [num_tokens, hidden_dim];
+ * no other row is read, nothing else is written.  Stands in for the rmsnorm_add_bf16_forward call plus
+ * the `normed + (n-1) * hidden_dim` slice at src/model/supported/llama/llama3.cu:254-263 (and the same
+ * lines of qwen2.cu / qwen3.cu), which normalise all n rows and rewrite the residual stream although
+ * nothing reads either again: 8 * hidden_dim * (n-1) bytes per forward at prefill. */
+int rh_rmsnorm_add_last_row_bf16(void* y_last, const void* x, const void* residual, const void* g,
+                                 int num_tokens, int hidden_dim, float eps, void* stream);
 
 /* Per-token symmetric INT8: x_scale = amax/127, q = clamp(rn(x * (127/amax)), -127, 127);
  * a zero row gives scale 0 and codes 0.
@@ -240,10 +259,10 @@ int rh_selftest_static(unsigned int* mismatches_host, int num_counters, void* st
  * Synchronises the device. */
 int rh_device_error(int* error_host);
 
-/* Failure-detection self-check: one warp waits, with a limit of `polls` (1..65536) polls, on a
- * barrier that nothing completes.  The wait must run out: *gave_up_host becomes 1, *error_host the
- * recorded error word (non-zero), the kernel returns normally and the context stays usable.  The
- * sticky device error word is restored afterwards.  Diagnostic: allocates, synchronises. */
+/* Failure-detection self-check: one warp waits, with a limit of `polls` (1..65536) polls of up to 20 us
+ * each, on a barrier that nothing completes.  The wait must run out: *gave_up_host becomes 1, *error_host
+ * the error word the probe recorded (non-zero; a private word — the sticky device error word is not
+ * touched), the kernel returns normally and the context stays usable.  Diagnostic: allocates, synchronises. */
 int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host);
 
 /* ---- Tuning knobs (process-wide; for experiments, defaults are the tuned values) --------- */

@@ -21,10 +21,12 @@ _ll, _sz, _u64, _i32 = C.c_longlong, C.c_size_t, C.c_uint64, C.c_int32
 # name -> argtypes; every function returns int unless listed in _RESTYPES
 SIGNATURES = {
     "rh_version": [],
+    "rh_init": [_i],
     "rh_status_string": [_i],
     "rh_last_error_string": [],
     "rh_rmsnorm_bf16": [_p, _p, _p, _i, _i, _f, _p],
     "rh_rmsnorm_add_bf16": [_p, _p, _p, _p, _p, _i, _i, _f, _p],
+    "rh_rmsnorm_add_last_row_bf16": [_p, _p, _p, _p, _i, _i, _f, _p],
     "rh_quantize_per_token_int8": [_p, _p, _p, _i, _i, _p],
     "rh_dequantize_w8a8": [_p, _p, _p, _p, _i, _i, _p],
     "rh_quantize_kv_fp8": [_p, _p, _p, _p, _i, _i, _i, _p],

@@ -1,4 +1,5 @@
-"""Builds librh_kernels.so in-tree with nvcc for sm_100a.
+"""Builds librh_kernels.so (the kernels) and librh_linear.so (the W8A8 linear wrapper, which adds the
+cuBLASLt dependency) in-tree with nvcc for sm_100a.
 
 Usage: python -m runtherder_b200.build [--force] [--verbose]
 
@@ -20,6 +21,8 @@ CSRC = PKG / "csrc"
 OUT = PKG / "_C"
 INCLUDE = PKG.parent / "include"
 LIB = OUT / "librh_kernels.so"
+LINEAR_LIB = OUT / "librh_linear.so"
+LINEAR_SOURCES = ["linear_w8a8.cu"]
 
 SOURCES = ["capi.cu", "rows.cu", "swiglu.cu", "rope_kv.cu", "embedding.cu", "flash_decode.cu", "flash_prefill.cu", "flash_prefill_tc.cu", "synth.cu", "dropin.cu", "selftest_static.cu"]
 
@@ -64,12 +67,24 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
         objs = list(pool.map(compile_one, SOURCES))
+        linear_objs = list(pool.map(compile_one, LINEAR_SOURCES))
     if force or _stale(LIB, objs):
         cmd = [cc, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link of librh_kernels.so failed")
+    if force or _stale(LINEAR_LIB, linear_objs + [LIB]):
+        # The wrapper resolves the kernels from librh_kernels.so beside it and cuBLASLt from the process
+        # (a Python process that imported torch has libcublasLt.so.12 mapped already) or the CUDA toolkit.
+        cuda_lib = str(Path(cc).resolve().parent.parent / "lib64")
+        cmd = [cc, "-shared", "-o", str(LINEAR_LIB), *map(str, linear_objs), f"-L{OUT}", "-lrh_kernels",
+               f"-L{cuda_lib}", "-lcublasLt", "-cudart", "static",
+               "-Xlinker", "-rpath=$ORIGIN", "-Xlinker", f"-rpath={cuda_lib}"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("link of librh_linear.so failed")
     return LIB
 
 

@@ -6,6 +6,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
 
 #include "rh_common.cuh"
 
@@ -61,6 +65,64 @@ int resident_ctas(const void* kernel, int threads, size_t dyn_smem) {
 
 int tuning(int slot) { return g_tuning[slot].load(std::memory_order_relaxed); }
 
+namespace {
+struct SetupKey {
+    const void* kernel;
+    int device;
+    size_t smem;
+    bool operator<(const SetupKey& o) const { return std::tie(kernel, device, smem) < std::tie(o.kernel, o.device, o.smem); }
+};
+struct Registered {
+    const void* kernel;
+    int threads;
+    size_t smem;
+};
+std::mutex& setup_mutex() { static std::mutex m; return m; }
+std::map<SetupKey, int>& setup_table() { static std::map<SetupKey, int> t; return t; }
+std::vector<Registered>& registry() { static std::vector<Registered> r; return r; }
+}  // namespace
+
+int kernel_setup(const void* kernel, int threads, size_t dyn_smem) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+    const SetupKey key{kernel, dev, dyn_smem};
+    std::lock_guard<std::mutex> lock(setup_mutex());
+    auto& table = setup_table();
+    const auto it = table.find(key);
+    if (it != table.end()) return it->second;
+    // Dynamic plus static shared memory beyond 48 KB needs the opt-in; asking for what the launch will use
+    // is always allowed, so ask whenever there is a dynamic part.
+    if (dyn_smem > 0 &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dyn_smem)) != cudaSuccess)
+        (void)cudaGetLastError();
+    const int resident = resident_ctas(kernel, threads, dyn_smem);
+    table.emplace(key, resident);
+    return resident;
+}
+
+int register_kernel(const void* kernel, int threads, size_t dyn_smem) {
+    std::lock_guard<std::mutex> lock(setup_mutex());
+    registry().push_back(Registered{kernel, threads, dyn_smem});
+    return 0;
+}
+
+int setup_all_registered() {
+    std::vector<Registered> list;
+    {
+        std::lock_guard<std::mutex> lock(setup_mutex());
+        list = registry();
+    }
+    for (const Registered& r : list) {
+        if (r.threads > 0) {
+            (void)kernel_setup(r.kernel, r.threads, r.smem);
+        } else {   // no set-up of its own: asking for its attributes makes the runtime load its code
+            cudaFuncAttributes attrs;
+            if (cudaFuncGetAttributes(&attrs, r.kernel) != cudaSuccess) (void)cudaGetLastError();
+        }
+    }
+    return static_cast<int>(list.size());
+}
+
 int* device_error_word() {
     static std::atomic<int*> cache[kMaxDevices];
     int dev = 0;
@@ -82,21 +144,7 @@ namespace {
 // operand they can meet: all 65536 bf16 gate values for the sigmoid reciprocal, all non-NaN
 // non-negative bf16 values for the quantisation scale and inverse scale.
 __global__ void selftest_kernel(unsigned int* mismatches) {
-    const unsigned int bits = blockIdx.x * blockDim.x + threadIdx.x;   // 0 .. 65535
-    const float g = __uint_as_float(bits << 16);
-    if (g >= kGateExactBelow) {   // the range the kernels send down the refined-reciprocal path (NaN excluded)
-        const unsigned int want = __float_as_uint(sigmoid_reference(g));
-        if (__float_as_uint(sigmoid2<1>(splat2(g)).x) != want) atomicAdd(&mismatches[0], 1u);
-        if (__float_as_uint(sigmoid2<2>(splat2(g)).y) != want) atomicAdd(&mismatches[1], 1u);
-    }
-    if (bits <= 0x7f80u) {                                             // +0 .. +Inf
-        const float amax = g;
-        const float inv127 = (amax > 0.0f) ? (127.0f / amax) : 0.0f, inv448 = (amax > 0.0f) ? (448.0f / amax) : 0.0f;
-        if (__float_as_uint(quant_inv_scale<127>(amax)) != __float_as_uint(inv127)) atomicAdd(&mismatches[2], 1u);
-        if (__float_as_uint(quant_inv_scale<448>(amax)) != __float_as_uint(inv448)) atomicAdd(&mismatches[3], 1u);
-        if (__float_as_uint(quant_scale<127>(amax)) != __float_as_uint(amax / 127.0f)) atomicAdd(&mismatches[4], 1u);
-        if (__float_as_uint(quant_scale<448>(amax)) != __float_as_uint(amax / 448.0f)) atomicAdd(&mismatches[5], 1u);
-    }
+    selftest_checks(blockIdx.x * blockDim.x + threadIdx.x, [&](int slot) { atomicAdd(&mismatches[slot], 1u); });
 }
 
 }  // namespace
@@ -110,6 +158,10 @@ extern "C" int rh_selftest(unsigned int* mismatches_host) {
     if (cudaMalloc(&dev, 8 * sizeof(unsigned int)) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selftest: cudaMalloc failed");
     cudaMemset(dev, 0, 8 * sizeof(unsigned int));
     selftest_kernel<<<256, 256>>>(dev);
+    if (int e = host::check_launch("selftest_kernel")) {
+        cudaFree(dev);
+        return e;
+    }
     const cudaError_t err = cudaMemcpy(mismatches_host, dev, 8 * sizeof(unsigned int), cudaMemcpyDeviceToHost);
     cudaFree(dev);
     if (err != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selftest: %s", cudaGetErrorString(err));
@@ -136,20 +188,22 @@ __global__ void bounded_wait_probe_kernel(int polls, int* error_word, int* gave_
 extern "C" int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host) {
     RH_REQUIRE(gave_up_host && error_host, RH_ERR_INVALID_ARG, "rh_selfcheck_bounded_wait: null pointer");
     RH_REQUIRE(polls >= 1 && polls <= (1 << 16), RH_ERR_INVALID_ARG, "rh_selfcheck_bounded_wait: polls must be in 1..65536");
-    int* word = host::device_error_word();
-    RH_REQUIRE(word != nullptr, RH_ERR_CUDA, "rh_selfcheck_bounded_wait: error word unavailable");
-    int* flag = nullptr;
-    if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selfcheck_bounded_wait: cudaMalloc failed");
-    int saved = 0;
-    cudaMemcpy(&saved, word, sizeof(int), cudaMemcpyDeviceToHost);
-    cudaMemset(word, 0, sizeof(int));
-    cudaMemset(flag, 0, sizeof(int));
-    bounded_wait_probe_kernel<<<1, 32>>>(polls, word, flag);
-    cudaError_t err = cudaMemcpy(gave_up_host, flag, sizeof(int), cudaMemcpyDeviceToHost);
-    if (err == cudaSuccess) err = cudaMemcpy(error_host, word, sizeof(int), cudaMemcpyDeviceToHost);
-    cudaMemcpy(word, &saved, sizeof(int), cudaMemcpyHostToDevice);   // the probe leaves the sticky word as it found it
-    cudaFree(flag);
+    // The probe records into a private word, not the sticky per-device one, so an error that a kernel on
+    // another stream reports meanwhile is neither lost nor mistaken for the probe's.
+    int* scratch = nullptr;   // [0] gave-up flag, [1] the probe's error word
+    if (cudaMalloc(&scratch, 2 * sizeof(int)) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selfcheck_bounded_wait: cudaMalloc failed");
+    cudaMemset(scratch, 0, 2 * sizeof(int));
+    bounded_wait_probe_kernel<<<1, 32>>>(polls, scratch + 1, scratch);
+    if (int e = host::check_launch("bounded_wait_probe_kernel")) {
+        cudaFree(scratch);
+        return e;
+    }
+    int result[2] = {0, 0};
+    const cudaError_t err = cudaMemcpy(result, scratch, sizeof(result), cudaMemcpyDeviceToHost);
+    cudaFree(scratch);
     if (err != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selfcheck_bounded_wait: %s", cudaGetErrorString(err));
+    *gave_up_host = result[0];
+    *error_host = result[1];
     return RH_OK;
 }
 
@@ -162,7 +216,23 @@ extern "C" int rh_device_error(int* error_host) {
     return RH_OK;
 }
 
-extern "C" int rh_version(void) { return 100; }
+extern "C" int rh_init(int device) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_init: no CUDA device");
+    RH_REQUIRE(device >= 0 && device < count, RH_ERR_INVALID_ARG, "rh_init: device %d out of range (0..%d)", device, count - 1);
+    int previous = 0;
+    if (cudaGetDevice(&previous) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_init: cudaGetDevice failed");
+    if (cudaSetDevice(device) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_init: cudaSetDevice(%d) failed", device);
+    (void)host::num_sms();
+    const bool word_ok = host::device_error_word() != nullptr;
+    (void)host::setup_all_registered();
+    (void)cudaGetLastError();
+    (void)cudaSetDevice(previous);
+    if (!word_ok) return host::fail(RH_ERR_CUDA, "rh_init: the device error word is unavailable on device %d", device);
+    return RH_OK;
+}
+
+extern "C" int rh_version(void) { return 101; }
 
 extern "C" const char* rh_status_string(int status) {
     switch (status) {
@@ -181,9 +251,9 @@ extern "C" const char* rh_last_error_string(void) { return host::g_last_error; }
 extern "C" int rh_tune(const char* key, int value) {
     static const char* const kNames[host::kTuneSlots] = {"rows_ctas_per_sm", "swiglu_ctas_per_sm",
                                                          "rope_warps_per_cta", "embed_ctas_per_sm",
-                                                         "elem_ctas_per_sm", "swiglu_threads",
-                                                         "swiglu_rcp_steps", "rows_stages", "swiglu_stages",
-                                                         "rows_smem_h", "rows_prefetch", "swiglu_prefetch", "no_pdl", "prefill_tiles", "prefill_parts"};
+                                                         "elem_ctas_per_sm", "(unused)",
+                                                         "swiglu_rcp_steps", "(unused)", "swiglu_stages",
+                                                         "rows_smem_h", "rows_prefetch", "row_tickets", "no_pdl", "prefill_tiles", "prefill_parts"};
     RH_REQUIRE(key != nullptr, RH_ERR_INVALID_ARG, "rh_tune: null key");
     for (int i = 0; i < host::kTuneSlots; ++i) {
         if (std::strcmp(key, kNames[i]) == 0) {

@@ -148,7 +148,7 @@ extern "C" int rh_stage_positions(int* positions, int* decode_pos_or_null, int s
     RH_REQUIRE(positions != nullptr, RH_ERR_INVALID_ARG, "rh_stage_positions: null pointer");
     RH_REQUIRE(n >= 1, RH_ERR_INVALID_ARG, "rh_stage_positions: stage needs at least one token");
     RH_REQUIRE(start_pos >= 0, RH_ERR_INVALID_ARG, "rh_stage_positions: start_pos must be >= 0");
-    host::launch(stage_positions_kernel, dim3((n + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), positions, decode_pos_or_null, start_pos, n);
+    host::launch<stage_positions_kernel>(dim3((n + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), positions, decode_pos_or_null, start_pos, n);
     return host::check_launch("stage_positions_kernel");
 }
 
@@ -157,7 +157,7 @@ extern "C" int rh_decode_advance(int* token_slot_or_null, int* position_or_null,
     RH_REQUIRE(position_or_null || decode_pos_or_null || token_slot_or_null, RH_ERR_INVALID_ARG,
                "rh_decode_advance: nothing to advance");
     RH_REQUIRE(step >= 0, RH_ERR_INVALID_ARG, "rh_decode_advance: step must be >= 0");
-    host::launch(decode_advance_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), token_slot_or_null, position_or_null,
+    host::launch<decode_advance_kernel>(dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), token_slot_or_null, position_or_null,
                                                                          decode_pos_or_null, next_token_or_null, step);
     return host::check_launch("decode_advance_kernel");
 }
@@ -177,7 +177,7 @@ extern "C" int rh_qkv_bias_add_bf16(void* q, void* k, void* v, const void* q_bia
     long long grid = (total + 255) / 256;
     const long long cap = static_cast<long long>(host::num_sms()) * 16;
     if (grid > cap) grid = cap;
-    host::launch(qkv_bias_add_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, static_cast<cudaStream_t>(stream), 
+    host::launch<qkv_bias_add_kernel>(dim3(static_cast<unsigned>(grid)), dim3(256), 0, static_cast<cudaStream_t>(stream), 
         static_cast<uint4*>(q), static_cast<uint4*>(k), static_cast<uint4*>(v), static_cast<const uint4*>(q_bias),
         static_cast<const uint4*>(k_bias), static_cast<const uint4*>(v_bias), total, q_vecs, kv_vecs);
     return host::check_launch("qkv_bias_add_kernel");
@@ -195,7 +195,7 @@ extern "C" int rh_embedding_lookup_bf16(void* out, const void* table, const int*
     if (per_sm <= 0) per_sm = 64;   // pure copy: resident CTAs = bytes in flight
     const long long cap = static_cast<long long>(host::num_sms()) * per_sm;
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
-    host::launch(embedding_kernel, dim3(grid), dim3(kEmbThreads), 0, static_cast<cudaStream_t>(stream), 
+    host::launch<embedding_kernel>(dim3(grid), dim3(kEmbThreads), 0, static_cast<cudaStream_t>(stream), 
         static_cast<uint4*>(out), static_cast<const uint4*>(table), token_ids, num_tokens, hidden_dim / kVec);
     return host::check_launch("embedding_kernel");
 }
@@ -213,10 +213,10 @@ extern "C" int rh_dequantize_w8a8(void* y, const int32_t* acc, const float* x_sc
     if (grid > cap) grid = cap;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (vec4)
-        host::launch(dequant_w8a8_kernel<true>, dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
+        host::launch<dequant_w8a8_kernel<true>>(dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
             static_cast<__nv_bfloat16*>(y), acc, x_scale, static_cast<const __nv_bfloat16*>(w_scale), m, n);
     else
-        host::launch(dequant_w8a8_kernel<false>, dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
+        host::launch<dequant_w8a8_kernel<false>>(dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
             static_cast<__nv_bfloat16*>(y), acc, x_scale, static_cast<const __nv_bfloat16*>(w_scale), m, n);
     return host::check_launch("dequant_w8a8_kernel");
 }

@@ -623,18 +623,8 @@ template <int D, bool kWide>
 void launch_partial_as(const FdArgs& a, cudaStream_t stream) {
     const dim3 grid(static_cast<unsigned>(a.num_kv_heads * a.row_chunks), static_cast<unsigned>(a.num_splits));
     constexpr int smem = FdRing<D>::kSmemBytes;
-    if constexpr (smem > 48 * 1024) {   // opt in once per device; the attribute is per device and idempotent
-        static std::atomic<unsigned> configured{0};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        const unsigned bit = 1u << (dev & 31);
-        if ((configured.load(std::memory_order_relaxed) & bit) == 0) {
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(&flash_decode_partial_kernel<D, kWide>),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-            configured.fetch_or(bit, std::memory_order_relaxed);
-        }
-    }
-    host::launch(flash_decode_partial_kernel<D, kWide>, grid, dim3(kFdThreads), static_cast<size_t>(smem), stream, a);
+    (void)host::setup<&flash_decode_partial_kernel<D, kWide>, kFdThreads, static_cast<size_t>(smem)>();   // shared-memory opt-in, once per device
+    host::launch<flash_decode_partial_kernel<D, kWide>>(grid, dim3(kFdThreads), static_cast<size_t>(smem), stream, a);
 }
 
 template <int D>
@@ -699,10 +689,10 @@ extern "C" int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_
     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
     const float* part = partial;
     switch (head_dim) {
-        case 32: host::launch(flash_decode_reduce_kernel<32>, rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
-        case 64: host::launch(flash_decode_reduce_kernel<64>, rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
-        case 128: host::launch(flash_decode_reduce_kernel<128>, rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
-        default: host::launch(flash_decode_reduce_kernel<256>, rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
+        case 32: host::launch<flash_decode_reduce_kernel<32>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
+        case 64: host::launch<flash_decode_reduce_kernel<64>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
+        case 128: host::launch<flash_decode_reduce_kernel<128>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
+        default: host::launch<flash_decode_reduce_kernel<256>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
     }
     return host::check_launch(fn);
 }

@@ -393,21 +393,12 @@ int launch_prefill(PfArgs a, cudaStream_t stream, const char* fn) {
     const int warps = a.heads_per_cta * a.subs;
     const int tokens_per_cta = 16 * kMT * a.subs;
     const int smem = PfSmem<kMT>::bytes(warps);
-    {   // opt in to the shared memory once per device
-        static std::atomic<unsigned> configured{0};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        const unsigned bit = 1u << (dev & 31);
-        if ((configured.load(std::memory_order_relaxed) & bit) == 0) {
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(&flash_prefill_kernel<kMT>),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<kMT>::bytes(kPfMaxWarps));
-            configured.fetch_or(bit, std::memory_order_relaxed);
-        }
-    }
+    // opt in to the largest shared-memory request of this form, once per device
+    (void)host::setup<&flash_prefill_kernel<kMT>, kPfMaxWarps * 32, static_cast<size_t>(PfSmem<kMT>::bytes(kPfMaxWarps))>();
     const dim3 grid(static_cast<unsigned>((a.n_new + tokens_per_cta - 1) / tokens_per_cta),
                     static_cast<unsigned>(a.num_kv_heads * a.head_chunks));
     RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
-    host::launch(flash_prefill_kernel<kMT>, grid, dim3(static_cast<unsigned>(warps * 32)), static_cast<size_t>(smem), stream, a);
+    host::launch<flash_prefill_kernel<kMT>>(grid, dim3(static_cast<unsigned>(warps * 32)), static_cast<size_t>(smem), stream, a);
     return host::check_launch(fn);
 }
 

@@ -604,21 +604,17 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     const int knob = host::tuning(host::kPrefillParts);
     const int parts = knob >= 20 ? knob - 20 : knob;
     const size_t smem = knob >= 20 ? 120u * 1024u : static_cast<size_t>(tc::kSmemBytes);
-    auto go = [&](auto kernel, int threads) {
-        static std::atomic<unsigned> configured[3];      // per kernel form: the devices already set up
-        std::atomic<unsigned>& done = configured[threads >> 8];
-        int dev = 0;
-        cudaGetDevice(&dev);
-        const unsigned bit = 1u << (dev & 31);
-        if ((done.load(std::memory_order_relaxed) & bit) == 0) {
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
-            done.fetch_or(bit, std::memory_order_relaxed);
-        }
-        host::launch(kernel, grid, dim3(threads), smem, stream, a);
-    };
-    if (parts == 1) go(tc::flash_prefill_tc_kernel<1>, 128);
-    else if (parts == 4) go(tc::flash_prefill_tc_kernel<4>, 512);
-    else go(tc::flash_prefill_tc_kernel<2>, 256);
+    constexpr size_t kOptIn = 120u * 1024u;   // the padded request is the largest one
+    if (parts == 1) {
+        (void)host::setup<&tc::flash_prefill_tc_kernel<1>, 128, kOptIn>();
+        host::launch<tc::flash_prefill_tc_kernel<1>>(grid, dim3(128), smem, stream, a);
+    } else if (parts == 4) {
+        (void)host::setup<&tc::flash_prefill_tc_kernel<4>, 512, kOptIn>();
+        host::launch<tc::flash_prefill_tc_kernel<4>>(grid, dim3(512), smem, stream, a);
+    } else {
+        (void)host::setup<&tc::flash_prefill_tc_kernel<2>, 256, kOptIn>();
+        host::launch<tc::flash_prefill_tc_kernel<2>>(grid, dim3(256), smem, stream, a);
+    }
     return host::check_launch(fn);
 }
 

@@ -75,26 +75,37 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 // They are issued through PTX with an explicit .rn.  Beware: a paired multiply feeding a paired add
 // is merged into a paired fused multiply-add regardless (intrinsics and PTX alike), so no code here
 // lets a mul2_rn result flow straight into an add2_rn where the double rounding matters.
-__device__ __forceinline__ unsigned long long f2_bits(float2 v) {
-    return (static_cast<unsigned long long>(__float_as_uint(v.y)) << 32) | __float_as_uint(v.x);
-}
-__device__ __forceinline__ float2 bits_f2(unsigned long long b) {
-    return make_float2(__uint_as_float(static_cast<uint32_t>(b)), __uint_as_float(static_cast<uint32_t>(b >> 32)));
-}
+// The register pairs are formed inside the asm block (mov.b64 of two 32-bit registers), which costs no
+// instruction; building the 64-bit operand with shifts and ors in C++ leaves it to the optimiser.
 __device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) {
-    unsigned long long d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
-    return bits_f2(d);
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
 }
 __device__ __forceinline__ float2 add2_rn(float2 a, float2 b) {
-    unsigned long long d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
-    return bits_f2(d);
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
 }
 __device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)), "l"(f2_bits(c)));
-    return bits_f2(d);
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
 }
 __device__ __forceinline__ float2 bf2_to_f2(uint32_t w) { return make_float2(bf_lo(w), bf_hi(w)); }
 __device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
@@ -147,22 +158,29 @@ __device__ __forceinline__ uint32_t amax_acc_bf16x2(uint32_t m, uint32_t w) {
 // INT8 code of p = y*inv without the conversion unit: adding 1.5*2^23 leaves
 // round_half_even(p) in the low mantissa byte (two's complement).  |p| <= 127.0001 for a
 // finite row, so the reference's clamp never engages; valid only for finite p.
-// The product is a paired multiply, the additions are scalar: a paired add directly behind a paired
-// multiply gets merged into a paired fused multiply-add even with explicit .rn on both, and the
-// single rounding then breaks exact .5 ties (y = amax/2 gives 63.5 -> must round to 64, not 63).
-__device__ __forceinline__ float2 int8_code_fast2(uint32_t w, float2 inv2) {
-    const float2 p = mul2_rn(bf2_to_f2(w), inv2);
-    return make_float2(__fadd_rn(p.x, 12582912.0f), __fadd_rn(p.y, 12582912.0f));
+// The reference rounds twice (the product, then the conversion), so the addition must see the ROUNDED
+// product: a paired add directly behind a paired multiply gets merged into one fused multiply-add
+// (even with explicit .rn on both), whose single rounding breaks exact .5 ties (y = amax/2 gives 63.5
+// -> must round to 64, not 63).  The sequence below keeps both roundings and stays paired: the product
+// is taken with 4*inv (an exact scaling, so it rounds like y*inv), and the addition is a fused
+// multiply-add by 0.25 (exact) — a multiply cannot be merged into another multiply's operand.
+// `inv4` is 4*inv; callers check that it did not overflow.
+__device__ __forceinline__ float2 int8_code_fast2(uint32_t w, float2 inv4) {
+    return fma2_rn(mul2_rn(bf2_to_f2(w), inv4), splat2(0.25f), splat2(12582912.0f));
 }
-__device__ __forceinline__ uint2 pack_int8x8_fast(const uint4& w, float inv) {
-    const float2 inv2 = splat2(inv);
-    const float2 c0 = int8_code_fast2(w.x, inv2), c1 = int8_code_fast2(w.y, inv2);
-    const float2 c2 = int8_code_fast2(w.z, inv2), c3 = int8_code_fast2(w.w, inv2);
+__device__ __forceinline__ uint2 pack_int8x8_fast4(const uint4& w, float2 inv4) {
+    const float2 c0 = int8_code_fast2(w.x, inv4), c1 = int8_code_fast2(w.y, inv4);
+    const float2 c2 = int8_code_fast2(w.z, inv4), c3 = int8_code_fast2(w.w, inv4);
     const uint32_t lo = __byte_perm(__byte_perm(__float_as_uint(c0.x), __float_as_uint(c0.y), 0x0040),
                                     __byte_perm(__float_as_uint(c1.x), __float_as_uint(c1.y), 0x0040), 0x5410);
     const uint32_t hi = __byte_perm(__byte_perm(__float_as_uint(c2.x), __float_as_uint(c2.y), 0x0040),
                                     __byte_perm(__float_as_uint(c3.x), __float_as_uint(c3.y), 0x0040), 0x5410);
     return make_uint2(lo, hi);
+}
+// Largest inverse scale the paired sequence takes (4*inv must stay finite).
+constexpr float kFastInvMax = 8.0e37f;
+__device__ __forceinline__ uint2 pack_int8x8_fast(const uint4& w, float inv) {
+    return pack_int8x8_fast4(w, splat2(inv * 4.0f));
 }
 
 // Eight E4M3 codes (round-to-nearest-even, saturate to +-448), the conversion __nv_fp8_e4m3(float) does.
@@ -231,8 +249,46 @@ __device__ __forceinline__ float2 sigmoid2(float2 g) {
     if (kSteps >= 2) r = fma2_rn(fma2_rn(nd, r, splat2(1.0f)), r, r);
     return r;
 }
+// The fused kernels use the NEGATED sigmoid: the reciprocal is taken of -(1 + e) (the sign rides on the
+// instruction's operand), which makes the refinement r' = r + r * (1 - d * r) two paired fused
+// multiply-adds on (d, -r) with no negated copy of d.  Every step is sign-symmetric, so the result is
+// exactly -sigmoid2<1>(g); rh_selftest checks it for every gate.  Same validity range as sigmoid2.
+// (Letting two or four gates share one reciprocal — seed = reciprocal of the product times the other
+// members — was measured too: it passes the parity tests but is no faster, and seeds a few units in the
+// last place off are not provably absorbed by one refinement step for 221 of the 65536 gates.)
+__device__ __forceinline__ float2 neg_sigmoid2(float2 g) {
+    const float2 t = mul2_rn(g, splat2(-1.4426950408889634f));
+    const float2 d = add2_rn(make_float2(ex2_approx(t.x), ex2_approx(t.y)), splat2(1.0f));
+    const float2 rn = make_float2(rcp_approx(-d.x), rcp_approx(-d.y));
+    return fma2_rn(rn, fma2_rn(d, rn, splat2(1.0f)), rn);
+}
 // The reference's expression, verbatim (src/kernels/activation.cu:36).
 __device__ __forceinline__ float sigmoid_reference(float g) { return 1.0f / (1.0f + __expf(-g)); }
+
+// Exhaustive check of the division-free sequences above against IEEE division, over every operand they
+// can meet; `bits` runs over 0..65535 (one thread each) and count(slot) is called per mismatch.
+//   0, 1  sigmoid2<1>, sigmoid2<2> against the reference's expression, every bf16 gate >= kGateExactBelow
+//   2..5  kQMax/amax and amax/kQMax for 127 and 448, every non-negative bf16 amax
+//   6     neg_sigmoid2 (what the fused kernels use) against the negated reference expression
+template <typename Count>
+__device__ __forceinline__ void selftest_checks(unsigned int bits, Count count) {
+    const float g = __uint_as_float(bits << 16);
+    if (g >= kGateExactBelow) {   // the range the kernels send down the refined-reciprocal path (NaN excluded)
+        const unsigned int want = __float_as_uint(sigmoid_reference(g));
+        if (__float_as_uint(sigmoid2<1>(splat2(g)).x) != want) count(0);
+        if (__float_as_uint(sigmoid2<2>(splat2(g)).y) != want) count(1);
+        const float2 ns = neg_sigmoid2(splat2(g));
+        if (__float_as_uint(ns.x) != (want ^ 0x80000000u) || __float_as_uint(ns.y) != (want ^ 0x80000000u)) count(6);
+    }
+    if (bits <= 0x7f80u) {                                             // +0 .. +Inf
+        const float amax = g;
+        const float inv127 = (amax > 0.0f) ? (127.0f / amax) : 0.0f, inv448 = (amax > 0.0f) ? (448.0f / amax) : 0.0f;
+        if (__float_as_uint(quant_inv_scale<127>(amax)) != __float_as_uint(inv127)) count(2);
+        if (__float_as_uint(quant_inv_scale<448>(amax)) != __float_as_uint(inv448)) count(3);
+        if (__float_as_uint(quant_scale<127>(amax)) != __float_as_uint(amax / 127.0f)) count(4);
+        if (__float_as_uint(quant_scale<448>(amax)) != __float_as_uint(amax / 448.0f)) count(5);
+    }
+}
 
 // ---- reductions ----------------------------------------------------------------------------
 //
@@ -284,20 +340,43 @@ int fail(int status, const char* fmt, ...);  // records the message for rh_last_
 int check_launch(const char* what);           // cudaGetLastError -> RH_ERR_LAUNCH
 int num_sms();                                // SM count of the current device (cached per device)
 int tuning(int slot);                         // rh_tune value, 0 = use the default
-int resident_ctas(const void* kernel, int threads, size_t dyn_smem = 0);  // CTAs per SM (>= 1)
+int resident_ctas(const void* kernel, int threads, size_t dyn_smem = 0);  // CTAs per SM (>= 1), uncached query
+
+// One-time set-up of a kernel on the CURRENT device: opts in to `dyn_smem` bytes of dynamic shared memory
+// when that exceeds the 48 KB default, and asks how many CTAs of `threads` threads fit on an SM (>= 1).
+// The answer is cached per (kernel, device, dyn_smem) behind a mutex, so any host thread may call it for
+// any device; after the first call it is a table lookup.  rh_init() makes that first call for every kernel
+// the library registered, so that no launch has set-up left to do.
+int kernel_setup(const void* kernel, int threads, size_t dyn_smem = 0);
+int register_kernel(const void* kernel, int threads, size_t dyn_smem);   // adds to rh_init()'s list; returns 0
+int setup_all_registered();                                              // what rh_init() runs on the current device
+// Naming KernelAtLoad<&kernel, threads, smem>::token in a launcher registers that instantiation while the
+// library is being loaded (a static data member of a class template is initialised at load time once used).
+template <auto kKernel, int kThreads, size_t kSmem = 0>
+struct KernelAtLoad {
+    static inline const int token = register_kernel(reinterpret_cast<const void*>(kKernel), kThreads, kSmem);
+};
+// The usual launcher prologue: register at load, set up (or look up) on this device.
+template <auto kKernel, int kThreads, size_t kSmem = 0>
+inline int setup() {
+    (void)KernelAtLoad<kKernel, kThreads, kSmem>::token;
+    return kernel_setup(reinterpret_cast<const void*>(kKernel), kThreads, kSmem);
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kSwigluThreads,
-                kSwigluRcpSteps, kRowsStages, kSwigluStages, kRowsSmemH, kRowsPrefetch,
-                kSwigluPrefetch, kNoPdl, kPrefillTiles, kPrefillParts, kTuneSlots };
+enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kUnusedA,
+                kSwigluRcpSteps, kUnusedB, kSwigluStages, kRowsSmemH, kRowsPrefetch,
+                kRowTickets, kNoPdl, kPrefillTiles, kPrefillParts, kTuneSlots };
 
-// Launches `kernel` with the programmatic-stream-serialization attribute (unless rh_tune("no_pdl", 1)):
+// Launches kKernel with the programmatic-stream-serialization attribute (unless rh_tune("no_pdl", 1)):
 // the kernel may be scheduled while the previous kernel of `stream` drains; it orders itself with
 // pdl_enter().  Inside stream capture the edge becomes a programmatic dependency of the graph.
-// A failure is left in the runtime's last-error slot for check_launch().
+// A failure is left in the runtime's last-error slot for check_launch().  Every kernel launched this
+// way is on rh_init()'s list (registered while the library loads), so its code can be made resident
+// on a device before the first launch.
 template <typename... P, typename... A>
-inline void launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+inline void launch_pointer(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -309,6 +388,11 @@ inline void launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cud
     cfg.attrs = &attr;
     cfg.numAttrs = tuning(kNoPdl) != 0 ? 0 : 1;
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+template <auto kKernel, typename... A>
+inline void launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    (void)KernelAtLoad<kKernel, 0, 0>::token;   // threads 0: nothing to set up, only to load
+    launch_pointer(kKernel, grid, block, smem, stream, static_cast<A&&>(args)...);
 }
 
 }  // namespace rh::host

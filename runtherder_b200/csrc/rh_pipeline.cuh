@@ -9,8 +9,9 @@
 //    cluster launch;
 //  * source address, destination address and size are multiples of 16 bytes;
 //  * every wait is bounded: after kSpinLimit failed polls the waiter records an error in the
-//    library's per-device error word (passed to the kernel) and gives up, so a kernel can never spin
-//    forever.
+//    library's per-device error word (passed to the kernel) and gives up; kernels that synchronise
+//    their consumers make the give-up a CTA-wide decision behind their row barrier, so nobody is left
+//    waiting at a barrier for threads that have gone.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -27,7 +28,11 @@ int* device_error_word();
 
 namespace pipe {
 
-constexpr int kSpinLimit = 1 << 22;  // polls; each try_wait already blocks for a while in hardware
+// A failed poll does not come back at once: try_wait suspends the thread in hardware until the phase
+// completes or kSuspendNs have passed, so a waiting warp issues next to nothing while it waits and is
+// woken the moment the copy lands.  kSpinLimit polls of up to kSuspendNs each bound a wait to ~1.3 s.
+constexpr int kSpinLimit = 1 << 16;
+constexpr uint32_t kSuspendNs = 20000;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -48,10 +53,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
         : "memory");
     return ok != 0;
 }

@@ -453,19 +453,19 @@ int launch_rope(RopeArgs p, bool norm, bool kv, cudaStream_t stream) {
     if (aligned) {
         const size_t smem = static_cast<size_t>(warps) * kRopeDepth * 64 * sizeof(uint4);   // <= 32 KB
         if (kv) {
-            if (norm) host::launch(rope_kv_kernel<D, true, true>, dim3(g), dim3(b), smem, stream, p);
-            else host::launch(rope_kv_kernel<D, false, true>, dim3(g), dim3(b), smem, stream, p);
+            if (norm) host::launch<rope_kv_kernel<D, true, true>>(dim3(g), dim3(b), smem, stream, p);
+            else host::launch<rope_kv_kernel<D, false, true>>(dim3(g), dim3(b), smem, stream, p);
         } else {
-            if (norm) host::launch(rope_kv_kernel<D, true, false>, dim3(g), dim3(b), smem, stream, p);
-            else host::launch(rope_kv_kernel<D, false, false>, dim3(g), dim3(b), smem, stream, p);
+            if (norm) host::launch<rope_kv_kernel<D, true, false>>(dim3(g), dim3(b), smem, stream, p);
+            else host::launch<rope_kv_kernel<D, false, false>>(dim3(g), dim3(b), smem, stream, p);
         }
     } else {
         if (kv) {
-            if (norm) host::launch(rope_kv_generic_kernel<D, true, true>, dim3(g), dim3(b), 0, stream, p);
-            else host::launch(rope_kv_generic_kernel<D, false, true>, dim3(g), dim3(b), 0, stream, p);
+            if (norm) host::launch<rope_kv_generic_kernel<D, true, true>>(dim3(g), dim3(b), 0, stream, p);
+            else host::launch<rope_kv_generic_kernel<D, false, true>>(dim3(g), dim3(b), 0, stream, p);
         } else {
-            if (norm) host::launch(rope_kv_generic_kernel<D, true, false>, dim3(g), dim3(b), 0, stream, p);
-            else host::launch(rope_kv_generic_kernel<D, false, false>, dim3(g), dim3(b), 0, stream, p);
+            if (norm) host::launch<rope_kv_generic_kernel<D, true, false>>(dim3(g), dim3(b), 0, stream, p);
+            else host::launch<rope_kv_generic_kernel<D, false, false>>(dim3(g), dim3(b), 0, stream, p);
         }
     }
     return host::check_launch("rope_kv_kernel");
@@ -515,7 +515,7 @@ extern "C" int rh_rope_bf16(void* q, void* k, const int* positions, const float*
     long long grid = (pairs + 255) / 256;
     const long long cap = static_cast<long long>(host::num_sms()) * 16;
     if (grid > cap) grid = cap;
-    host::launch(rope_generic_kernel, dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
+    host::launch<rope_generic_kernel>(dim3(static_cast<unsigned>(grid)), dim3(256), 0, s, 
         static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), positions, inv_freq, pairs,
         num_q_heads, num_kv_heads, head_dim);
     return host::check_launch("rope_generic_kernel");

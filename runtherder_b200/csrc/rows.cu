@@ -17,7 +17,6 @@
 #include <type_traits>
 
 #include "rh_common.cuh"
-#include "rh_pipeline.cuh"
 
 namespace rh {
 
@@ -32,6 +31,7 @@ enum : unsigned {
     kFStoreY = 4u,  // write the bf16 normalised row
     kFInt8 = 8u,    // write INT8 codes + amax/127
     kFFp8 = 16u,    // write E4M3 codes + amax/448 at the at_pos-relative destination row
+    kFSkipH = 32u,  // with kFAdd: h is formed but not written (nobody reads the residual stream afterwards)
 };
 
 struct RowArgs {
@@ -49,48 +49,53 @@ struct RowArgs {
     float eps;
 };
 
-template <bool kStaged>
-__device__ __forceinline__ void row_sync() {
-    if constexpr (kStaged) pipe::consumer_sync(kRowThreads);  // the producer warp is not part of it
-    else __syncthreads();
-}
-
-// Per-CTA constants of a launch.
+// Per-thread view of a launch: which vectors of a row this thread owns and where they live.
+// kFull: the row is exactly VPT * 256 vectors, so no tail predicate exists and every per-row offset
+// is a compile-time constant.
+template <int VPT, bool kFull>
 struct RowCtx {
-    int tid, lane, warp, n_vecs;
+    int tid, lane, warp, n_vecs_rt;
     float dim_f, inv_dim;
     bool dim_pow2;
-    long long slot_base;
+    __device__ __forceinline__ int n_vecs() const { return kFull ? VPT * kRowThreads : n_vecs_rt; }
+    __device__ __forceinline__ bool live(int s) const { return kFull || tid + s * kRowThreads < n_vecs_rt; }
 };
 
-template <unsigned F>
-__device__ __forceinline__ RowCtx make_ctx(const RowArgs& a) {
-    RowCtx c;
+template <int VPT, bool kFull>
+__device__ __forceinline__ RowCtx<VPT, kFull> make_ctx(const RowArgs& a) {
+    RowCtx<VPT, kFull> c;
     c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5;
-    c.n_vecs = a.dim / kVec;
+    c.n_vecs_rt = a.dim / kVec;
     c.dim_f = static_cast<float>(a.dim);
     c.dim_pow2 = (a.dim & (a.dim - 1)) == 0;  // then ss/dim is an exact scaling
     c.inv_dim = 1.0f / c.dim_f;
-    c.slot_base = 0;
-    if constexpr ((F & kFFp8) != 0) c.slot_base = static_cast<long long>(*a.at_pos) * a.rows_per_pos;
     return c;
 }
 
+// This thread's pointers into the current row (vector tid of the row; vector s is 256 further on).
+// They advance by one grid stride per row, so no per-row 64-bit multiply is left in the loop.
+struct RowPtrs {
+    const uint4* x;
+    const uint4* r;
+    uint4* h_out;
+    uint4* y;
+    uint2* codes;
+    float* scale;   // of the current destination row
+};
+
 // Everything that happens to one row once its vectors sit in registers (xv, rv): h, h_out, the
-// sum of squares and rrms, y, amax, codes and scale.  Shared by the direct-load and the staged kernel.
+// sum of squares and rrms, y, amax, codes and scale.
 // kSmemH: the fp32 row h is parked in shared memory between the two passes instead of in 8*VPT
 // registers per thread (layout [slot][half][thread] float4: conflict-free), which buys a resident CTA.
-template <int VPT, unsigned F, bool kStaged, bool kSmemH = false>
-__device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, long long row, int parity,
+template <int VPT, unsigned F, bool kSmemH, bool kFull>
+__device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx<VPT, kFull>& c, const RowPtrs& p,
                                             const uint4 (&xv)[VPT], const uint4 (&rv)[VPT], const uint4 (&gw)[VPT],
-                                            float (&s_ss)[2][kRowWarps], float (&s_mx)[2][kRowWarps],
-                                            float4* s_h = nullptr) {
+                                            float* s_ss, float* s_mx, float4* s_h) {
     constexpr bool kNorm = (F & kFNorm) != 0, kAdd = (F & kFAdd) != 0, kStoreY = (F & kFStoreY) != 0;
     constexpr bool kInt8 = (F & kFInt8) != 0, kFp8 = (F & kFFp8) != 0, kQuant = kInt8 || kFp8;
-    const int tid = c.tid, lane = c.lane, warp = c.warp, n_vecs = c.n_vecs;
-    const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(n_vecs);
+    const int tid = c.tid, lane = c.lane, warp = c.warp;
 
-    uint32_t yw[VPT][4];  // the row as the next kernel would read it back: packed bf16
+    uint4 yw[VPT];  // the row as the next kernel would read it back: packed bf16
 
     if constexpr (kNorm) {
         float h[kSmemH ? 1 : VPT][8];
@@ -98,8 +103,7 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
 #pragma unroll
         for (int s0 = 0; s0 < VPT; ++s0) {
             const int s = kSmemH ? 0 : s0;           // register slot
-            const int i = tid + s0 * kRowThreads;
-            if (i < n_vecs) {
+            if (c.live(s0)) {
                 if constexpr (kAdd) {
                     const uint32_t xw[4] = {xv[s0].x, xv[s0].y, xv[s0].z, xv[s0].w};
                     const uint32_t rw[4] = {rv[s0].x, rv[s0].y, rv[s0].z, rv[s0].w};
@@ -109,7 +113,7 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
                         h[s][2 * k] = hh.x;
                         h[s][2 * k + 1] = hh.y;
                     }
-                    st_vec(static_cast<uint4*>(a.h_out) + row_off + i, pack8(h[s]));
+                    if constexpr ((F & kFSkipH) == 0) st_vec(p.h_out + s0 * kRowThreads, pack8(h[s]));
                 } else {
                     unpack8(xv[s0], h[s]);
                 }
@@ -122,14 +126,14 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
             }
         }
         ss = group_sum<32>(ss);
-        if (lane == 0) s_ss[parity][warp] = ss;
-        row_sync<kStaged>();
-        const float total = group_sum<kRowWarps>(s_ss[parity][lane & (kRowWarps - 1)]);
+        if (lane == 0) s_ss[warp] = ss;
+        __syncthreads();
+        const float total = group_sum<kRowWarps>(s_ss[lane & (kRowWarps - 1)]);
         const float rrms = rsqrtf((c.dim_pow2 ? total * c.inv_dim : total / c.dim_f) + a.eps);
+        const float2 rrms2 = splat2(rrms);
 #pragma unroll
         for (int s = 0; s < VPT; ++s) {
-            const int i = tid + s * kRowThreads;
-            if (i < n_vecs) {
+            if (c.live(s)) {
                 const uint32_t gws[4] = {gw[s].x, gw[s].y, gw[s].z, gw[s].w};
                 float hv[8];
                 if constexpr (kSmemH) {   // each thread reads back exactly what it wrote: no barrier needed
@@ -140,21 +144,19 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
 #pragma unroll
                     for (int j = 0; j < 8; ++j) hv[j] = h[s][j];
                 }
+                uint32_t w[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {   // y = (h * rrms) * g, two elements per instruction
-                    const float2 t = mul2_rn(make_float2(hv[2 * k], hv[2 * k + 1]), splat2(rrms));
-                    const float2 yf = mul2_rn(t, bf2_to_f2(gws[k]));
-                    yw[s][k] = pack_bf16x2(yf.x, yf.y);
+                    const float2 yf = mul2_rn(mul2_rn(make_float2(hv[2 * k], hv[2 * k + 1]), rrms2), bf2_to_f2(gws[k]));
+                    w[k] = pack_bf16x2(yf.x, yf.y);
                 }
-                if constexpr (kStoreY)
-                    st_vec(static_cast<uint4*>(a.y) + row_off + i, make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]));
+                yw[s] = make_uint4(w[0], w[1], w[2], w[3]);
+                if constexpr (kStoreY) st_vec(p.y + s * kRowThreads, yw[s]);
             }
         }
     } else {
 #pragma unroll
-        for (int s = 0; s < VPT; ++s) {
-            yw[s][0] = xv[s].x; yw[s][1] = xv[s].y; yw[s][2] = xv[s].z; yw[s][3] = xv[s].w;
-        }
+        for (int s = 0; s < VPT; ++s) yw[s] = xv[s];
     }
 
     if constexpr (kQuant) {
@@ -163,10 +165,11 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
         uint32_t m2 = 0u;
 #pragma unroll
         for (int s = 0; s < VPT; ++s) {
-            const int i = tid + s * kRowThreads;
-            if (i < n_vecs) {
-#pragma unroll
-                for (int w = 0; w < 4; ++w) m2 = amax_acc_bf16x2(m2, yw[s][w]);
+            if (c.live(s)) {
+                m2 = amax_acc_bf16x2(m2, yw[s].x);
+                m2 = amax_acc_bf16x2(m2, yw[s].y);
+                m2 = amax_acc_bf16x2(m2, yw[s].z);
+                m2 = amax_acc_bf16x2(m2, yw[s].w);
             }
         }
         const float m_lo = bf_lo(m2), m_hi = bf_hi(m2);
@@ -176,89 +179,104 @@ __device__ __forceinline__ void process_row(const RowArgs& a, const RowCtx& c, l
             amax = 0.0f;
 #pragma unroll
             for (int s = 0; s < VPT; ++s) {
-                const int i = tid + s * kRowThreads;
-                if (i < n_vecs) {
+                if (c.live(s)) {
+                    float f[8];
+                    unpack8(yw[s], f);
 #pragma unroll
-                    for (int w = 0; w < 4; ++w)
-                        amax = fmaxf(amax, fmaxf(fabsf(bf_lo(yw[s][w])), fabsf(bf_hi(yw[s][w]))));
+                    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
                 }
             }
         }
         amax = warp_max_nonneg(amax);
-        if (lane == 0) s_mx[parity][warp] = amax;
-        row_sync<kStaged>();
-        amax = warp_max_nonneg(s_mx[parity][lane & (kRowWarps - 1)]);
+        if (lane == 0) s_mx[warp] = amax;
+        __syncthreads();
+        amax = warp_max_nonneg(s_mx[lane & (kRowWarps - 1)]);
 
         constexpr int kQMax = kInt8 ? 127 : 448;
         const float inv = quant_inv_scale<kQMax>(amax);
-        const long long dst_row = row + c.slot_base;
-        if (tid == 0) a.scale[dst_row] = quant_scale<kQMax>(amax);
-        uint2* c_row = static_cast<uint2*>(a.codes) + static_cast<size_t>(dst_row) * n_vecs;
+        if (tid == 0) *p.scale = quant_scale<kQMax>(amax);
+        if (kInt8 && finite && inv <= kFastInvMax) {  // a huge inverse (tiny amax) takes the exact path
+            const float2 inv4 = splat2(inv * 4.0f);
 #pragma unroll
-        for (int s = 0; s < VPT; ++s) {
-            const int i = tid + s * kRowThreads;
-            if (i < n_vecs) {
-                if (kInt8 && finite && inv <= 3.0e38f) {  // an overflowed inverse (subnormal amax) takes the exact path
-                    st_vec8(c_row + i, pack_int8x8_fast(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), inv));
-                } else {
+            for (int s = 0; s < VPT; ++s)
+                if (c.live(s)) st_vec8(p.codes + s * kRowThreads, pack_int8x8_fast4(yw[s], inv4));
+        } else {
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                if (c.live(s)) {
                     float yf[8];
-                    unpack8(make_uint4(yw[s][0], yw[s][1], yw[s][2], yw[s][3]), yf);
-                    st_vec8(c_row + i, kInt8 ? pack_int8x8(yf, inv) : pack_e4m3x8(yf, inv));
+                    unpack8(yw[s], yf);
+                    st_vec8(p.codes + s * kRowThreads, kInt8 ? pack_int8x8(yf, inv) : pack_e4m3x8(yf, inv));
                 }
             }
         }
     }
 }
 
-template <int VPT, unsigned F>
-__device__ __forceinline__ void load_gains(const RowArgs& a, int n_vecs, uint4 (&gw)[VPT]) {
-    if constexpr ((F & kFNorm) != 0) {
-#pragma unroll
-        for (int s = 0; s < VPT; ++s) {
-            const int i = static_cast<int>(threadIdx.x) + s * kRowThreads;
-            if (i < n_vecs) gw[s] = ld_weight(static_cast<const uint4*>(a.g) + i);
-        }
-    }
-}
-
-// Direct-load kernel.  kDepth = 0: each thread loads its vectors of the row straight into registers.
-// kDepth >= 1: each thread keeps the vectors of its next kDepth rows on their way into private
-// shared-memory slots (cp.async), so the global-load latency of a row is paid while the previous rows
-// are being reduced and quantised.
-template <int VPT, unsigned F, bool kSmemH = false, int kDepth = 0>
+// A CTA of 256 threads walks rows blockIdx.x, blockIdx.x + gridDim.x, ...  kDepth = 0: each thread loads
+// its vectors of the row straight into registers.  kDepth >= 1: each thread keeps the vectors of its next
+// kDepth rows on their way into private shared-memory slots (cp.async), so the global-load latency of a
+// row is paid while the previous rows are being reduced and quantised.
+template <int VPT, unsigned F, bool kSmemH, int kDepth, bool kFull>
 __global__ void __launch_bounds__(kRowThreads, (kSmemH ? 4 : ((F & kFNorm) == 0 ? (VPT <= 2 ? 6 : 2) : (VPT <= 2 ? 3 : 1))))
 rows_kernel(const RowArgs a) {
-    constexpr bool kAdd = (F & kFAdd) != 0;
+    constexpr bool kNorm = (F & kFNorm) != 0, kAdd = (F & kFAdd) != 0, kStoreY = (F & kFStoreY) != 0;
+    constexpr bool kQuant = (F & (kFInt8 | kFFp8)) != 0;
     constexpr int kOps = kAdd ? 2 : 1;
     __shared__ float s_ss[2][kRowWarps];
     __shared__ float s_mx[2][kRowWarps];
     __shared__ float4 s_h[kSmemH ? VPT * 2 * kRowThreads : 1];
     extern __shared__ uint4 pre[];   // [kDepth][kOps][VPT][256], thread-private columns
     pdl_wait();
-    const RowCtx c = make_ctx<F>(a);
+    const RowCtx<VPT, kFull> c = make_ctx<VPT, kFull>(a);
+    const int n_vecs = c.n_vecs();
     uint4 gw[VPT];
-    load_gains<VPT, F>(a, c.n_vecs, gw);
-
-    auto fetch = [&](long long row, int slot, uint32_t after) {
-        const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(c.n_vecs);
+    if constexpr (kNorm) {
 #pragma unroll
-        for (int s = 0; s < VPT; ++s) {
-            const int i = c.tid + s * kRowThreads;
-            if (i < c.n_vecs) {
-                cp_async16(pre + ((slot * kOps + 0) * VPT + s) * kRowThreads + c.tid, static_cast<const uint4*>(a.x) + row_off + i, after);
-                if constexpr (kAdd)
-                    cp_async16(pre + ((slot * kOps + 1) * VPT + s) * kRowThreads + c.tid,
-                               static_cast<const uint4*>(a.residual) + row_off + i, after);
+        for (int s = 0; s < VPT; ++s)
+            if (c.live(s)) gw[s] = ld_weight(static_cast<const uint4*>(a.g) + c.tid + s * kRowThreads);
+    }
+
+    // Pointers of this thread into its current row; one grid stride further per row.
+    const size_t first = static_cast<size_t>(blockIdx.x) * n_vecs + c.tid;
+    const size_t stride = static_cast<size_t>(gridDim.x) * n_vecs;
+    RowPtrs p;
+    p.x = static_cast<const uint4*>(a.x) + first;
+    p.r = kAdd ? static_cast<const uint4*>(a.residual) + first : nullptr;
+    p.h_out = (kAdd && (F & kFSkipH) == 0) ? static_cast<uint4*>(a.h_out) + first : nullptr;
+    p.y = kStoreY ? static_cast<uint4*>(a.y) + first : nullptr;
+    p.codes = nullptr;
+    p.scale = nullptr;
+    if constexpr (kQuant) {
+        long long slot_base = 0;
+        if constexpr ((F & kFFp8) != 0) slot_base = static_cast<long long>(*a.at_pos) * a.rows_per_pos;
+        p.codes = static_cast<uint2*>(a.codes) + static_cast<size_t>(slot_base) * n_vecs + first;
+        p.scale = a.scale + slot_base + blockIdx.x;
+    }
+
+    // The prefetch cursor runs kDepth rows ahead of the row being processed.
+    const uint4* fx = p.x;
+    const uint4* fr = p.r;
+    long long frow = blockIdx.x;
+    auto fetch = [&](int slot, uint32_t after) {
+        if (frow < a.num_rows) {
+#pragma unroll
+            for (int s = 0; s < VPT; ++s) {
+                if (c.live(s)) {
+                    cp_async16(pre + ((slot * kOps + 0) * VPT + s) * kRowThreads + c.tid, fx + s * kRowThreads, after);
+                    if constexpr (kAdd)
+                        cp_async16(pre + ((slot * kOps + 1) * VPT + s) * kRowThreads + c.tid, fr + s * kRowThreads, after);
+                }
             }
         }
+        cp_async_commit();
+        frow += gridDim.x;
+        fx += stride;
+        if constexpr (kAdd) fr += stride;
     };
     if constexpr (kDepth > 0) {
 #pragma unroll
-        for (int d = 0; d < kDepth; ++d) {
-            const long long row = blockIdx.x + static_cast<long long>(d) * gridDim.x;
-            if (row < a.num_rows) fetch(row, d, 0u);
-            cp_async_commit();
-        }
+        for (int d = 0; d < kDepth; ++d) fetch(d, 0u);
     }
 
     int parity = 0, slot = 0;
@@ -270,7 +288,7 @@ rows_kernel(const RowArgs a) {
             uint32_t tie = 0u;
 #pragma unroll
             for (int s = 0; s < VPT; ++s) {
-                if (c.tid + s * kRowThreads < c.n_vecs) {
+                if (c.live(s)) {
                     xv[s] = pre[((slot * kOps + 0) * VPT + s) * kRowThreads + c.tid];
                     tie ^= xv[s].x;
                     if constexpr (kAdd) {
@@ -279,104 +297,27 @@ rows_kernel(const RowArgs a) {
                     }
                 }
             }
-            const long long ahead = row + static_cast<long long>(kDepth) * gridDim.x;
-            if (ahead < a.num_rows) fetch(ahead, slot, tie);   // refill the slot just drained
-            cp_async_commit();
-            slot = (slot + 1 == kDepth) ? 0 : slot + 1;
+            fetch(slot, tie);   // refill the slot just drained, behind the reads above
+            if constexpr (kDepth > 1) slot = (slot + 1 == kDepth) ? 0 : slot + 1;
         } else {
-            const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(c.n_vecs);
 #pragma unroll
             for (int s = 0; s < VPT; ++s) {
-                const int i = c.tid + s * kRowThreads;
-                if (i < c.n_vecs) {
-                    xv[s] = ld_stream(static_cast<const uint4*>(a.x) + row_off + i);
-                    if constexpr (kAdd) rv[s] = ld_stream(static_cast<const uint4*>(a.residual) + row_off + i);
+                if (c.live(s)) {
+                    xv[s] = ld_stream(p.x + s * kRowThreads);
+                    if constexpr (kAdd) rv[s] = ld_stream(p.r + s * kRowThreads);
                 }
             }
         }
-        process_row<VPT, F, false, kSmemH>(a, c, row, parity, xv, rv, gw, s_ss, s_mx, s_h);
+        process_row<VPT, F, kSmemH, kFull>(a, c, p, xv, rv, gw, s_ss[parity], s_mx[parity], s_h);
+        p.x += stride;
+        if constexpr (kAdd) {
+            p.r += stride;
+            if constexpr ((F & kFSkipH) == 0) p.h_out += stride;
+        }
+        if constexpr (kStoreY) p.y += stride;
+        if constexpr (kQuant) { p.codes += stride; p.scale += gridDim.x; }
     }
     if constexpr (kDepth > 0) cp_async_wait<0>();
-}
-
-// Staged kernel: a producer thread streams the rows through a shared-memory ring with bulk copies
-// (one slot = the 256 vectors, 4 KB per operand, that the 256 consumer threads read together), so
-// several rows per CTA are always in flight and the consumers only ever wait on shared memory.
-// Thread t still owns vectors t, t+256, ...: the arithmetic, and every bit of the output, is that
-// of the direct-load kernel.
-constexpr int kSlotBytes = kRowThreads * 16;
-
-template <int VPT, unsigned F>
-__global__ void __launch_bounds__(kRowThreads + 32, ((F & kFNorm) != 0 ? 4 : 1))
-rows_staged_kernel(const RowArgs a, const int stages, int* error_word) {
-    constexpr bool kAdd = (F & kFAdd) != 0, kSmemH = (F & kFNorm) != 0;
-    constexpr int kOps = kAdd ? 2 : 1;
-    extern __shared__ __align__(128) unsigned char ring[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(ring + static_cast<size_t>(stages) * kOps * kSlotBytes);
-    uint64_t* empty = full + stages;
-    __shared__ float s_ss[2][kRowWarps];
-    __shared__ float s_mx[2][kRowWarps];
-    __shared__ float4 s_h[kSmemH ? VPT * 2 * kRowThreads : 1];
-
-    const int n_vecs = a.dim / kVec;
-    const int slots_per_row = (n_vecs + kRowThreads - 1) / kRowThreads;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) {
-            pipe::mbar_init(full + s, 1);
-            pipe::mbar_init(empty + s, kRowWarps);
-        }
-        pipe::mbar_init_fence();
-    }
-    __syncthreads();
-    pdl_wait();
-
-    if (threadIdx.x >= kRowThreads) {   // producer warp: one thread issues every copy of this CTA
-        if (threadIdx.x == kRowThreads) {
-            int s = 0;
-            uint32_t round = 0;   // how many times the ring has wrapped
-            for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x) {
-                const size_t row_off = static_cast<size_t>(row) * static_cast<size_t>(n_vecs);
-                for (int sl = 0; sl < slots_per_row; ++sl) {
-                    if (round > 0 && !pipe::mbar_wait(empty + s, (round - 1) & 1, __LINE__, error_word)) return;
-                    const int vec0 = sl * kRowThreads;
-                    const uint32_t bytes = static_cast<uint32_t>(min(kRowThreads, n_vecs - vec0)) * 16u;
-                    unsigned char* dst = ring + static_cast<size_t>(s) * kOps * kSlotBytes;
-                    pipe::mbar_expect_tx(full + s, bytes * kOps);
-                    pipe::bulk_load(dst, static_cast<const uint4*>(a.x) + row_off + vec0, bytes, full + s);
-                    if constexpr (kAdd)
-                        pipe::bulk_load(dst + kSlotBytes, static_cast<const uint4*>(a.residual) + row_off + vec0, bytes, full + s);
-                    if (++s == stages) { s = 0; ++round; }
-                }
-            }
-        }
-        return;
-    }
-
-    const RowCtx c = make_ctx<F>(a);
-    uint4 gw[VPT];
-    load_gains<VPT, F>(a, c.n_vecs, gw);
-
-    int parity = 0, s = 0;
-    uint32_t phase = 0;
-    for (long long row = blockIdx.x; row < a.num_rows; row += gridDim.x, parity ^= 1) {
-        if (row + gridDim.x >= a.num_rows) pdl_trigger();   // last row of this CTA
-        uint4 xv[VPT], rv[VPT];
-#pragma unroll
-        for (int sl = 0; sl < VPT; ++sl) {
-            if (sl < slots_per_row) {
-                if (!pipe::mbar_wait(full + s, phase, __LINE__, error_word)) return;
-                const unsigned char* src = ring + static_cast<size_t>(s) * kOps * kSlotBytes + c.tid * 16;
-                if (c.tid + sl * kRowThreads < c.n_vecs) {
-                    xv[sl] = *reinterpret_cast<const uint4*>(src);
-                    if constexpr (kAdd) rv[sl] = *reinterpret_cast<const uint4*>(src + kSlotBytes);
-                }
-                __syncwarp();
-                if (c.lane == 0) pipe::mbar_arrive(empty + s);   // this warp is done with the slot
-                if (++s == stages) { s = 0; phase ^= 1; }
-            }
-        }
-        process_row<VPT, F, true, kSmemH>(a, c, row, parity, xv, rv, gw, s_ss, s_mx, s_h);
-    }
 }
 
 // Short rows (dim <= 256): kLanes = next power of two >= dim/8 lanes own one row, one
@@ -455,78 +396,47 @@ __global__ void __launch_bounds__(kRowThreads) short_rows_kernel(const RowArgs a
     }
 }
 
-// Grid = resident CTAs of this instantiation on the whole device (queried once), so each
-// CTA keeps its gains in registers and walks its share of the rows.
-template <int VPT, unsigned F>
-void launch_long(const RowArgs& a, cudaStream_t stream) {
+// Grid = CTAs of this instantiation that fit on the whole device (set up once per device), capped at
+// three per SM for the prefetching forms, so each CTA keeps its gains in registers and walks its share of
+// the rows.
+template <int VPT, unsigned F, bool kSmemH, int kDepth, bool kFull>
+void launch_form(const RowArgs& a, cudaStream_t stream, int per_sm_cap) {
     constexpr int kOps = (F & kFAdd) ? 2 : 1;
-    // The direct-load kernel is the default: measured on B200 the row kernels are bound by their
-    // per-row dependency chain (two block reductions), not by load latency, and the ring's extra warp
-    // costs a resident CTA.  rh_tune("rows_stages", n >= 2) selects the staged kernel with n slots.
-    const int stages = host::tuning(host::kRowsStages);
-    // Rows up to 4096 wide (two slots per row); wider rows keep too much in registers to add a ring.
-    const bool staged = VPT <= 2 && stages >= 2 && a.num_rows >= 4LL * host::num_sms();
-    if constexpr (VPT <= 2) if (staged) {
-        const size_t smem = static_cast<size_t>(stages) * kOps * kSlotBytes + 2 * stages * sizeof(uint64_t);
-        static int configured_stages = 0;
-        static int resident = 1;
-        if (configured_stages != stages) {   // first use (or a changed ring depth): opt in to the shared memory
-            cudaFuncSetAttribute(reinterpret_cast<const void*>(&rows_staged_kernel<VPT, F>),
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-            resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_staged_kernel<VPT, F>), kRowThreads + 32, smem);
-            configured_stages = stages;
-        }
-        const int tuned = host::tuning(host::kRowsCtasPerSm);
-        const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
-        const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-        host::launch(rows_staged_kernel<VPT, F>, dim3(grid), dim3(kRowThreads + 32), smem, stream, a, stages, host::device_error_word());
-        return;
-    }
+    constexpr size_t smem = static_cast<size_t>(kDepth) * kOps * VPT * kRowThreads * sizeof(uint4);
+    constexpr auto kernel = &rows_kernel<VPT, F, kSmemH, kDepth, kFull>;
+    const int resident = host::setup<kernel, kRowThreads, smem>();
     const int tuned = host::tuning(host::kRowsCtasPerSm);
+    const int per_sm = tuned > 0 ? tuned : (per_sm_cap > 0 && resident > per_sm_cap ? per_sm_cap : resident);
+    const long long cap = static_cast<long long>(host::num_sms()) * per_sm;
+    const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
+    host::launch<kernel>(dim3(grid), dim3(kRowThreads), smem, stream, a);
+}
+
+template <int VPT, unsigned F, bool kFull>
+void launch_long(const RowArgs& a, cudaStream_t stream) {
     if constexpr (VPT <= 2) {
         // Plenty of rows: cp.async prefetch ring, rh_tune("rows_prefetch", depth 1..3; 4 = off).  Defaults
         // from measurements at 65536 x 4096 on B200: norm + INT8 one row ahead (295 us vs 322 us), plain
         // quantisation two rows ahead (120 us vs 131 us), both with three CTAs per SM; the bf16-output norm
         // is store-bound and loses with a ring (370 us vs 332 us), so it keeps the plain loads.
         constexpr bool kQuantOut = (F & (kFInt8 | kFFp8)) != 0;
+        constexpr bool kSm = (F & kFNorm) != 0;
         int depth = host::tuning(host::kRowsPrefetch);
         if (depth == 0) depth = !kQuantOut ? 4 : ((F & kFNorm) != 0 ? 1 : 2);
         if (depth <= 3 && a.num_rows >= 4LL * host::num_sms() && host::tuning(host::kRowsSmemH) != 1) {
-            constexpr bool kSm = (F & kFNorm) != 0;
-            constexpr int kOps = (F & kFAdd) ? 2 : 1;
-            auto go = [&](auto depth_tag) {
-                constexpr int kD = decltype(depth_tag)::value;
-                const size_t smem = static_cast<size_t>(kD) * kOps * VPT * kRowThreads * sizeof(uint4);
-                static int resident = 0;
-                const void* fn = reinterpret_cast<const void*>(&rows_kernel<VPT, F, kSm, kD>);
-                if (resident == 0) {
-                    cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-                    resident = host::resident_ctas(fn, kRowThreads, smem);
-                }
-                const int per_sm = tuned > 0 ? tuned : (resident < 3 ? resident : 3);
-                const long long cap = static_cast<long long>(host::num_sms()) * per_sm;
-                const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-                host::launch(rows_kernel<VPT, F, kSm, kD>, dim3(grid), dim3(kRowThreads), smem, stream, a);
-            };
-            if (depth == 1) go(std::integral_constant<int, 1>{});
-            else if (depth == 2) go(std::integral_constant<int, 2>{});
-            else go(std::integral_constant<int, 3>{});
+            if (depth == 1) launch_form<VPT, F, kSm, 1, kFull>(a, stream, 3);
+            else if (depth == 2) launch_form<VPT, F, kSm, 2, kFull>(a, stream, 3);
+            else launch_form<VPT, F, kSm, 3, kFull>(a, stream, 3);
             return;
         }
     }
     if constexpr ((F & kFNorm) != 0 && VPT <= 4) {   // 8 KB of shared memory per slot: up to 32 KB static
         if (host::tuning(host::kRowsSmemH) != 1) {   // rh_tune("rows_smem_h", 1) keeps h in registers
-            static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F, true>), kRowThreads);
-            const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
-            const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-            host::launch(rows_kernel<VPT, F, true>, dim3(grid), dim3(kRowThreads), 0, stream, a);
+            launch_form<VPT, F, true, 0, kFull>(a, stream, 0);
             return;
         }
     }
-    static const int resident = host::resident_ctas(reinterpret_cast<const void*>(&rows_kernel<VPT, F>), kRowThreads);
-    const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
-    const int grid = static_cast<int>(a.num_rows < cap ? a.num_rows : cap);
-    host::launch(rows_kernel<VPT, F>, dim3(grid), dim3(kRowThreads), 0, stream, a);
+    launch_form<VPT, F, false, 0, kFull>(a, stream, 0);
 }
 
 template <unsigned F>
@@ -540,20 +450,21 @@ int launch_rows(const RowArgs& a, cudaStream_t stream) {
         const long long cap = static_cast<long long>(host::num_sms()) * 8;
         const int grid = static_cast<int>(want < cap ? want : cap);
         switch (lanes) {
-            case 1: host::launch(short_rows_kernel<1, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
-            case 2: host::launch(short_rows_kernel<2, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
-            case 4: host::launch(short_rows_kernel<4, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
-            case 8: host::launch(short_rows_kernel<8, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
-            case 16: host::launch(short_rows_kernel<16, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
-            default: host::launch(short_rows_kernel<32, F>, dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 1: host::launch<short_rows_kernel<1, F>>(dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 2: host::launch<short_rows_kernel<2, F>>(dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 4: host::launch<short_rows_kernel<4, F>>(dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 8: host::launch<short_rows_kernel<8, F>>(dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            case 16: host::launch<short_rows_kernel<16, F>>(dim3(grid), dim3(kRowThreads), 0, stream, a); break;
+            default: host::launch<short_rows_kernel<32, F>>(dim3(grid), dim3(kRowThreads), 0, stream, a); break;
         }
         return host::check_launch("short_rows_kernel");
     }
     const int vpt = (n_vecs + kRowThreads - 1) / kRowThreads;
-    if (vpt <= 1) launch_long<1, F>(a, stream);
-    else if (vpt <= 2) launch_long<2, F>(a, stream);
-    else if (vpt <= 4) launch_long<4, F>(a, stream);
-    else launch_long<8, F>(a, stream);
+    // Rows of exactly 2 x 256 or 4 x 256 vectors (4096 and 8192 wide) take the form without tail predicates.
+    if (vpt <= 1) launch_long<1, F, false>(a, stream);
+    else if (vpt <= 2) { if (n_vecs == 2 * kRowThreads) launch_long<2, F, true>(a, stream); else launch_long<2, F, false>(a, stream); }
+    else if (vpt <= 4) { if (n_vecs == 4 * kRowThreads) launch_long<4, F, true>(a, stream); else launch_long<4, F, false>(a, stream); }
+    else launch_long<8, F, false>(a, stream);
     return host::check_launch("rows_kernel");
 }
 
@@ -595,6 +506,19 @@ extern "C" int rh_rmsnorm_add_bf16(void* y, void* h_out, const void* x, const vo
                RH_ERR_MISALIGNED, "rh_rmsnorm_add_bf16: pointers must be 16-byte aligned");
     RowArgs a{y, h_out, x, residual, g, nullptr, nullptr, nullptr, 0, num_tokens, hidden_dim, eps};
     return launch_rows<kFNorm | kFAdd | kFStoreY>(a, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int rh_rmsnorm_add_last_row_bf16(void* y_last, const void* x, const void* residual, const void* g,
+                                            int num_tokens, int hidden_dim, float eps, void* stream) {
+    if (int e = check_rows("rh_rmsnorm_add_last_row_bf16", num_tokens, hidden_dim)) return e;
+    RH_REQUIRE(y_last && x && residual && g, RH_ERR_INVALID_ARG, "rh_rmsnorm_add_last_row_bf16: null pointer");
+    RH_REQUIRE(eps > 0.0f, RH_ERR_INVALID_ARG, "rh_rmsnorm_add_last_row_bf16: eps must be > 0");
+    RH_REQUIRE(host::aligned16(y_last) && host::aligned16(x) && host::aligned16(residual) && host::aligned16(g),
+               RH_ERR_MISALIGNED, "rh_rmsnorm_add_last_row_bf16: pointers must be 16-byte aligned");
+    const size_t last = static_cast<size_t>(num_tokens - 1) * static_cast<size_t>(hidden_dim) * sizeof(__nv_bfloat16);
+    RowArgs a{y_last, nullptr, static_cast<const char*>(x) + last, static_cast<const char*>(residual) + last, g,
+              nullptr, nullptr, nullptr, 0, 1, hidden_dim, eps};
+    return launch_rows<kFNorm | kFAdd | kFStoreY | kFSkipH>(a, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int rh_quantize_per_token_int8(int8_t* q, float* x_scale, const void* x, int num_tokens,

@@ -29,27 +29,12 @@ namespace {
 // runtime's symbol lookup — it is never passed to a kernel as a pointer.
 static __device__ __align__(256) unsigned int g_selftest_counters[RH_SELFTEST_MAX_COUNTERS];
 
-// Same checks as the allocating self-test's kernel: every bf16 gate through the refined sigmoid
-// reciprocal (one and two steps), every non-negative bf16 amax through the four scale divisions.
+// Same checks as the allocating self-test's kernel (selftest_checks: every bf16 gate through the refined
+// sigmoid reciprocals, every non-negative bf16 amax through the four scale divisions).
 __global__ void selftest_static_kernel(unsigned int* counters, int num_counters) {
-    const unsigned int bits = blockIdx.x * blockDim.x + threadIdx.x;   // 0 .. 65535
-    const float g = __uint_as_float(bits << 16);
-    auto count = [&](int slot) {
+    selftest_checks(blockIdx.x * blockDim.x + threadIdx.x, [&](int slot) {
         if (slot < num_counters) atomicAdd(&counters[slot], 1u);
-    };
-    if (g >= kGateExactBelow) {
-        const unsigned int want = __float_as_uint(sigmoid_reference(g));
-        if (__float_as_uint(sigmoid2<1>(splat2(g)).x) != want) count(0);
-        if (__float_as_uint(sigmoid2<2>(splat2(g)).y) != want) count(1);
-    }
-    if (bits <= 0x7f80u) {
-        const float amax = g;
-        const float inv127 = (amax > 0.0f) ? (127.0f / amax) : 0.0f, inv448 = (amax > 0.0f) ? (448.0f / amax) : 0.0f;
-        if (__float_as_uint(quant_inv_scale<127>(amax)) != __float_as_uint(inv127)) count(2);
-        if (__float_as_uint(quant_inv_scale<448>(amax)) != __float_as_uint(inv448)) count(3);
-        if (__float_as_uint(quant_scale<127>(amax)) != __float_as_uint(amax / 127.0f)) count(4);
-        if (__float_as_uint(quant_scale<448>(amax)) != __float_as_uint(amax / 448.0f)) count(5);
-    }
+    });
 }
 
 constexpr int kMaxDevices = 64;

@@ -21,6 +21,7 @@ __all__ = [
     "dequantize_w8a8", "quantize_kv_fp8", "dequantize_kv_fp8", "swiglu_bf16_forward", "rope_bf16",
     "embedding_lookup_bf16_forward", "qkv_bias_add_bf16_forward", "stage_positions", "decode_advance",
     "flash_split_scratch_floats", "flash_decode_split_bf16", "flash_prefill_bf16", "tune", "bias_rope_kv_fp8", "rmsnorm_add_quant_int8", "swiglu_quant_int8", "rope_kv_fp8",
+    "rmsnorm_add_last_row", "init",
 ]
 
 
@@ -78,6 +79,20 @@ def rmsnorm_add_bf16_forward(y, h_out, x, residual, g, num_tokens: int, hidden_d
     call("rh_rmsnorm_add_bf16", _ptr(y, _BF, n, "y"), _ptr(h_out, _BF, n, "h_out"), _ptr(x, _BF, n, "x"),
          _ptr(residual, _BF, n, "residual"), _ptr(g, _BF, hidden_dim, "g"), num_tokens, hidden_dim, eps,
          _stream(stream))
+
+
+def rmsnorm_add_last_row(y_last, x, residual, g, num_tokens: int, hidden_dim: int, eps: float, stream=None) -> None:
+    """y_last[hidden_dim] = row num_tokens-1 of rmsnorm(x + residual) * g: the final norm when only the last
+    token feeds lm_head (llama3.cu:254-263 normalises every row and slices)."""
+    n = num_tokens * hidden_dim
+    call("rh_rmsnorm_add_last_row_bf16", _ptr(y_last, _BF, hidden_dim, "y_last"), _ptr(x, _BF, n, "x"),
+         _ptr(residual, _BF, n, "residual"), _ptr(g, _BF, hidden_dim, "g"), num_tokens, hidden_dim, eps, _stream(stream))
+
+
+def init(device: int = 0) -> None:
+    """rh_init: makes every kernel of the library resident and set up on `device`, so that even the first
+    call of an entry point may be recorded into a CUDA graph."""
+    call("rh_init", int(device))
 
 
 def quantize_per_token_int8(q, x_scale, x, num_tokens: int, dim: int, stream=None) -> None:

@@ -36,3 +36,44 @@ def gather_rows(local: torch.Tensor, total_rows: int, group=None) -> torch.Tenso
     dist.all_gather(parts, flat.contiguous(), group=group)
     rows = [p.view(local.dtype).view(pad.shape)[: e - b] for p, (b, e) in zip(parts, bounds)]
     return torch.cat(rows, dim=0)
+
+
+def boundary_windows(total_rows: int, world_size: int, half_width: int = 64) -> List[Tuple[int, int]]:
+    """Row windows [lo, hi) worth checking after a sharded run: the first rows, the last rows, and
+    `half_width` rows either side of every shard boundary (merged where they overlap)."""
+    cuts = [0] + [e for _, e in all_shard_bounds(total_rows, world_size)]
+    spans = sorted((max(0, c - half_width), min(total_rows, c + half_width)) for c in cuts)
+    merged: List[Tuple[int, int]] = []
+    for lo, hi in spans:
+        if hi <= lo:
+            continue
+        if merged and lo <= merged[-1][1]:
+            merged[-1] = (merged[-1][0], max(merged[-1][1], hi))
+        else:
+            merged.append((lo, hi))
+    return merged
+
+
+def gather_window(local: torch.Tensor, total_rows: int, lo: int, hi: int, group=None) -> torch.Tensor:
+    """Verification helper: all ranks receive global rows [lo, hi) of a row-sharded tensor, each row taken
+    from the rank that owns it under `shard_bounds` (`local` is this rank's whole row block).  Every rank
+    contributes a fixed-size buffer to one all-gather; rows it does not own are left zero and ignored."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    bounds = all_shard_bounds(total_rows, world)
+    b, e = bounds[rank]
+    if local.shape[0] != e - b:
+        raise ValueError(f"rank {rank} holds {local.shape[0]} rows, its block is [{b}, {e})")
+    n = hi - lo
+    mine = torch.zeros((n,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    o_lo, o_hi = max(lo, b), min(hi, e)
+    if o_hi > o_lo:
+        mine[o_lo - lo:o_hi - lo] = local[o_lo - b:o_hi - b]
+    flat = mine.view(torch.uint8) if mine.dtype != torch.uint8 else mine
+    parts = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(parts, flat.contiguous(), group=group)
+    out = torch.empty_like(mine)
+    for p, (rb, re_) in zip(parts, bounds):
+        r_lo, r_hi = max(lo, rb), min(hi, re_)
+        if r_hi > r_lo:
+            out[r_lo - lo:r_hi - lo] = p.view(local.dtype).view(mine.shape)[r_lo - lo:r_hi - lo]
+    return out

@@ -9,16 +9,20 @@ from pathlib import Path
 
 import numpy as np
 
+import os
+
 ROOT = Path(__file__).resolve().parent.parent
 ORACLE_DIR = ROOT / "oracle"
-REFERENCE_ROOT = Path("/root/reference")
+# Where the reference's sources lie when they are present at all (the checkers under oracle/_ref are
+# built from them in place); REF overrides it, exactly as for oracle/Makefile.
+REFERENCE_ROOT = Path(os.environ.get("REF", "/root/reference"))
 
 _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_long
 _sz, _u64, _u32, _i32, _u16, _u8 = C.c_size_t, C.c_uint64, C.c_uint32, C.c_int32, C.c_uint16, C.c_uint8
 
 
 def _make(target: str) -> None:
-    subprocess.run(["make", "-C", str(ORACLE_DIR), target], check=True, capture_output=True)
+    subprocess.run(["make", "-C", str(ORACLE_DIR), f"REF={REFERENCE_ROOT}", target], check=True, capture_output=True)
 
 
 def load_oracle() -> C.CDLL:
@@ -116,6 +120,19 @@ def load_ref_cuda():
     for name, args in sig.items():
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = args, None
+    return lib
+
+
+def load_ref_matmul():
+    """The reference's W8A8 linear layer (matmul.cu + cuBLASLt); None when the prebuilt library is absent."""
+    path = ORACLE_DIR / "_ref" / "libref_matmul.so"
+    if not path.exists():
+        if not REFERENCE_ROOT.exists():
+            return None
+        _make("_ref/libref_matmul.so")
+    lib = C.CDLL(str(path))
+    lib.refmatmul_linear_w8a8.argtypes = [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p]
+    lib.refmatmul_linear_w8a8.restype = None
     return lib
 
 

@@ -28,8 +28,8 @@ REFERENCE_CXX_SYMBOLS = [
 BIAS_CXX_SYMBOL = "_ZN10runtherder7kernels25qkv_bias_add_bf16_forwardEP13__nv_bfloat16S2_S2_PKS1_S4_S4_iiiP11CUstream_st"
 
 
-def declared_entry_points():
-    text = (ROOT / "include" / "rh_kernels.h").read_text()
+def declared_entry_points(header="rh_kernels.h"):
+    text = (ROOT / "include" / header).read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(rh_[a-z0-9_]+)\s*\(", text)))
 
@@ -43,6 +43,16 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert set(names) == set(_lib.SIGNATURES), "ctypes signature table and header disagree"
     assert _lib.lib.rh_version() >= 100
     assert _lib.lib.rh_status_string(2) == b"unsupported dimension"
+
+
+def test_linear_library_loads_and_exports_every_declared_symbol():
+    """librh_linear.so (the W8A8 linear wrapper; links cuBLASLt) against include/rh_linear.h."""
+    from runtherder_b200 import linear
+    names = declared_entry_points("rh_linear.h")
+    assert "rh_linear_w8a8_prequantized" in names and len(names) >= 5
+    for name in names:
+        assert hasattr(linear.lib, name), f"{name} is declared in rh_linear.h but not exported"
+    assert set(names) == set(linear.SIGNATURES), "ctypes signature table and header disagree"
 
 
 def test_library_exports_reference_cxx_signatures():

@@ -3,6 +3,7 @@ C++ signatures (oracle/_ref/dropin_test_*), must pass.  (2) The fused chain must
 graph and pick up new positions / write slots on replay, as the reference's decode loop requires
 (src/engine/generator.cu:46-68: pointers frozen, contents of positions and at_pos change)."""
 import subprocess
+import sys
 from pathlib import Path
 
 import pytest
@@ -13,7 +14,7 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-@pytest.mark.parametrize("suite", ["rmsnorm", "quantization", "rope", "activation", "bias"])
+@pytest.mark.parametrize("suite", ["rmsnorm", "quantization", "rope", "activation", "bias", "flash_decode", "flash_prefill"])
 def test_reference_kernel_tests_pass_against_this_library(suite):
     exe = ROOT / "oracle" / "_ref" / f"dropin_test_{suite}"
     if not exe.exists():
@@ -82,7 +83,7 @@ def test_bounded_wait_gives_up_and_reports():
     assert err.value != 0 and (err.value & 0xff) == 1 and (err.value >> 8) > 0    # (source line << 8) | code
     after = C.c_int(-1)
     _lib.call("rh_device_error", C.byref(after))
-    assert after.value == 0                                                        # sticky word restored
+    assert after.value == 0                                                        # the sticky word is not the probe's
     x = torch.ones(8, device="cuda")
     assert float((x * 2).sum()) == 16.0                                            # context still usable
 
@@ -191,3 +192,71 @@ def test_dependent_launch_keeps_stream_order_for_device_scalars_and_in_place_cha
     got = chain(sync=False)
     for a, b in zip(got, want):
         assert bits_equal(a, b)
+
+
+_FIRST_USE_IN_CAPTURE = r"""
+import sys
+sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+import torch
+from gpu_util import bits_equal
+from runtherder_b200 import kernels as K, layer_ops, synth
+from runtherder_b200.configs import C0, C3
+torch.cuda.set_device(0)
+K.init(0)                      # nothing of the library has run yet in this process
+for cfg in (C0, C3.with_tokens(700)):
+    T = cfg.tokens
+    ins = synth.make_inputs(cfg)                       # the generators are not part of the captured path
+    q0 = ins["q"].clone()
+    outs = layer_ops.alloc_outputs(cfg, T, slots=T)
+    last = torch.empty(cfg.hidden, dtype=torch.bfloat16, device="cuda")
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):     # first use of every kernel below is inside this capture
+            layer_ops.fused_layer_step(cfg, ins, outs, with_embedding=True)
+            K.rmsnorm_add_last_row(last, ins["x"], ins["residual"], ins["g_ffn"], T, cfg.hidden, cfg.eps)
+    graph.replay()
+    torch.cuda.synchronize()
+    got = {{k: v.clone() for k, v in outs.items()}}
+    got["q"], got["last"] = ins["q"].clone(), last.clone()
+    ins["q"].copy_(q0)
+    outs2 = layer_ops.alloc_outputs(cfg, T, slots=T)
+    layer_ops.fused_layer_step(cfg, ins, outs2, with_embedding=True)     # the same calls, eagerly
+    K.rmsnorm_add_last_row(last, ins["x"], ins["residual"], ins["g_ffn"], T, cfg.hidden, cfg.eps)
+    torch.cuda.synchronize()
+    outs2["q"], outs2["last"] = ins["q"], last
+    for k, v in got.items():
+        if v.dtype.is_floating_point or v.dtype in (torch.int8, torch.uint8):
+            assert bits_equal(v, outs2[k]), (cfg.name, k)
+print("FIRST-USE-IN-CAPTURE-OK")
+"""
+
+
+def test_first_use_of_every_kernel_inside_capture_after_rh_init():
+    """A fresh process calls rh_init and then records a layer's whole chain into a CUDA graph as the very
+    first use of the library: no kernel has set-up left to do inside the capture, and the replay produces
+    the bytes of the eager calls."""
+    code = _FIRST_USE_IN_CAPTURE.format(root=str(ROOT), tests=str(ROOT / "tests"))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "FIRST-USE-IN-CAPTURE-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.parametrize("T,H", [(35, 3072), (511, 3072), (1, 4096), (700, 4096), (9, 264)])
+def test_final_norm_of_the_last_row_only(T, H):
+    """rh_rmsnorm_add_last_row_bf16 == row T-1 of rmsnorm_add_bf16_forward (the reference's final norm,
+    llama3.cu:254-263), bit for bit, against the reference's own kernel; the inputs are left untouched."""
+    from gpu_util import bits_equal, ref_cuda_or_skip, to_dev
+    from refgen import make_bf16_random
+    from runtherder_b200 import kernels as K
+    ref = ref_cuda_or_skip()
+    x = to_dev(make_bf16_random(T * H, 1.0, 41)).view(T, H)
+    r = to_dev(make_bf16_random(T * H, 1.0, 42)).view(T, H)
+    g = to_dev(make_bf16_random(H, 1.0, 43))
+    x0, r0 = x.clone(), r.clone()
+    y = torch.empty(T, H, dtype=torch.bfloat16, device="cuda"); h = torch.empty_like(y)
+    ref.rmsnorm_add_bf16_forward(y, h, x, r, g, T, H, 1e-5)
+    last = torch.full((H,), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.rmsnorm_add_last_row(last, x, r, g, T, H, 1e-5)
+    torch.cuda.synchronize()
+    assert bits_equal(last, y[T - 1])
+    assert bits_equal(x, x0) and bits_equal(r, r0)

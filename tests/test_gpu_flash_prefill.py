@@ -17,7 +17,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import RefCuda, to_np
+from gpu_util import ref_cuda_or_skip, to_np
 from oracle_lib import Oracle
 from test_gpu_flash_decode import ROWMAX_TOL, ULP_TOL, ordered
 
@@ -32,7 +32,7 @@ def orc():
 @pytest.fixture(scope="module")
 def ref():
     try:
-        return RefCuda()
+        return ref_cuda_or_skip()
     except RuntimeError as exc:
         pytest.skip(str(exc))
 

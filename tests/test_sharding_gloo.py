@@ -55,6 +55,42 @@ def _worker_gather(rank, world, port, T, H, result_dir):
     dist.destroy_process_group()
 
 
+def _worker_window(rank, world, port, T, H, result_dir):
+    sys.path.insert(0, str(HERE)); sys.path.insert(0, str(HERE.parent))
+    from refgen import make_bf16_random
+    from runtherder_b200.sharding import boundary_windows, gather_window, shard_bounds
+    _init(rank, world, port)
+    full = torch.from_numpy(make_bf16_random(T * H, 1.0, 7).reshape(T, H).view(np.int16)).view(torch.bfloat16)
+    scales = torch.arange(T, dtype=torch.float32) + 0.5
+    b, e = shard_bounds(T, world, rank)
+    ok = True
+    windows = boundary_windows(T, world, half_width=5)
+    for lo, hi in windows:
+        w = gather_window(full[b:e].clone(), T, lo, hi)
+        ok = ok and torch.equal(w.view(torch.int16), full[lo:hi].view(torch.int16))
+        ws = gather_window(scales[b:e].clone(), T, lo, hi)
+        ok = ok and torch.equal(ws, scales[lo:hi])
+    covered = set()
+    for lo, hi in windows:
+        covered.update(range(lo, hi))
+    cuts = {0, T - 1} | {c for c in (shard_bounds(T, world, r)[0] for r in range(world))} \
+        | {max(0, shard_bounds(T, world, r)[1] - 1) for r in range(world)}
+    ok = ok and cuts <= covered
+    if rank == 0:
+        Path(result_dir, "ok").write_text("1" if ok else "0")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("T,world", [(511, 2), (64, 2), (35, 3)])
+def test_boundary_windows_gather_the_owning_ranks_rows(tmp_path, T, world):
+    """gather_window (what `bench.py --gpus N` verifies the shards with): every window around a shard
+    boundary comes back with each row taken from the rank that owns it, for uneven splits too."""
+    port = _free_port()
+    mp.spawn(_worker_window, args=(world, port, T, 24, str(tmp_path)), nprocs=world, join=True)
+    assert (tmp_path / "ok").read_text() == "1"
+
+
 @pytest.mark.parametrize("T", [511, 64])
 def test_two_rank_row_shards_reassemble(tmp_path, T):
     port = _free_port()
