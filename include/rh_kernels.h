@@ -6,9 +6,12 @@
  *  - Every pointer is a DEVICE pointer unless the parameter is documented as host.
  *    bf16 tensors are passed as void* (16-bit patterns), FP8 E4M3 as uint8_t*.
  *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
- *  - All work is enqueued on `stream`; no call synchronises, allocates or keeps a
- *    pointer, so every call may be recorded into a CUDA graph.  positions /
- *    at_pos / token ids are read on the device at execution time.
+ *  - All work is enqueued on `stream`; no kernel entry point synchronises, allocates or
+ *    keeps a pointer, so every such call may be recorded into a CUDA graph.  positions /
+ *    at_pos / token ids are read on the device at execution time.  The exceptions are the
+ *    diagnostics, each documented where it is declared: rh_selftest, rh_selftest_static,
+ *    rh_device_error and rh_selfcheck_bounded_wait synchronise (the first and the last
+ *    also allocate), and rh_init is host-side set-up.
  *  - Row starts must be 16-byte aligned (bf16 row length a multiple of 8).
  *  - Return value: RH_OK or an rh_status error; rh_last_error_string() gives the
  *    reason for the last failure on the calling thread.  Nothing is launched
@@ -129,7 +132,7 @@ size_t rh_flash_split_scratch_floats(int num_q_heads, int head_dim, int max_spli
  * K[j,kvh]) V[j,kvh] over keys j = 0 .. *cache_len, K/V = E4M3 code * per-(token, kv head) scale
  * (layout: include/runtherder/attention/kv_view.h:8-19); *cache_len is read on the device.
  * `partial` is caller-owned scratch of rh_flash_split_scratch_floats(Hq, D, num_splits) floats;
- * any num_splits >= 1 is correct at any *cache_len.  head_dim in {32, 64, 128, 256}.  The result
+ * any num_splits >= 1 is correct at any *cache_len.  head_dim in {32, 64, 128, 256, 512} (512 takes a plain CUDA-core form).  The result
  * differs from a serial fp32 evaluation by float reassociation only (at most 1 bf16 ulp).
  * Replaces flash_decode_split_bf16 (include/runtherder/kernels/flash_decode.cuh:27-62,
  * src/kernels/flash_decode.cu:271-325; called from src/attention/adaptive.cu:30-33). */
@@ -174,7 +177,8 @@ int rh_swiglu_quant_int8(int8_t* q, float* x_scale, void* y_or_null, const void*
  * (include/runtherder/engine/kv_cache.h:62-78).  q is rotated in place; the rotated bf16 k is
  * written to k_out when it is not NULL (k_out may alias k_in).  k_cache/v_cache/k_scale/v_scale are
  * the layer's slabs ([max_seq, Hkv, D] E4M3 and [max_seq, Hkv] fp32); slot = *at_pos + token.
- * head_dim must be a multiple of 16. */
+ * head_dim must be one of 16, 32, 64, 128, 256 (other even head_dims: rh_rope_bf16 followed by
+ * rh_quantize_kv_fp8). */
 int rh_rope_kv_fp8(void* q, void* k_out_or_null, const void* k_in, const void* v_in,
                    const void* q_norm_or_null, const void* k_norm_or_null, float eps,
                    const int* positions, const float* inv_freq, uint8_t* k_cache, float* k_scale,
@@ -268,13 +272,16 @@ int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host);
 /* ---- Tuning knobs (process-wide; for experiments, defaults are the tuned values) --------- */
 
 /* key: "rows_ctas_per_sm", "swiglu_ctas_per_sm", "rope_warps_per_cta", "embed_ctas_per_sm",
- * "swiglu_threads" (256|512), "swiglu_rcp_steps" (1|2|3 = IEEE division), "rows_stages" /
- * "swiglu_stages" (depth of the bulk-copy staging ring, 1 = direct loads), "no_pdl" (1 = launch
+ * "swiglu_rcp_steps" (stand-alone SwiGLU: 1|2 refinement steps, 3 = IEEE division), "swiglu_stages"
+ * (depth of the bulk-copy staging ring of the fused SwiGLU kernel, 1 = direct loads), "rows_prefetch"
+ * (rows a row kernel keeps in flight through its cp.async ring, 1..3; 4 = plain loads), "rows_smem_h"
+ * (1 = keep the fp32 row in registers instead of shared memory), "no_pdl" (1 = launch
  * without the programmatic-dependent-launch attribute; by default each kernel may be scheduled
  * while the previous kernel of its stream drains and orders itself on the device before its first
  * memory access, so stream semantics are unchanged), "prefill_tiles" (1|2: the mma.sync forms of the prefill
  * attention kernel with one or two 16-row tiles per warp; default: the tcgen05 form with S and O in tensor
- * memory), "prefill_parts" (1|2|4 threads share a query row of the tcgen05 form; default 2); value <= 0 restores the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
+ * memory), "prefill_parts" (1|2|4 threads share a query row of the tcgen05 form; default 2); value <= 0 restores
+ * the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
 int rh_tune(const char* key, int value);
 
 #ifdef __cplusplus

@@ -9,6 +9,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <utility>
 #include <vector>
 
 #include "rh_common.cuh"
@@ -90,11 +91,20 @@ int kernel_setup(const void* kernel, int threads, size_t dyn_smem) {
     auto& table = setup_table();
     const auto it = table.find(key);
     if (it != table.end()) return it->second;
-    // Dynamic plus static shared memory beyond 48 KB needs the opt-in; asking for what the launch will use
-    // is always allowed, so ask whenever there is a dynamic part.
-    if (dyn_smem > 0 &&
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dyn_smem)) != cudaSuccess)
-        (void)cudaGetLastError();
+    // Dynamic plus static shared memory beyond 48 KB needs the opt-in.  The attribute is a ceiling on the
+    // dynamic part, so it is only ever raised: never below the 48 KB every kernel starts with, never below
+    // what an earlier request for this kernel on this device asked for.
+    if (dyn_smem > 0) {
+        static std::map<std::pair<const void*, int>, size_t> ceiling;
+        size_t& have = ceiling[{kernel, dev}];
+        const size_t want = dyn_smem > 48 * 1024 ? dyn_smem : 48 * 1024;
+        if (want > have) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(want)) == cudaSuccess)
+                have = want;
+            else
+                (void)cudaGetLastError();
+        }
+    }
     const int resident = resident_ctas(kernel, threads, dyn_smem);
     table.emplace(key, resident);
     return resident;

@@ -619,6 +619,94 @@ __global__ void __launch_bounds__(kFdReduceThreads) flash_decode_reduce_kernel(_
     }
 }
 
+// head_dim 512 (the reference accepts it, src/kernels/flash_decode.cu:313-314; none of its models uses it):
+// a plain form of the same split — a CTA per (query head, split), warp w takes keys w, w+4, ... of the
+// split, a lane owns 16 of the 512 dims (one 128-bit load of K codes and one of V codes per key), the
+// score is a shuffle-reduced dot product, the online-softmax state (m, l, acc) is fp32 — and writes the
+// scratch slab in the layout the reduce kernel reads.  The tensor-core form above would need 256
+// registers of tile and accumulator per lane at this width.
+constexpr int kFdWideDim = 512;
+
+__device__ __forceinline__ void e4m3x16_to_f32(const uint4& w, float (&f)[16]) {
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t lo, hi;
+        e4m3x4_to_f16x2x2(words[i], lo, hi);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+        f[4 * i] = a.x; f[4 * i + 1] = a.y; f[4 * i + 2] = b.x; f[4 * i + 3] = b.y;
+    }
+}
+
+__global__ void __launch_bounds__(kFdThreads) flash_decode_partial_wide_kernel(const FdArgs p) {
+    constexpr int D = kFdWideDim;
+    __shared__ float s_acc[kFdWarps][D];
+    __shared__ float s_m[kFdWarps], s_l[kFdWarps];
+    const int qh = blockIdx.x, split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kvh = qh / p.group;
+    pdl_enter();
+    const int n_keys = *p.cache_len + 1;
+    const int per = (n_keys + p.num_splits - 1) / p.num_splits;
+    const int begin = split * per, end = min(n_keys, begin + per);
+
+    float qf[16];
+    {
+        const uint4* qp = reinterpret_cast<const uint4*>(p.q + static_cast<size_t>(qh) * D + lane * 16);
+        float lo[8], hi[8];
+        unpack8(qp[0], lo);
+        unpack8(qp[1], hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { qf[i] = lo[i] * p.scale_log2e; qf[8 + i] = hi[i] * p.scale_log2e; }
+    }
+    float m = kFdMInit, l = 0.0f, acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+    for (int key = begin + warp; key < end; key += kFdWarps) {
+        const size_t row = static_cast<size_t>(key) * p.num_kv_heads + kvh;
+        const uint4 kc = *reinterpret_cast<const uint4*>(p.k + row * D + lane * 16);
+        const uint4 vc = *reinterpret_cast<const uint4*>(p.v + row * D + lane * 16);
+        const float ks = p.k_scale[row], vs = p.v_scale[row];
+        float kf[16], vf[16];
+        e4m3x16_to_f32(kc, kf);
+        float dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dot = fmaf(qf[i], kf[i], dot);
+        dot = group_sum<32>(dot) * ks;
+        const float m_new = fmaxf(m, dot);
+        const float corr = ex2_approx(m - m_new), w = ex2_approx(dot - m_new);
+        l = l * corr + w;
+        e4m3x16_to_f32(vc, vf);
+        const float wv = w * vs;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = fmaf(wv, vf[i], acc[i] * corr);
+        m = m_new;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s_acc[warp][lane * 16 + i] = acc[i];
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+    __syncthreads();
+    float big = s_m[0];
+#pragma unroll
+    for (int wv = 1; wv < kFdWarps; ++wv) big = fmaxf(big, s_m[wv]);
+    const long long hs = static_cast<long long>(p.num_q_heads) * p.num_splits;
+    const long long slot = static_cast<long long>(qh) * p.num_splits + split;
+    for (int d = threadIdx.x; d < D; d += kFdThreads) {
+        float a = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kFdWarps; ++wv) a += s_acc[wv][d] * ex2_approx(s_m[wv] - big);
+        p.partial[2 * hs + slot * D + d] = a;
+    }
+    if (threadIdx.x == 0) {
+        float lsum = 0.0f;
+#pragma unroll
+        for (int wv = 0; wv < kFdWarps; ++wv) lsum += s_l[wv] * ex2_approx(s_m[wv] - big);
+        p.partial[slot] = big;
+        p.partial[hs + slot] = lsum;
+    }
+}
+
 template <int D, bool kWide>
 void launch_partial_as(const FdArgs& a, cudaStream_t stream) {
     const dim3 grid(static_cast<unsigned>(a.num_kv_heads * a.row_chunks), static_cast<unsigned>(a.num_splits));
@@ -656,8 +744,8 @@ extern "C" int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_
     RH_REQUIRE(num_kv_heads >= 1, RH_ERR_INVALID_ARG, "%s: num_kv_heads must be >= 1", fn);
     RH_REQUIRE(num_q_heads % num_kv_heads == 0, RH_ERR_INVALID_ARG,
                "%s: num_q_heads must be divisible by num_kv_heads", fn);
-    RH_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256, RH_ERR_UNSUPPORTED_DIM,
-               "%s: head_dim must be one of 32, 64, 128, 256", fn);
+    RH_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256 || head_dim == 512, RH_ERR_UNSUPPORTED_DIM,
+               "%s: head_dim must be one of 32, 64, 128, 256, 512", fn);
     RH_REQUIRE(host::aligned16(q) && host::aligned16(k) && host::aligned16(v) && host::aligned16(partial),
                RH_ERR_MISALIGNED, "%s: q, k, v and partial must be 16-byte aligned", fn);
     RH_REQUIRE((reinterpret_cast<uintptr_t>(out) & 7u) == 0, RH_ERR_MISALIGNED, "%s: out must be 8-byte aligned", fn);
@@ -682,7 +770,11 @@ extern "C" int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_
         case 32: launch_partial<32>(a, s); break;
         case 64: launch_partial<64>(a, s); break;
         case 128: launch_partial<128>(a, s); break;
-        default: launch_partial<256>(a, s); break;
+        case 256: launch_partial<256>(a, s); break;
+        default:
+            host::launch<flash_decode_partial_wide_kernel>(dim3(static_cast<unsigned>(num_q_heads), static_cast<unsigned>(num_splits)),
+                                                           dim3(kFdThreads), 0, s, a);
+            break;
     }
     if (const int st = host::check_launch(fn)) return st;
     const dim3 rgrid(static_cast<unsigned>(num_q_heads)), rblock(kFdReduceThreads);
@@ -692,7 +784,8 @@ extern "C" int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_
         case 32: host::launch<flash_decode_reduce_kernel<32>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
         case 64: host::launch<flash_decode_reduce_kernel<64>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
         case 128: host::launch<flash_decode_reduce_kernel<128>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
-        default: host::launch<flash_decode_reduce_kernel<256>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
+        case 256: host::launch<flash_decode_reduce_kernel<256>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
+        default: host::launch<flash_decode_reduce_kernel<512>>(rgrid, rblock, 0, s, o, part, num_splits, num_q_heads); break;
     }
     return host::check_launch(fn);
 }

@@ -214,6 +214,26 @@ def test_cache_len_is_read_on_the_device_at_replay(orc):
         assert not torch.equal(kc[p], kc0[p])           # the step's own append is part of the history
 
 
+@pytest.mark.parametrize("cache_len,Hq,Hkv,splits", [(300, 8, 2, 4), (1000, 4, 4, 8), (0, 2, 1, 3), (77, 6, 2, 32)])
+def test_flash_decode_head_dim_512(orc, ref, cache_len, Hq, Hkv, splits):
+    """head_dim 512, which the reference's split kernel accepts (src/kernels/flash_decode.cu:313-314) and its
+    naive kernel does not (attention.cu:116, at most 256): this library and the reference's split kernel are
+    both held to the exact attention."""
+    D = 512
+    q, kc, ks, vc, vs = make_case(cache_len, Hq, Hkv, D, seed=cache_len + 3 * splits)
+    scale = 1.0 / math.sqrt(D)
+    out = run_ours(q, kc, ks, vc, vs, cache_len, splits, scale)
+    exact_bits, exact = orc.attention_decode_fp8(to_np(q), to_np(kc), to_np(vc), to_np(ks), to_np(vs), cache_len, scale)
+    check_against_exact(out, exact_bits, exact, "this library, head_dim 512")
+    from runtherder_b200 import kernels as K
+    cl = torch.tensor([cache_len], dtype=torch.int32, device="cuda")
+    out_split = torch.empty_like(out)
+    part = torch.empty(K.flash_split_scratch_floats(Hq, D, splits), dtype=torch.float32, device="cuda")
+    ref.flash_decode_split_bf16(out_split, q, kc, vc, ks, vs, part, splits, cl, Hq, Hkv, D, scale)
+    torch.cuda.synchronize()
+    check_against_exact(out_split, exact_bits, exact, "reference split kernel, head_dim 512")
+
+
 def test_argument_checks():
     from runtherder_b200 import _lib
     from runtherder_b200 import kernels as K
@@ -233,7 +253,7 @@ def test_argument_checks():
     assert status() == 0
     assert status(num_splits=0) == 1                     # RH_ERR_INVALID_ARG
     assert status(Hq=3) == 1                             # not divisible by the kv heads
-    assert status(D=48) == 2 and status(D=512) == 2      # RH_ERR_UNSUPPORTED_DIM
+    assert status(D=48) == 2 and status(D=1024) == 2     # RH_ERR_UNSUPPORTED_DIM (nothing is launched)
     assert _lib.lib.rh_flash_decode_split_bf16(out.data_ptr(), q.data_ptr(), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(),
                                                vs.data_ptr(), part.data_ptr(), 4, None, 4, 2, 64, 0.125, None) == 1
     torch.cuda.synchronize()

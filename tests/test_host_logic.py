@@ -60,7 +60,7 @@ def test_capi_rejects_bad_arguments_before_launching():
     assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 0, A, 8, 2, 128, 0.1, None) == 1      # num_splits
     assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 4, None, 8, 2, 128, 0.1, None) == 1   # cache_len null
     assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 4, A, 8, 3, 128, 0.1, None) == 1      # 8 % 3
-    assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 4, A, 8, 2, 512, 0.1, None) == 2
+    assert status("rh_flash_decode_split_bf16", A, A, A, A, A, A, A, 4, A, 8, 2, 1024, 0.1, None) == 2
     assert status("rh_flash_decode_split_bf16", A, A + 2, A, A, A, A, A, 4, A, 8, 2, 128, 0.1, None) == 3
     assert L.lib.rh_flash_split_scratch_floats(32, 128, 32) == 32 * 32 * 130
     assert status("rh_flash_prefill_bf16", A, A, A, A, A, A, 0, A, 8, 2, 128, 0.1, None) == 1              # n_new
