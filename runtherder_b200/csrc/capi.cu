@@ -261,7 +261,7 @@ extern "C" const char* rh_last_error_string(void) { return host::g_last_error; }
 extern "C" int rh_tune(const char* key, int value) {
     static const char* const kNames[host::kTuneSlots] = {"rows_ctas_per_sm", "swiglu_ctas_per_sm",
                                                          "rope_warps_per_cta", "embed_ctas_per_sm",
-                                                         "elem_ctas_per_sm", "(unused)",
+                                                         "elem_ctas_per_sm", "swiglu_ring",
                                                          "swiglu_rcp_steps", "(unused)", "swiglu_stages",
                                                          "rows_smem_h", "rows_prefetch", "row_tickets", "no_pdl", "prefill_tiles", "prefill_parts"};
     RH_REQUIRE(key != nullptr, RH_ERR_INVALID_ARG, "rh_tune: null key");

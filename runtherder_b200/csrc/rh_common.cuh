@@ -365,7 +365,7 @@ inline int setup() {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kUnusedA,
+enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCtasPerSm, kElemCtasPerSm, kSwigluRingOff,
                 kSwigluRcpSteps, kUnusedB, kSwigluStages, kRowsSmemH, kRowsPrefetch,
                 kRowTickets, kNoPdl, kPrefillTiles, kPrefillParts, kTuneSlots };
 

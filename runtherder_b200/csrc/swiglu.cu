@@ -143,12 +143,12 @@ __device__ __forceinline__ uint4 swiglu_slot(const uint4& gv, const uint4& uv, u
 
 // A thread whose gates left the fast range recomputes its vectors verbatim from global memory (only in
 // the variant that does not store y, so gate and up still hold the inputs).
-template <int VPT, bool kFull>
+template <int VPT, bool kFull, int kCT = kSwiThreads>
 __device__ __forceinline__ void redo_exact(uint4 (&yw)[VPT], uint32_t& m2, const uint4* g_row, const uint4* u_row, int tid, int n_vecs) {
     m2 = 0u;
 #pragma unroll
     for (int s = 0; s < VPT; ++s) {
-        const int i = tid + s * kSwiThreads;
+        const int i = tid + s * kCT;
         if (kFull || i < n_vecs) {
             yw[s] = flip_signs(swiglu8<0>(ld_stream(g_row + i), ld_stream(u_row + i)));
             m2 = amax_acc4(m2, yw[s]);
@@ -156,9 +156,9 @@ __device__ __forceinline__ void redo_exact(uint4 (&yw)[VPT], uint32_t& m2, const
     }
 }
 
-// Row amax -> scale -> codes, from the packed products (kNegated: -y) of the CTA's 256 threads.  `sync` is the
-// barrier among those threads.  kFull: the row is exactly VPT * 256 vectors, no tail predicate anywhere.
-template <int VPT, bool kFull, bool kNegated, typename Sync>
+// Row amax -> scale -> codes, from the packed products (kNegated: -y) of the CTA's kCT consumer threads.  `sync` is the
+// barrier among those threads.  kFull: the row is exactly VPT * kCT vectors, no tail predicate anywhere.
+template <int VPT, bool kFull, bool kNegated, int kCT = kSwiThreads, typename Sync>
 __device__ __forceinline__ void quantise_row(const uint4 (&yw)[VPT], uint32_t m2, int tid, int n_vecs, float* s_mx,
                                              int8_t* q, float* x_scale, long long row, Sync sync) {
     const int lane = tid & 31, warp = tid >> 5;
@@ -171,7 +171,7 @@ __device__ __forceinline__ void quantise_row(const uint4 (&yw)[VPT], uint32_t m2
         amax = 0.0f;
 #pragma unroll
         for (int s = 0; s < VPT; ++s) {
-            if (kFull || tid + s * kSwiThreads < n_vecs) {
+            if (kFull || tid + s * kCT < n_vecs) {
                 float f[8];
                 unpack8(yw[s], f);
 #pragma unroll
@@ -182,7 +182,7 @@ __device__ __forceinline__ void quantise_row(const uint4 (&yw)[VPT], uint32_t m2
     amax = warp_max_nonneg(amax);
     if (lane == 0) s_mx[warp] = amax;
     sync();
-    amax = warp_max_nonneg(s_mx[lane & (kSwiWarps - 1)]);
+    amax = warp_max_nonneg(lane < kCT / 32 ? s_mx[lane] : 0.0f);
 
     const float inv = quant_inv_scale<127>(amax);
     if (tid == 0) x_scale[row] = quant_scale<127>(amax);
@@ -191,13 +191,13 @@ __device__ __forceinline__ void quantise_row(const uint4 (&yw)[VPT], uint32_t m2
         const float2 ninv4 = splat2(inv * (kNegated ? -4.0f : 4.0f));
 #pragma unroll
         for (int s = 0; s < VPT; ++s) {
-            const int i = tid + s * kSwiThreads;
+            const int i = tid + s * kCT;
             if (kFull || i < n_vecs) st_vec8(q_row + i, pack_int8x8_fast4(yw[s], ninv4));
         }
     } else {
 #pragma unroll
         for (int s = 0; s < VPT; ++s) {
-            const int i = tid + s * kSwiThreads;
+            const int i = tid + s * kCT;
             if (kFull || i < n_vecs) {
                 float f[8];
                 unpack8(yw[s], f);
@@ -365,6 +365,105 @@ int launch_swiglu_quant_staged(int8_t* q, float* x_scale, void* y, const void* g
     return host::check_launch("swiglu_quant_staged_kernel");
 }
 
+// Ring kernel: the staged kernel for rows that divide evenly — kCT consumer threads x VPT vectors is the
+// whole row and VPT is a multiple of the kStages ring slots — so that every slot index, shared-memory offset
+// and barrier address is a compile-time constant and a slot's wait parity depends at most on the row's
+// parity: no ring cursor, no wrap test, no address arithmetic per slot.  SwiGLU + INT8 has no ordered
+// reduction, so the element-to-thread mapping is free: a 14336-wide row (1792 vectors) runs as 224 threads
+// x 8 vectors over 4 slots, 8192 as 256 x 4 over 4, 12288 as 256 x 6 over 3.  Codes only (y is not stored).
+template <int VPT, int kCT, int kStages>
+__global__ void __launch_bounds__(kCT + 32, 4)
+swiglu_quant_ring_kernel(int8_t* __restrict__ q, float* __restrict__ x_scale, const void* gate, const void* up,
+                         long long num_tokens, int* error_word) {
+    static_assert(VPT % kStages == 0 && kCT % 32 == 0, "shape");
+    constexpr int kWarps = kCT / 32, kUses = VPT / kStages;     // uses of a slot per row
+    constexpr int kVecBytes = kCT * 16, kStageBytes = 2 * kVecBytes;
+    constexpr int n_vecs = VPT * kCT;
+    __shared__ __align__(128) unsigned char ring[kStages * kStageBytes];
+    __shared__ uint64_t full[kStages], empty[kStages];
+    __shared__ float s_mx[2][kWarps];
+    __shared__ int s_gave_up;
+
+    const int tid = threadIdx.x, lane = tid & 31;
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+            pipe::mbar_init(full + s, 1);
+            pipe::mbar_init(empty + s, kWarps);
+        }
+        s_gave_up = 0;
+        pipe::mbar_init_fence();
+    }
+    __syncthreads();
+    pdl_wait();
+
+    if (tid >= kCT) {
+        if (tid == kCT) {
+            uint32_t n_row = 0;                                   // rows this CTA has issued
+            for (long long row = blockIdx.x; row < num_tokens; row += gridDim.x, ++n_row) {
+                const uint4* g_row = static_cast<const uint4*>(gate) + static_cast<size_t>(row) * n_vecs;
+                const uint4* u_row = static_cast<const uint4*>(up) + static_cast<size_t>(row) * n_vecs;
+#pragma unroll
+                for (int sl = 0; sl < VPT; ++sl) {
+                    const int s = sl % kStages;
+                    const uint32_t use = n_row * kUses + sl / kStages;   // how often slot s has been filled before
+                    if (use > 0 && !pipe::mbar_wait(empty + s, (use - 1) & 1, __LINE__, error_word)) return;
+                    unsigned char* dst = ring + s * kStageBytes;
+                    pipe::mbar_expect_tx(full + s, kStageBytes);
+                    pipe::bulk_load(dst, g_row + sl * kCT, kVecBytes, full + s);
+                    pipe::bulk_load(dst + kVecBytes, u_row + sl * kCT, kVecBytes, full + s);
+                }
+            }
+        }
+        return;
+    }
+
+    int parity = 0;
+    uint32_t row_bit = 0;                                         // (rows processed) & 1
+    for (long long row = blockIdx.x; row < num_tokens; row += gridDim.x, parity ^= 1, row_bit ^= 1) {
+        if (row + gridDim.x >= num_tokens) pdl_trigger();   // last row of this CTA
+        uint4 yw[VPT];
+        uint32_t m2 = 0u, gmin = kGateMinInit;
+#pragma unroll
+        for (int sl = 0; sl < VPT; ++sl) {
+            const int s = sl % kStages;
+            // use number of slot s = rows * kUses + sl / kStages: its parity needs the row only when kUses is odd
+            const uint32_t phase = ((kUses & 1) ? row_bit : 0u) ^ ((sl / kStages) & 1);
+            if (!pipe::mbar_wait(full + s, phase, __LINE__, error_word)) {
+                s_gave_up = 1;
+                break;
+            }
+            const unsigned char* src = ring + s * kStageBytes + tid * 16;
+            const uint4 gv = *reinterpret_cast<const uint4*>(src);
+            const uint4 uv = *reinterpret_cast<const uint4*>(src + kVecBytes);
+            __syncwarp();
+            if (lane == 0) pipe::mbar_arrive(empty + s);
+            yw[sl] = swiglu_slot<false>(gv, uv, nullptr, m2, gmin);
+        }
+        if (gate_min_needs_exact(gmin))
+            redo_exact<VPT, true, kCT>(yw, m2, static_cast<const uint4*>(gate) + static_cast<size_t>(row) * n_vecs,
+                                       static_cast<const uint4*>(up) + static_cast<size_t>(row) * n_vecs, tid, n_vecs);
+        bool gave_up = false;
+        quantise_row<VPT, true, true, kCT>(yw, m2, tid, n_vecs, s_mx[parity], q, x_scale, row, [&] {
+            pipe::consumer_sync(kCT);
+            gave_up = *reinterpret_cast<volatile int*>(&s_gave_up) != 0;
+        });
+        if (gave_up) return;   // every consumer reads the same flag behind the same barrier
+    }
+}
+
+template <int VPT, int kCT, int kStages>
+int launch_swiglu_quant_ring(int8_t* q, float* x_scale, const void* gate, const void* up, long long num_tokens,
+                             cudaStream_t stream) {
+    constexpr auto kernel = &swiglu_quant_ring_kernel<VPT, kCT, kStages>;
+    const int resident = host::setup<kernel, kCT + 32>();
+    const int tuned = host::tuning(host::kSwigluCtasPerSm);
+    const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
+    const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
+    host::launch<kernel>(dim3(grid), dim3(kCT + 32), 0, stream, q, x_scale, gate, up, num_tokens, host::device_error_word());
+    return host::check_launch("swiglu_quant_ring_kernel");
+}
+
 template <int VPT, bool kStoreY, bool kFull>
 int launch_swiglu_quant_direct(int8_t* q, float* x_scale, void* y, const void* gate, const void* up,
                                long long num_tokens, int inter_dim, cudaStream_t stream) {
@@ -443,6 +542,14 @@ extern "C" int rh_swiglu_quant_int8(int8_t* q, float* x_scale, void* y_or_null, 
                RH_ERR_MISALIGNED, "rh_swiglu_quant_int8: pointers must be 16-byte aligned (q: 8)");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n_vecs = inter_dim / kVec;
+    // Rows that divide evenly into a static ring (see swiglu_quant_ring_kernel), when there are rows to stream
+    // and y is not wanted; rh_tune("swiglu_ring", 1) turns it off.
+    if (y_or_null == nullptr && num_tokens >= 4LL * host::num_sms() && host::tuning(host::kSwigluRingOff) != 1 &&
+        host::tuning(host::kSwigluStages) == 0) {
+        if (inter_dim == 14336) return launch_swiglu_quant_ring<8, 224, 4>(q, x_scale, gate, up, num_tokens, s);
+        if (inter_dim == 8192) return launch_swiglu_quant_ring<4, 256, 4>(q, x_scale, gate, up, num_tokens, s);
+        if (inter_dim == 12288) return launch_swiglu_quant_ring<6, 256, 3>(q, x_scale, gate, up, num_tokens, s);
+    }
     // 256 threads x up to 8 vectors each (7 x 256 = 14336 / 8 exactly).
 #define RH_SWIGLU(V) return launch_swiglu_quant<V>(q, x_scale, y_or_null, gate, up, num_tokens, inter_dim, s)
     switch ((n_vecs + 255) / 256) {

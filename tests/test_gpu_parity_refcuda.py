@@ -144,11 +144,12 @@ def _gates_with_extremes(T, I, seed):
     return g
 
 
-@pytest.mark.parametrize("T,I", [(700, 14336), (650, 8192), (640, 1000), (35, 8192), (3, 12288)])
+@pytest.mark.parametrize("T,I", [(700, 14336), (650, 8192), (600, 12288), (1300, 14336), (640, 1000), (35, 8192), (3, 12288)])
 def test_fused_swiglu_quant_extreme_gates_and_aliasing(env, T, I):
     """The fused SwiGLU + INT8 entry against the reference's swiglu -> quantize sequence, with gates outside
-    the refined reciprocal's range in every row, for both kernel forms (>= 4 * SMs rows take the staged one)
-    and with y aliasing gate or up: a row must never be recomputed from memory it has already overwritten."""
+    the refined reciprocal's range in every row, for every kernel form (>= 4 * SMs rows take the staged
+    kernel, or the static-ring kernel when the row divides evenly and y is not stored) and with y aliasing
+    gate or up: a row must never be recomputed from memory it has already overwritten."""
     gate = env.to_dev(_gates_with_extremes(T, I, 0xA11A5))
     up = env.to_dev(rand_bf16((T, I), 2.0, 0xB0B))
     y0 = torch.empty_like(gate)

@@ -145,3 +145,56 @@ def test_row_locality_of_the_oracle():
         qs, ss = ORC.quant_int8(ys)
         assert np.array_equal(ys, y[b:e]) and np.array_equal(hs, h[b:e])
         assert np.array_equal(qs, q[b:e]) and np.array_equal(ss, s[b:e])
+
+
+def test_new_entry_points_reject_bad_arguments_before_launching():
+    # final norm of the last row, rh_init, the W8A8 linear wrapper (matmul.cu:135-136)
+    assert status("rh_rmsnorm_add_last_row_bf16", A, A, A, A, 0, 128, 1e-5, None) == 1
+    assert status("rh_rmsnorm_add_last_row_bf16", A, A, A, A, 4, 12, 1e-5, None) == 2
+    assert status("rh_rmsnorm_add_last_row_bf16", A, A, None, A, 4, 128, 1e-5, None) == 1
+    assert status("rh_rmsnorm_add_last_row_bf16", A, A + 8, A, A, 4, 128, 1e-5, None) == 3
+    assert status("rh_init", -1) != 0                       # no such device (and no device at all on a CPU box)
+    from runtherder_b200 import linear
+    call = linear.lib.rh_linear_w8a8_prequantized
+    assert call(A, A, A, A, A, A, 4, 8, 6, A, None, 0, None) == 2     # k % 4
+    assert call(A, A, A, A, A, A, 0, 8, 8, A, None, 0, None) == 1     # m
+    assert call(A, A, A, A, A, A, 4, 8, 8, None, None, 0, None) == 1  # no cuBLASLt handle
+    assert call(A, A, A, A, A, A, 4, 8, 8, A, None, 64, None) == 1    # workspace size without a workspace
+    assert linear.lib.rh_linear_w8a8(A, None, A, A, A, A, A, 4, 8, 8, A, None, 0, None) == 1
+    assert linear.lib.rh_linear_release(None) == 1
+
+
+def test_boundary_windows_cover_every_cut():
+    from runtherder_b200.sharding import boundary_windows
+    for T, world, half in ((65536, 8, 64), (511, 8, 64), (511, 2, 5), (35, 3, 4), (8, 8, 64)):
+        wins = boundary_windows(T, world, half)
+        assert all(0 <= lo < hi <= T for lo, hi in wins)
+        assert all(a[1] < b[0] for a, b in zip(wins, wins[1:]))           # disjoint, ordered, merged
+        covered = set()
+        for lo, hi in wins:
+            covered.update(range(lo, hi))
+        for b, e in all_shard_bounds(T, world):
+            if e > b:
+                assert b in covered and e - 1 in covered
+        assert 0 in covered and T - 1 in covered
+    assert boundary_windows(65536, 8, 64)[0] == (0, 64) and len(boundary_windows(65536, 8, 64)) == 9
+
+
+def test_host_record_layout():
+    """The chunk records of the pinned-host driver: fields 256-byte aligned, no overlap, payload = sum of fields."""
+    from runtherder_b200.host_path import _Record
+    rec = _Record([("x", (3072,), torch.bfloat16), ("ids", (), torch.int32), ("q", (24, 128), torch.bfloat16),
+                   ("codes", (3072,), torch.int8), ("s", (), torch.float32)], rows=100)
+    spans = []
+    for name, (off, shape, dtype) in rec.fields.items():
+        n = int(np.prod(shape)) * torch.tensor([], dtype=dtype).element_size()
+        assert off % 256 == 0 and shape[0] == 100
+        spans.append((off, off + n))
+    spans.sort()
+    assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:])) and spans[-1][1] <= rec.nbytes
+    assert rec.payload == 100 * (3072 * 2 + 4 + 24 * 128 * 2 + 3072 + 4)
+    block = torch.zeros(rec.nbytes, dtype=torch.uint8)
+    v = rec.views(block, 7)
+    assert v["q"].shape == (7, 24, 128) and v["ids"].shape == (7,) and v["codes"].dtype == torch.int8
+    v["ids"][:] = torch.arange(7, dtype=torch.int32)
+    assert rec.views(block)["ids"][:7].tolist() == list(range(7))         # views alias the block
