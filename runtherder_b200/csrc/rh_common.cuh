@@ -376,7 +376,7 @@ enum TuneSlot { kRowsCtasPerSm = 0, kSwigluCtasPerSm, kRopeWarpsPerCta, kEmbedCt
 // way is on rh_init()'s list (registered while the library loads), so its code can be made resident
 // on a device before the first launch.
 template <typename... P, typename... A>
-inline void launch_pointer(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+inline void launch_pointer(bool dependent, void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -386,13 +386,19 @@ inline void launch_pointer(void (*kernel)(P...), dim3 grid, dim3 block, size_t s
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = tuning(kNoPdl) != 0 ? 0 : 1;
+    cfg.numAttrs = (!dependent || tuning(kNoPdl) != 0) ? 0 : 1;
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
 }
 template <auto kKernel, typename... A>
 inline void launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
     (void)KernelAtLoad<kKernel, 0, 0>::token;   // threads 0: nothing to set up, only to load
-    launch_pointer(kKernel, grid, block, smem, stream, static_cast<A&&>(args)...);
+    launch_pointer(true, kKernel, grid, block, smem, stream, static_cast<A&&>(args)...);
+}
+// The same without the attribute: the kernel starts only when its predecessor in the stream has completed.
+template <auto kKernel, typename... A>
+inline void launch_plain(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    (void)KernelAtLoad<kKernel, 0, 0>::token;
+    launch_pointer(false, kKernel, grid, block, smem, stream, static_cast<A&&>(args)...);
 }
 
 }  // namespace rh::host

@@ -460,7 +460,12 @@ int launch_swiglu_quant_ring(int8_t* q, float* x_scale, const void* gate, const 
     const int tuned = host::tuning(host::kSwigluCtasPerSm);
     const long long cap = static_cast<long long>(host::num_sms()) * (tuned > 0 ? tuned : resident);
     const int grid = static_cast<int>(num_tokens < cap ? num_tokens : cap);
-    host::launch<kernel>(dim3(grid), dim3(kCT + 32), 0, stream, q, x_scale, gate, up, num_tokens, host::device_error_word());
+    // Launched WITHOUT the programmatic-dependent-launch attribute.  Four of these CTAs take an SM's whole
+    // register file (64 x 256 x 4), and a launch that carries the attribute gets only three per SM (measured:
+    // the fourth CTA of every SM then runs as a second wave on its own, 0.72 -> 0.96 ms at 65536 rows), which a
+    // persistent grid with a fixed row assignment cannot absorb.  The kernel still orders itself with
+    // griddepcontrol.wait (a no-op here) and still releases its own dependents early.
+    host::launch_plain<kernel>(dim3(grid), dim3(kCT + 32), 0, stream, q, x_scale, gate, up, num_tokens, host::device_error_word());
     return host::check_launch("swiglu_quant_ring_kernel");
 }
 
