@@ -254,8 +254,9 @@ __device__ __forceinline__ float2 sigmoid2(float2 g) {
 // multiply-adds on (d, -r) with no negated copy of d.  Every step is sign-symmetric, so the result is
 // exactly -sigmoid2<1>(g); rh_selftest checks it for every gate.  Same validity range as sigmoid2.
 // (Letting two or four gates share one reciprocal — seed = reciprocal of the product times the other
-// members — was measured too: it passes the parity tests but is no faster, and seeds a few units in the
-// last place off are not provably absorbed by one refinement step for 221 of the 65536 gates.)
+// members — was measured too: no faster at full clock, and not exact: over all 3.6e9 ordered pairs of bf16
+// gates the pair-shared sigmoid misrounds 306 264 of 7.2e9 halves, which the bf16 rounding of the product
+// hides from almost every test.)
 __device__ __forceinline__ float2 neg_sigmoid2(float2 g) {
     const float2 t = mul2_rn(g, splat2(-1.4426950408889634f));
     const float2 d = add2_rn(make_float2(ex2_approx(t.x), ex2_approx(t.y)), splat2(1.0f));
