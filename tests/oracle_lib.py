@@ -14,8 +14,9 @@ import os
 ROOT = Path(__file__).resolve().parent.parent
 ORACLE_DIR = ROOT / "oracle"
 # Where the reference's sources lie when they are present at all (the checkers under oracle/_ref are
-# built from them in place); REF overrides it, exactly as for oracle/Makefile.
-REFERENCE_ROOT = Path(os.environ.get("REF", "/root/reference"))
+# built from them in place): a checkout named `reference` beside this repository, or wherever REF points,
+# exactly as for oracle/Makefile.
+REFERENCE_ROOT = Path(os.environ.get("REF", str(ROOT.parent / "reference")))
 
 _p, _i, _f, _l = C.c_void_p, C.c_int, C.c_float, C.c_long
 _sz, _u64, _u32, _i32, _u16, _u8 = C.c_size_t, C.c_uint64, C.c_uint32, C.c_int32, C.c_uint16, C.c_uint8
