@@ -1006,7 +1006,9 @@ def time_end_to_end(cfg, ins, rows, total_bytes, world, barrier, max_over_ranks,
     import torch
     from runtherder_b200 import host_path
     weights = {k: ins[k] for k in ("g_attn", "inv_freq", "table")}
-    runner = host_path.HostSweep(cfg, rows, weights, chunk_rows=4096, n_slots=3, device=dev)
+    # at least eight chunks per step, so that the two copy directions and the kernels overlap on small shards too
+    chunk_rows = max(512, min(4096, rows // 8))
+    runner = host_path.HostSweep(cfg, rows, weights, chunk_rows=chunk_rows, n_slots=3, device=dev)
     host_in = runner.alloc_host_inputs(ins)
     host_out = runner.alloc_host_outputs()
     h2d, d2h = runner.bytes_per_step()
@@ -1029,7 +1031,8 @@ def time_end_to_end(cfg, ins, rows, total_bytes, world, barrier, max_over_ranks,
             "steps": steps, "h2d_bytes_per_step": int(h2d_all), "d2h_bytes_per_step": int(d2h_all),
             "pcie_gbs": {"h2d": round(h2d_all / (ms * 1e-3) / 1e9, 1), "d2h": round(d2h_all / (ms * 1e-3) / 1e9, 1)},
             "launches_per_step": n // steps, "pinned_near_gpu": runner.cpus is not None,
-            "what": "per 4096-row chunk: one pinned input record -> one H2D copy -> four fused kernels -> one D2H copy of "
+            "chunk_rows": chunk_rows,
+            "what": "per chunk of rows: one pinned input record -> one H2D copy -> four fused kernels -> one D2H copy of "
                     "the output record (+ the in-place rotated q); host-to-device, compute and device-to-host each on "
                     "their own stream; bounded by the PCIe link of each GPU"}
 
