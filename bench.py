@@ -619,6 +619,12 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
     use_graph = args.graph == "on" or (args.graph == "auto" and cfg.tokens == 1)
     launches_per_step = forward()
     torch.cuda.synchronize()
+    # Eager steps replay the forward's C-ABI calls as recorded once (same entry points, pointers and stream):
+    # what a C++ caller pays per launch, without the Python mirror's argument checks between the launches.
+    from runtherder_b200._lib import CallPlan
+    with CallPlan() as plan:
+        forward()
+    torch.cuda.synchronize()
     graph = None
     if use_graph:
         side = torch.cuda.Stream(device=dev)
@@ -629,7 +635,7 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
             with torch.cuda.graph(graph, stream=side):
                 forward()
         torch.cuda.synchronize()
-    step = graph.replay if graph is not None else forward
+    step = graph.replay if graph is not None else plan.replay
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -659,7 +665,9 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
                        "int8": cfg.int8, "qk_norm": cfg.qk_norm, "start_pos": cfg.start_pos, "seed": cfg.seed,
                        "ops_per_layer": [n for n, _ in cfg.chain_ops()] + (["attention (flash decode: 2 launches)" if T == 1 else "attention (flash prefill)"] if partial is not None else []),
                        "algorithmic_bytes_per_row_per_layer": per_row,
-                       "buffer_sets": n_sets, "cuda_graph": graph is not None, "parallelism": f"rows/{world}",
+                       "buffer_sets": n_sets, "cuda_graph": graph is not None,
+                       "launch_path": "one CUDA graph" if graph is not None else "recorded C-ABI calls replayed from Python",
+                       "parallelism": f"rows/{world}",
                        "l2": f"{n_sets} rotating buffer sets; a set is {'larger' if layer_bytes > 126e6 else 'smaller'} than the 126 MB L2"},
             "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step, "clocks": clocks.summary()}
 

@@ -82,8 +82,43 @@ def _load() -> C.CDLL:
 lib = _load()
 
 
+_recording = None   # the call list of the active CallPlan, if any
+
+
+class CallPlan:
+    """Records the C-ABI calls made inside its `with` block (they are executed as usual) and replays them:
+    the same entry points with the same pointers, sizes and stream, without the Python mirror's argument
+    checks in between — the launch cost a C++ caller of the library sees.  Only valid while the tensors whose
+    addresses were recorded are alive and for the stream that was current when it was recorded."""
+
+    def __init__(self):
+        self.calls = []
+
+    def __enter__(self):
+        global _recording
+        if _recording is not None:
+            raise RuntimeError("a CallPlan is already recording")
+        _recording = self.calls
+        return self
+
+    def __exit__(self, *exc):
+        global _recording
+        _recording = None
+
+    def replay(self) -> int:
+        """Issues every recorded call again; returns how many were issued."""
+        for fn, name, args in self.calls:
+            status = fn(*args)
+            if status != RH_OK:
+                raise RhError(name, status, lib.rh_last_error_string().decode())
+        return len(self.calls)
+
+
 def call(name: str, *args) -> None:
     """Invoke an rh_* entry point and raise RhError on a non-zero status."""
-    status = getattr(lib, name)(*args)
+    fn = getattr(lib, name)
+    if _recording is not None:
+        _recording.append((fn, name, args))
+    status = fn(*args)
     if status != RH_OK:
         raise RhError(name, status, lib.rh_last_error_string().decode())

@@ -198,3 +198,23 @@ def test_host_record_layout():
     assert v["q"].shape == (7, 24, 128) and v["ids"].shape == (7,) and v["codes"].dtype == torch.int8
     v["ids"][:] = torch.arange(7, dtype=torch.int32)
     assert rec.views(block)["ids"][:7].tolist() == list(range(7))         # views alias the block
+
+
+def test_call_plan_records_and_replays_c_abi_calls():
+    """_lib.CallPlan: calls made inside the block are executed and recorded; replay issues them again with
+    the same arguments; a failing call raises on replay as it does live."""
+    with _lib.CallPlan() as plan:
+        _lib.call("rh_tune", b"rows_ctas_per_sm", 3)
+        _lib.call("rh_tune", b"rows_ctas_per_sm", 0)
+    assert [name for _, name, _ in plan.calls] == ["rh_tune", "rh_tune"]
+    assert plan.replay() == 2
+    _lib.call("rh_tune", b"rows_ctas_per_sm", 0)                 # nothing is recorded outside the block
+    assert len(plan.calls) == 2
+    bad = _lib.CallPlan()
+    bad.calls.append((_lib.lib.rh_tune, "rh_tune", (b"no_such_knob", 1)))
+    with pytest.raises(_lib.RhError):
+        bad.replay()
+    with _lib.CallPlan():
+        with pytest.raises(RuntimeError):
+            with _lib.CallPlan():
+                pass
