@@ -937,9 +937,10 @@ def time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph
                 n += layer_ops.reference_sequence(ref, cfg, ins[l % n_sets], outs[l % n_sets], scratch, dedup_quant=dedup,
                                                   attention_partial=partial)
             return n
-        n = forward()
+        with ref.record() as plan:      # eager steps replay the recorded calls, like our own arm's
+            n = forward()
         torch.cuda.synchronize()
-        step = forward
+        step = plan.replay
         if use_graph:
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):

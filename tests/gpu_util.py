@@ -57,6 +57,31 @@ def ref_cuda_or_skip():
         pytest.skip(str(exc))
 
 
+class _RefCallPlan:
+    def __init__(self, owner):
+        self.owner, self.calls = owner, []
+
+    def __getattr__(self, name):        # stands in for the ctypes library while recording
+        fn = getattr(self.owner._real_lib, name)
+
+        def recorded(*args):
+            self.calls.append((fn, args))
+            return fn(*args)
+        return recorded
+
+    def __enter__(self):
+        self.owner.lib = self
+        return self
+
+    def __exit__(self, *exc):
+        self.owner.lib = self.owner._real_lib
+
+    def replay(self):
+        for fn, args in self.calls:
+            fn(*args)
+        return len(self.calls)
+
+
 class RefCuda:
     """The reference's kernels, callable with torch tensors under the reference's names."""
 
@@ -65,6 +90,13 @@ class RefCuda:
         if self.lib is None:   # a checkout without the reference's sources and without the prebuilt checker
             raise RefCudaUnavailable("oracle/_ref/libref_cuda.so is not present and the reference's sources "
                                      "are not available to build it")
+        self._real_lib = self.lib
+
+    def record(self):
+        """Context manager: the calls made inside are executed and also recorded; the returned object's
+        replay() issues them again with the same pointers and sizes, skipping the tensor-to-pointer
+        conversions (the launch cost a C++ caller of the reference's kernels sees)."""
+        return _RefCallPlan(self)
 
     def rmsnorm_bf16_forward(self, y, x, g, T, H, eps, stream=None):
         self.lib.refcuda_rmsnorm(y.data_ptr(), x.data_ptr(), g.data_ptr(), T, H, eps, _s(stream))

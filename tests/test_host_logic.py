@@ -218,3 +218,24 @@ def test_call_plan_records_and_replays_c_abi_calls():
         with pytest.raises(RuntimeError):
             with _lib.CallPlan():
                 pass
+
+
+def test_reference_call_plan_records_through_a_stand_in_library():
+    """gpu_util.RefCuda.record(): calls go to the real library and are replayed with the same arguments."""
+    import gpu_util
+
+    class FakeLib:
+        def __init__(self):
+            self.seen = []
+
+        def refcuda_swiglu(self, *args):
+            self.seen.append(args)
+
+    owner = gpu_util.RefCuda.__new__(gpu_util.RefCuda)
+    owner.lib = owner._real_lib = FakeLib()
+    with owner.record() as plan:
+        owner.lib.refcuda_swiglu(1, 2, 3, 4, None)
+    assert owner.lib is owner._real_lib
+    owner.lib.refcuda_swiglu(9, 9, 9, 9, None)       # not recorded
+    assert plan.replay() == 1
+    assert owner._real_lib.seen == [(1, 2, 3, 4, None), (9, 9, 9, 9, None), (1, 2, 3, 4, None)]
