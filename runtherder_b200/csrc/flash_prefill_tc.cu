@@ -14,6 +14,12 @@
 //        rescale their columns of O in tensor memory when the running maximum moved
 //     -> O[128 x 128] += W V: four tcgen05.mma (M=128, N=128, K=16) with W read from tensor memory and V
 //        read MN-major from shared memory exactly as the cache stores it.
+// The default form (kFrag) reads the scores in the tensor core's accumulator-fragment shape instead
+// (tcgen05.ld 16x256b): a warp owns 16 rows and all 64 keys of the tile, a thread two rows and sixteen keys —
+// four runs of four consecutive keys — so a row's maximum is two shuffles away, no value crosses a warp, and a
+// thread reads 48 per-key constants per tile instead of 96.  For the weights to land where the A operand of
+// O += W V expects them, the K rows of the tile are laid out in the order that makes S column
+// 16a + 8h + 2c + e hold key 16a + 4c + 2h + e.
 // One elected thread issues the products; completion comes back through mbarriers (tcgen05.commit).
 // Every mbarrier wait is bounded and agreed on by the whole CTA (__syncthreads_or), and every path out
 // of the kernel releases the tensor memory it allocated.
@@ -223,14 +229,46 @@ __device__ __forceinline__ void tmem_ld(float* v, uint32_t addr) {
         for (int c = 0; c < kN; c += 32) tmem_ld32(v + c, addr + c);
     }
 }
+// Accumulator-fragment shape: 16 lanes x (8 x kRep) 32-bit columns per warp.  Thread t holds, per group of 8
+// columns, columns 2 (t % 4) and 2 (t % 4) + 1 of lane t / 4 (registers 4 g, 4 g + 1) and of lane t / 4 + 8
+// (registers 4 g + 2, 4 g + 3).
+__device__ __forceinline__ void tmem_ld_frag_x8(uint32_t* r, uint32_t addr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_frag_x4(uint32_t* r, uint32_t addr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st_frag_x4(uint32_t addr, const uint32_t* w) {
+    asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
+                   "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
+}
 // barrier among the `count` threads that share named barrier `id`
 __device__ __forceinline__ void named_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
 // byte offset of 16-byte chunk `chunk` (0..7) of 128-byte row `row`, swizzled with the row
 __device__ __forceinline__ int swz128(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
 // grid (token tiles, num_kv_heads * head_chunks), 128 * kParts threads.
-template <int kParts>
+template <int kParts, bool kFrag = false>
 __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const Args p) {
+    static_assert(!kFrag || kParts == 2, "the fragment form is written for eight warps");
     constexpr int kThreads = 128 * kParts;
     constexpr int kC = kKeys / kParts;       // score columns per thread
     constexpr int kOC = kD / kParts;         // output columns per thread
@@ -288,10 +326,12 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
     constexpr int kStep = kThreads / 64;     // chunk stride between this thread's chunks of a row
     constexpr int kNch = 8 / kStep;          // chunks per row and matrix
     const int key_l = tid & 63, c0 = tid >> 6;
+    // the key whose K row becomes row key_l of the K operand tile (the fragment form's column order, see the top)
+    const int kkey = kFrag ? ((key_l & 48) | ((key_l & 6) << 1) | ((key_l & 8) >> 2) | (key_l & 1)) : key_l;
     const size_t row_stride = static_cast<size_t>(p.num_kv_heads) * kD;
-    const size_t head_off = static_cast<size_t>(key_l) * row_stride + static_cast<size_t>(kvh) * kD + c0 * 16;
-    const uint8_t* gk = p.k + head_off;
-    const uint8_t* gv = p.v + head_off;
+    const size_t head_off = static_cast<size_t>(kvh) * kD + c0 * 16;
+    const uint8_t* gk = p.k + static_cast<size_t>(kkey) * row_stride + head_off;
+    const uint8_t* gv = p.v + static_cast<size_t>(key_l) * row_stride + head_off;
     const size_t tile_bytes = static_cast<size_t>(kKeys) * row_stride;
     const float* gks = p.k_scale + static_cast<size_t>(key_l) * p.num_kv_heads + kvh;
     const float* gvs = p.v_scale + static_cast<size_t>(key_l) * p.num_kv_heads + kvh;
@@ -305,14 +345,15 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
     }
     // K rows (with both scale vectors) and V rows travel as separate cp.async groups, issued in the order
     // K0 V0 K1 V1 ...: a wait that leaves one group pending always covers the tile part needed next.
-    int next_key_k = key_l, next_key_v = key_l;          // this thread's key in the tile the next issue fetches
+    int next_key_k = kkey, next_key_v = key_l;           // this thread's key in the tile the next issue fetches
     auto issue_k = [&]() {
         const bool live = next_key_k < total_keys;
 #pragma unroll
         for (int t = 0; t < kNch; ++t) cp16_zfill(base + raw_off[t], live ? gk + t * kStep * 16 : p.k, live);
-        if (tid < kKeys) {
-            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + tid * 4, live ? gks : p.k_scale, live);
-            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + kKeys * 4 + tid * 4, live ? gvs : p.v_scale, live);
+        if (tid < kKeys) {                                // the scales stay in key order
+            const bool live_s = next_key_k - kkey + tid < total_keys;
+            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + tid * 4, live_s ? gks : p.k_scale, live_s);
+            cp4_zfill(base + kOffRaw + 2 * kKeys * kD + kKeys * 4 + tid * 4, live_s ? gvs : p.v_scale, live_s);
         }
         cp_async_commit();
         gk += tile_bytes;
@@ -410,6 +451,16 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
 
     float m_run = kMInit, l_run = 0.0f;      // m_run is the same in all threads of a row; l_run is this thread's part
     bool failed = false;
+    // fragment form: this thread's two rows (lanes 16 (warp / 4) + lane / 4 and + 8 of the warp's quarter) and
+    // their state; its keys are 16 a + 4 (lane % 4) + i, a and i in 0..3
+    const int lane = tid & 31;
+    const int c2 = lane & 3;
+    const int row_a = 32 * (warp & 3) + 16 * (warp >> 2) + (lane >> 2), row_b = row_a + 8;
+    const uint32_t my_lanes16 = static_cast<uint32_t>(32 * (warp & 3) + 16 * (warp >> 2)) << 16;
+    const int slot_a = row_a / p.tokens_per_cta, slot_b = row_b / p.tokens_per_cta;
+    const int tok_a = tok0 + (row_a - slot_a * p.tokens_per_cta), tok_b = tok0 + (row_b - slot_b * p.tokens_per_cta);
+    const int qpos_a = clen + tok_a, qpos_b = clen + tok_b;
+    float m_a = kMInit, m_b = kMInit, l_a = 0.0f, l_b = 0.0f;
 
     // ---- prologue: K of tile 0 converted, S_0 = Q K_0^T under way, V of tile 0 converted meanwhile ----
     cp_async_wait<1>();                                          // K rows and scales of tile 0 (V rows may be pending)
@@ -432,6 +483,93 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             if (!ok) failed = true;
         }
 
+        if constexpr (kFrag) {
+            // ---- two rows x sixteen keys per thread: scales, mask, maxima (two shuffles), weights, sums ----
+            const float* const cst = reinterpret_cast<const float*>(sm + kOffCst) + 4 * c2;
+            uint32_t sr[32];
+            tmem_ld_frag_x8(sr, tmem_s + my_lanes16);
+            // pair 2 (2 a + h): row a, keys 16 a + 4 c2 + 2 h + {0, 1}; pair 2 (2 a + h) + 1: the same keys of row b.
+            // Paired fp32 instructions (two IEEE operations per issue slot) carry the scaling, the shift by the
+            // maximum, the denominators and the rescale of O.
+            float2 sv[16];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float4 kk = *reinterpret_cast<const float4*>(cst + 16 * a);
+                const float4 lg = *reinterpret_cast<const float4*>(cst + kKeys + 16 * a);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int r = 4 * (2 * a + h);
+                    const float2 k2 = h ? make_float2(kk.z, kk.w) : make_float2(kk.x, kk.y);
+                    const float2 l2 = h ? make_float2(lg.z, lg.w) : make_float2(lg.x, lg.y);
+                    sv[r / 2] = fma2_rn(make_float2(__uint_as_float(sr[r]), __uint_as_float(sr[r + 1])), k2, l2);
+                    sv[r / 2 + 1] = fma2_rn(make_float2(__uint_as_float(sr[r + 2]), __uint_as_float(sr[r + 3])), k2, l2);
+                }
+            }
+            if (j * kKeys + kKeys - 1 > min(qpos_a, qpos_b)) {       // tiles that reach past a row's diagonal
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int key = j * kKeys + 16 * (g >> 1) + 4 * c2 + 2 * (g & 1);
+                    if (key > qpos_a) sv[2 * g].x = -INFINITY;
+                    if (key + 1 > qpos_a) sv[2 * g].y = -INFINITY;
+                    if (key > qpos_b) sv[2 * g + 1].x = -INFINITY;
+                    if (key + 1 > qpos_b) sv[2 * g + 1].y = -INFINITY;
+                }
+            }
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                mx_a = fmaxf(mx_a, fmaxf(sv[2 * g].x, sv[2 * g].y));
+                mx_b = fmaxf(mx_b, fmaxf(sv[2 * g + 1].x, sv[2 * g + 1].y));
+            }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            // the maximum is followed exactly (see the other form below)
+            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            const float corr_a = ex2f(m_a - mn_a), corr_b = ex2f(m_b - mn_b);
+            m_a = mn_a;
+            m_b = mn_b;
+            const float2 neg_a = splat2(-mn_a), neg_b = splat2(-mn_b);
+            float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+            uint32_t wv[16];                 // word 4 a + h: row a, keys 16 a + 4 c2 + 2 h + {0, 1}; 4 a + 2 + h: row b
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float4 rv = *reinterpret_cast<const float4*>(cst + 2 * kKeys + 16 * a);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int g = 2 * a + h;
+                    const float2 r2 = h ? make_float2(rv.z, rv.w) : make_float2(rv.x, rv.y);
+                    const float2 xa = add2_rn(sv[2 * g], neg_a), xb = add2_rn(sv[2 * g + 1], neg_b);
+                    const float2 ea = make_float2(ex2f(xa.x), ex2f(xa.y)), eb = make_float2(ex2f(xb.x), ex2f(xb.y));
+                    sum_a = fma2_rn(ea, r2, sum_a);
+                    sum_b = fma2_rn(eb, r2, sum_b);
+                    wv[4 * a + h] = pack_f16x2(ea.x, ea.y);
+                    wv[4 * a + 2 + h] = pack_f16x2(eb.x, eb.y);
+                }
+            }
+            tmem_st_frag_x4(tmem_w + my_lanes16, wv);
+            l_a = fmaf(l_a, corr_a, sum_a.x + sum_a.y);
+            l_b = fmaf(l_b, corr_b, sum_b.x + sum_b.y);
+            if (j > 0 && __any_sync(0xffffffffu, corr_a != 1.0f || corr_b != 1.0f)) {
+                const float2 ca = splat2(corr_a), cb2 = splat2(corr_b);
+#pragma unroll 1
+                for (int cb = 0; cb < kD; cb += 32) {
+                    uint32_t ov[16];
+                    tmem_ld_frag_x4(ov, tmem_o + my_lanes16 + cb);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const float2 oa = mul2_rn(make_float2(__uint_as_float(ov[4 * g]), __uint_as_float(ov[4 * g + 1])), ca);
+                        const float2 ob = mul2_rn(make_float2(__uint_as_float(ov[4 * g + 2]), __uint_as_float(ov[4 * g + 3])), cb2);
+                        ov[4 * g] = __float_as_uint(oa.x);
+                        ov[4 * g + 1] = __float_as_uint(oa.y);
+                        ov[4 * g + 2] = __float_as_uint(ob.x);
+                        ov[4 * g + 3] = __float_as_uint(ob.y);
+                    }
+                    tmem_st_frag_x4(tmem_o + my_lanes16 + cb, ov);
+                }
+            }
+        } else {
         // ---- this thread's kC scores of its row: scales, mask, maximum ----
         const float* const cst = reinterpret_cast<const float*>(sm + kOffCst) + part * kC;
         const int key0 = j * kKeys + part * kC;
@@ -500,6 +638,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
                 tmem_st32(tmem_o + my_lane + part * kOC + cb, ov);
             }
         }
+        }   // !kFrag
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         fence_async_smem();
         tc_fence_before();
@@ -538,6 +677,33 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
         tc_fence_after();
         if (!ok) failed = true;
     }
+    if constexpr (kFrag) {
+        if (!__syncthreads_or(failed) && n_tiles > 0) {
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            const float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
+            const int hig_a = chunk * p.heads_per_cta + slot_a, hig_b = chunk * p.heads_per_cta + slot_b;
+            const bool valid_a = hig_a < p.group && tok_a < p.n_new, valid_b = hig_b < p.group && tok_b < p.n_new;
+            __nv_bfloat16* const dst_a = p.out + (static_cast<size_t>(valid_a ? tok_a : 0) * p.num_q_heads + (valid_a ? kvh * p.group + hig_a : 0)) * kD + 2 * c2;
+            __nv_bfloat16* const dst_b = p.out + (static_cast<size_t>(valid_b ? tok_b : 0) * p.num_q_heads + (valid_b ? kvh * p.group + hig_b : 0)) * kD + 2 * c2;
+#pragma unroll 1
+            for (int cb = 0; cb < kD; cb += 32) {
+                uint32_t ov[16];
+                tmem_ld_frag_x4(ov, tmem_o + my_lanes16 + cb);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if (valid_a)
+                        *reinterpret_cast<__nv_bfloat162*>(dst_a + cb + 8 * g) =
+                            __floats2bfloat162_rn(__uint_as_float(ov[4 * g]) * inv_a, __uint_as_float(ov[4 * g + 1]) * inv_a);
+                    if (valid_b)
+                        *reinterpret_cast<__nv_bfloat162*>(dst_b + cb + 8 * g) =
+                            __floats2bfloat162_rn(__uint_as_float(ov[4 * g + 2]) * inv_b, __uint_as_float(ov[4 * g + 3]) * inv_b);
+                }
+            }
+        }
+    } else {
     if constexpr (kParts > 1) xch[part * kRows + row] = l_run;     // last read of xch was before the loop's final barrier
     if (!__syncthreads_or(failed) && n_tiles > 0) {
         float l_row = l_run;
@@ -566,6 +732,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             }
         }
     }
+    }   // !kFrag
     cp_async_wait<0>();
     tc_fence_before();
     __syncthreads();
@@ -600,12 +767,16 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     const dim3 grid(static_cast<unsigned>((n_new + a.tokens_per_cta - 1) / a.tokens_per_cta),
                     static_cast<unsigned>(num_kv_heads * a.head_chunks));
     RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
-    // "prefill_parts" 1|2|4; +20 pads the shared-memory request so that one CTA fits per SM (a measuring aid)
+    // "prefill_parts": 0 or 3 the fragment form; 1|2|4 threads per score row (one lane = one row);
+    // +20 pads the shared-memory request so that one CTA fits per SM (a measuring aid)
     const int knob = host::tuning(host::kPrefillParts);
     const int parts = knob >= 20 ? knob - 20 : knob;
     const size_t smem = knob >= 20 ? 120u * 1024u : static_cast<size_t>(tc::kSmemBytes);
     constexpr size_t kOptIn = 120u * 1024u;   // the padded request is the largest one
-    if (parts == 1) {
+    if (parts <= 0 || parts == 3) {
+        (void)host::setup<&tc::flash_prefill_tc_kernel<2, true>, 256, kOptIn>();
+        host::launch<tc::flash_prefill_tc_kernel<2, true>>(grid, dim3(256), smem, stream, a);
+    } else if (parts == 1) {
         (void)host::setup<&tc::flash_prefill_tc_kernel<1>, 128, kOptIn>();
         host::launch<tc::flash_prefill_tc_kernel<1>>(grid, dim3(128), smem, stream, a);
     } else if (parts == 4) {
