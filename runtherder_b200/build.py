@@ -24,7 +24,7 @@ LIB = OUT / "librh_kernels.so"
 LINEAR_LIB = OUT / "librh_linear.so"
 LINEAR_SOURCES = ["linear_w8a8.cu"]
 
-SOURCES = ["capi.cu", "rows.cu", "swiglu.cu", "rope_kv.cu", "embedding.cu", "flash_decode.cu", "flash_prefill.cu", "flash_prefill_tc.cu", "synth.cu", "dropin.cu", "selftest_static.cu"]
+SOURCES = ["capi.cu", "rows.cu", "swiglu.cu", "rope_kv.cu", "embedding.cu", "flash_decode.cu", "flash_prefill.cu", "flash_prefill_tc.cu", "flash_prefill_ws.cu", "synth.cu", "dropin.cu", "selftest_static.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -28,242 +28,11 @@
 
 #include <atomic>
 
-#include "rh_common.cuh"
+#include "flash_prefill_tc.cuh"
 #include "rh_kernels.h"
-#include "rh_pipeline.cuh"
 
 namespace rh {
 namespace tc {
-
-constexpr int kD = 128;          // head_dim
-constexpr int kKeys = 64;        // keys per tile (N of the first product, K of the second)
-constexpr int kRows = 128;       // query rows per CTA (M)
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kMInit = -1.0e30f;
-constexpr float kLgFloor = -100.0f;
-constexpr int kTmemCols = 256;   // S: 64 columns, O: 128, W (f16 pairs): 32, upper half of Q (f16 pairs): 32
-constexpr uint32_t kSuspendNs = 20000;   // longest hardware sleep per mbarrier try
-constexpr int kWaitLimit = 1 << 16;   // polls; each try_wait already blocks for a while in hardware
-
-// shared-memory map, relative to a 1024-byte aligned base
-constexpr int kOffQ = 0;                        // [128 rows][128 B]: dims 0..63 of Q (dims 64..127 live in tensor memory)  16 KB
-constexpr int kOffK = kOffQ + kRows * 128;      // [2 dim blocks][64 keys][128 B]    16 KB
-constexpr int kOffV = kOffK + 2 * kKeys * 128;  // [2 dim blocks][64 keys][128 B]    16 KB (read MN-major)
-constexpr int kOffRaw = kOffV + 2 * kKeys * 128;   // raw K, raw V (8 KB each), 64 + 64 scales
-constexpr int kOffCst = kOffRaw + 2 * kKeys * kD + 2 * kKeys * 4;   // ksl[64], lgv[64], rvs[64]
-constexpr int kOffXch = kOffCst + 3 * kKeys * 4;                    // row maxima / sums exchanged between a row's threads: [4][128]
-constexpr int kOffBar = kOffXch + 4 * kRows * 4;                    // two mbarriers, the tmem base
-constexpr int kSmemBytes = kOffBar + 32 + 1024;                     // + slack for the alignment
-
-struct Args {
-    __nv_bfloat16* out;
-    const __nv_bfloat16* q;
-    const uint8_t* k;
-    const uint8_t* v;
-    const float* k_scale;
-    const float* v_scale;
-    const int* cache_len;
-    int* error_word;
-    int n_new;
-    int num_q_heads;
-    int num_kv_heads;
-    int group;           // query heads per kv head
-    int heads_per_cta;   // 1, 2 or 4
-    int tokens_per_cta;  // 128 / heads_per_cta
-    int head_chunks;     // ceil(group / heads_per_cta)
-    float scale_log2e;
-};
-
-__device__ __forceinline__ void e4m3x4_to_f16x2x2(uint32_t word, uint32_t& lo, uint32_t& hi) {
-    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
-        : "=r"(lo), "=r"(hi)
-        : "r"(word));
-}
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-    const __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-__device__ __forceinline__ float ex2f(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float lg2f(float x) {
-    float y;
-    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ void cp16_zfill(uint32_t dst, const void* src, bool valid) {
-    const int bytes = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp4_zfill(uint32_t dst, const void* src, bool valid) {
-    const int bytes = valid ? 4 : 0;
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-// Bounded wait on an mbarrier phase.  The suspend-time hint lets a waiting thread sleep in hardware up to
-// that long per try instead of polling, so waiting warps leave the issue slots to the warps with work.
-__device__ __forceinline__ bool mbar_wait_quiet(uint64_t* bar, uint32_t parity, int where, int* error_word) {
-    const uint32_t addr = pipe::smem_u32(bar);
-    for (int i = 0; i < kWaitLimit; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(addr), "r"(parity), "r"(kSuspendNs)
-            : "memory");
-        if (ok != 0) return true;
-    }
-    if (error_word != nullptr) atomicCAS(error_word, 0, (where << 8) | 1);
-    return false;
-}
-// generic-proxy writes to shared memory -> visible to the tensor core's (async proxy) reads
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (SBO), operand blocks
-// `lbo_bytes` apart in the leading dimension (used by the MN-major operand only).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);              // start address, 16-byte units
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;    // leading-dimension byte offset
-    d |= static_cast<uint64_t>((1024u >> 4) & 0x3FFFu) << 32;        // stride-dimension byte offset
-    d |= static_cast<uint64_t>(1) << 46;                             // descriptor version of this architecture
-    d |= static_cast<uint64_t>(2) << 61;                             // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: f16 x f16 -> f32, M = 128, N = n, A K-major, B K-major or MN-major.
-__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
-    return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kRows >> 4) << 24);
-}
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
-        : "memory");
-}
-// the same product with the A operand in tensor memory (row = lane, two f16 values per 32-bit column)
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(pipe::smem_u32(bar)) : "memory");
-}
-// 32 consecutive fp32 columns of this thread's tensor-memory lane
-__device__ __forceinline__ void tmem_ld32(float* v, uint32_t addr) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(addr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_st32(uint32_t addr, const float* v) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
-          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
-          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
-          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
-          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
-          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
-          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
-          "r"(__float_as_uint(v[31]))
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(float* v, uint32_t addr) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-// kN consecutive 32-bit columns of this thread's lane, from registers
-template <int kN>
-__device__ __forceinline__ void tmem_st_words(uint32_t addr, const uint32_t* w) {
-    static_assert(kN == 8 || kN == 16 || kN == 32, "columns per thread");
-    if constexpr (kN == 8) {
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                     ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-    } else if constexpr (kN == 16) {
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                     ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
-                       "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
-    } else {
-        tmem_st_words<16>(addr, w);
-        tmem_st_words<16>(addr + 16, w + 16);
-    }
-}
-template <int kN>
-__device__ __forceinline__ void tmem_ld(float* v, uint32_t addr) {
-    static_assert(kN == 16 || kN == 32 || kN == 64, "columns per thread");
-    if constexpr (kN == 16) {
-        tmem_ld16(v, addr);
-    } else {
-#pragma unroll
-        for (int c = 0; c < kN; c += 32) tmem_ld32(v + c, addr + c);
-    }
-}
-// Accumulator-fragment shape: 16 lanes x (8 x kRep) 32-bit columns per warp.  Thread t holds, per group of 8
-// columns, columns 2 (t % 4) and 2 (t % 4) + 1 of lane t / 4 (registers 4 g, 4 g + 1) and of lane t / 4 + 8
-// (registers 4 g + 2, 4 g + 3).
-__device__ __forceinline__ void tmem_ld_frag_x8(uint32_t* r, uint32_t addr) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(addr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_ld_frag_x4(uint32_t* r, uint32_t addr) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_st_frag_x4(uint32_t addr, const uint32_t* w) {
-    asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                 ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
-                   "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
-}
-// barrier among the `count` threads that share named barrier `id`
-__device__ __forceinline__ void named_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
-// byte offset of 16-byte chunk `chunk` (0..7) of 128-byte row `row`, swizzled with the row
-__device__ __forceinline__ int swz128(int row, int chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
 
 // grid (token tiles, num_kv_heads * head_chunks), 128 * kParts threads.
 template <int kParts, bool kFrag = false>
@@ -743,6 +512,8 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
 
 }  // namespace tc
 
+int launch_flash_prefill_ws(const tc::Args& a, dim3 grid, cudaStream_t stream, const char* fn);   // flash_prefill_ws.cu
+
 // Launcher used by rh_flash_prefill_bf16 when the tensor-memory form is selected.
 int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const uint8_t* v, const float* k_scale,
                             const float* v_scale, int n_new, const int* cache_len, int num_q_heads, int num_kv_heads,
@@ -773,6 +544,7 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     const int parts = knob >= 20 ? knob - 20 : knob;
     const size_t smem = knob >= 20 ? 120u * 1024u : static_cast<size_t>(tc::kSmemBytes);
     constexpr size_t kOptIn = 120u * 1024u;   // the padded request is the largest one
+    if (parts == 5) return launch_flash_prefill_ws(a, grid, stream, fn);
     if (parts <= 0 || parts == 3) {
         (void)host::setup<&tc::flash_prefill_tc_kernel<2, true>, 256, kOptIn>();
         host::launch<tc::flash_prefill_tc_kernel<2, true>>(grid, dim3(256), smem, stream, a);
