@@ -512,7 +512,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
 
 }  // namespace tc
 
-int launch_flash_prefill_ws(const tc::Args& a, dim3 grid, cudaStream_t stream, const char* fn);   // flash_prefill_ws.cu
+int launch_flash_prefill_ws(const tc::Args& a, int blocks, cudaStream_t stream, const char* fn);   // flash_prefill_ws.cu
 
 // Launcher used by rh_flash_prefill_bf16 when the tensor-memory form is selected.
 int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const uint8_t* v, const float* k_scale,
@@ -544,7 +544,7 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     const int parts = knob >= 20 ? knob - 20 : knob;
     const size_t smem = knob >= 20 ? 120u * 1024u : static_cast<size_t>(tc::kSmemBytes);
     constexpr size_t kOptIn = 120u * 1024u;   // the padded request is the largest one
-    if (parts == 5) return launch_flash_prefill_ws(a, grid, stream, fn);
+    if (parts == 5 || parts == 6) return launch_flash_prefill_ws(a, parts - 4, stream, fn);
     if (parts <= 0 || parts == 3) {
         (void)host::setup<&tc::flash_prefill_tc_kernel<2, true>, 256, kOptIn>();
         host::launch<tc::flash_prefill_tc_kernel<2, true>>(grid, dim3(256), smem, stream, a);

@@ -33,29 +33,41 @@ namespace ws {
 
 using namespace tc;
 
-constexpr int kSoftmaxWarps = 8;
-constexpr int kConvWarps = 3;
-constexpr int kConvThreads = 32 * kConvWarps;
-constexpr int kIssuerWarp = kSoftmaxWarps;
-constexpr int kThreads = 32 * (kSoftmaxWarps + 1 + kConvWarps);     // 384
-constexpr int kChunks = kKeys * 8;                                  // 16-byte chunks per raw tile
-constexpr int kPerConv = (kChunks + kConvThreads - 1) / kConvThreads;   // 6 (the last one only in the first warp)
+constexpr int kChunks = kKeys * 8;                       // 16-byte chunks per raw tile
 constexpr int kCstRing = 4;        // constants of tile j are read while those of tiles j+1, j+2 are written
-
-// shared-memory map, relative to a 1024-byte aligned base
-constexpr int kSQ = 0;                                   // [128 rows][128 B]: dims 0..63 of Q            16 KB
 constexpr int kTileBytes = 2 * kKeys * 128;              // an f16 operand tile: [2 dim blocks][64 keys][128 B]   16 KB
-constexpr int kSK = kSQ + kRows * 128;                   // two K tiles                                   32 KB
-constexpr int kSV = kSK + 2 * kTileBytes;                // two V tiles                                   32 KB
-constexpr int kSRawK = kSV + 2 * kTileBytes;             // raw K rows                                     8 KB
-constexpr int kSRawV = kSRawK + kKeys * kD;              // raw V rows                                     8 KB
-constexpr int kSRawS = kSRawV + kKeys * kD;              // 64 K scales, 64 V scales
-constexpr int kSCst = kSRawS + 2 * kKeys * 4;            // ring of {ksl[64], lgv[64], rvs[64]}
-constexpr int kSBar = kSCst + kCstRing * 3 * kKeys * 4;  // mbarriers, tensor-memory base, give-up flag
-constexpr int kSmemBytes = kSBar + 128 + 1024;
 
-// tile j uses entry j % 2 of the paired barriers, in that entry's phase j / 2
-enum Bar { kBarQK0 = 0, kBarQK1, kBarPV0, kBarPV1, kBarSRead, kBarWReady, kBarKReady0, kBarKReady1, kBarVReady0, kBarVReady1, kNumBars };
+// A CTA carries kBlocks row blocks of 128 query rows (consecutive token ranges of the same kv head and head
+// chunk) that share the converted K and V tiles: one block with two CTAs per SM, or two blocks in one CTA per
+// SM, where a tile is converted once for twice the rows.
+template <int kBlocks>
+struct Geo {
+    static constexpr int kSoftmaxWarps = 8 * kBlocks;
+    static constexpr int kIssuerWarp0 = kSoftmaxWarps;               // one product warp per row block
+    static constexpr int kConvWarp0 = kSoftmaxWarps + kBlocks;
+    static constexpr int kConvWarps = kBlocks == 1 ? 3 : 4;
+    static constexpr int kConvThreads = 32 * kConvWarps;
+    static constexpr int kThreads = 32 * (kConvWarp0 + kConvWarps);  // 384 or 704
+    static constexpr int kPerConv = (kChunks + kConvThreads - 1) / kConvThreads;
+    static constexpr int kTmem = kTmemCols * kBlocks;
+    // shared-memory map, relative to a 1024-byte aligned base
+    static constexpr int kSQ = 0;                                    // per block [128 rows][128 B]: dims 0..63 of Q
+    static constexpr int kSK = kSQ + kBlocks * kRows * 128;          // two K tiles                               32 KB
+    static constexpr int kSV = kSK + 2 * kTileBytes;                 // two V tiles                               32 KB
+    static constexpr int kSRawK = kSV + 2 * kTileBytes;              // raw K rows                                 8 KB
+    static constexpr int kSRawV = kSRawK + kKeys * kD;               // raw V rows                                 8 KB
+    static constexpr int kSRawS = kSRawV + kKeys * kD;               // 64 K scales, 64 V scales
+    static constexpr int kSCst = kSRawS + 2 * kKeys * 4;             // ring of {ksl[64], lgv[64], rvs[64]}
+    static constexpr int kSBar = kSCst + kCstRing * 3 * kKeys * 4;   // mbarriers, tensor-memory base, give-up flag
+    static constexpr int kSmemBytes = kSBar + 256 + 1024;
+    // mbarriers: per row block {S complete x2, O += W V complete x2, S read, W ready}, then K ready x2, V ready x2;
+    // tile j uses entry j % 2 of the paired ones, in that entry's phase j / 2
+    static constexpr int kBarsPerBlock = 6;
+    static constexpr int kBarKReady = kBarsPerBlock * kBlocks;
+    static constexpr int kBarVReady = kBarKReady + 2;
+    static constexpr int kNumBars = kBarVReady + 2;
+};
+enum BlockBar { kBarQK = 0, kBarPV = 2, kBarSRead = 4, kBarWReady = 5 };
 
 constexpr int kTries = 1 << 20;
 
@@ -82,55 +94,71 @@ __device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volat
 // the key whose K row becomes row r of the K operand tile (S column 16a + 8h + 2c + e holds key 16a + 4c + 2h + e)
 __device__ __forceinline__ int key_of_k_row(int r) { return (r & 48) | ((r & 6) << 1) | ((r & 8) >> 2) | (r & 1); }
 
-__global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Args p) {
+// grid (token tiles of kBlocks * tokens_per_cta tokens, num_kv_heads * head_chunks)
+template <int kBlocks>
+__global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_prefill_ws_kernel(const Args p) {
+    using G = Geo<kBlocks>;
     extern __shared__ unsigned char raw_smem[];
     const uint32_t base = (pipe::smem_u32(raw_smem) + 1023u) & ~1023u;          // shared-space address, 1 KB aligned
     unsigned char* const sm = raw_smem + (base - pipe::smem_u32(raw_smem));     // the same place, generic pointer
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(sm + kSBar);
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(sm + kSBar + 8 * kNumBars);
-    volatile int* const gave_up = reinterpret_cast<volatile int*>(sm + kSBar + 8 * kNumBars + 8);
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(sm + G::kSBar);
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(sm + G::kSBar + 8 * G::kNumBars);
+    volatile int* const gave_up = reinterpret_cast<volatile int*>(sm + G::kSBar + 8 * G::kNumBars + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.y / p.head_chunks;
     const int chunk = blockIdx.y - kvh * p.head_chunks;
     const int tile = gridDim.x - 1 - blockIdx.x;            // long (late) token tiles first
-    const int tok0 = tile * p.tokens_per_cta;
+    const int cta_tok0 = tile * (kBlocks * p.tokens_per_cta);
 
     if (tid == 0) {
-        pipe::mbar_init(&bars[kBarQK0], 1);
-        pipe::mbar_init(&bars[kBarQK1], 1);
-        pipe::mbar_init(&bars[kBarPV0], 1);
-        pipe::mbar_init(&bars[kBarPV1], 1);
-        pipe::mbar_init(&bars[kBarSRead], kSoftmaxWarps);
-        pipe::mbar_init(&bars[kBarWReady], kSoftmaxWarps);
-        pipe::mbar_init(&bars[kBarKReady0], kConvThreads);
-        pipe::mbar_init(&bars[kBarKReady1], kConvThreads);
-        pipe::mbar_init(&bars[kBarVReady0], kConvThreads);
-        pipe::mbar_init(&bars[kBarVReady1], kConvThreads);
+#pragma unroll
+        for (int g = 0; g < kBlocks; ++g) {
+            uint64_t* const bb = bars + g * G::kBarsPerBlock;
+            pipe::mbar_init(&bb[kBarQK], 1);
+            pipe::mbar_init(&bb[kBarQK + 1], 1);
+            pipe::mbar_init(&bb[kBarPV], 1);
+            pipe::mbar_init(&bb[kBarPV + 1], 1);
+            pipe::mbar_init(&bb[kBarSRead], 8);
+            pipe::mbar_init(&bb[kBarWReady], 8);
+        }
+        pipe::mbar_init(&bars[G::kBarKReady], G::kConvThreads);
+        pipe::mbar_init(&bars[G::kBarKReady + 1], G::kConvThreads);
+        pipe::mbar_init(&bars[G::kBarVReady], G::kConvThreads);
+        pipe::mbar_init(&bars[G::kBarVReady + 1], G::kConvThreads);
         *gave_up = 0;
         pipe::mbar_init_fence();
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pipe::smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(pipe::smem_u32(tmem_slot)), "r"(G::kTmem) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + kKeys, tmem_w = tmem + kKeys + kD;   // column offsets
-    const uint32_t tmem_q = tmem_w + kKeys / 2;
 
     pdl_enter();
     const int clen = *p.cache_len;
     const int total_keys = clen + p.n_new;
-    const int last_tok = min(tok0 + p.tokens_per_cta, p.n_new) - 1;
+    const int last_tok = min(cta_tok0 + kBlocks * p.tokens_per_cta, p.n_new) - 1;
+    // every row block walks the tiles the CTA's last token needs (an earlier block finds its last tile masked)
     const int n_tiles = min((total_keys + kKeys - 1) / kKeys, (clen + last_tok) / kKeys + 1);
 
-    // ---- Q (softmax warps): row tid % 128, bf16 -> f16; dims 0..63 to shared memory ([row][128 bytes, swizzled]) by
-    //      the first four warps, dims 64..127 to tensor memory (row = lane, two f16 per column) by the other four ----
-    if (warp < kSoftmaxWarps) {
-        const int row = tid & (kRows - 1), part = tid >> 7;
+    // this warp's row block (softmax and product warps) and that block's tensor memory: S 64 columns, O 128,
+    // W (f16 pairs) 32, the upper half of Q (f16 pairs) 32
+    const int blk = warp < G::kSoftmaxWarps ? warp >> 3 : (warp < G::kConvWarp0 ? warp - G::kIssuerWarp0 : 0);
+    const int wb = warp & 7;                                 // warp within the block's softmax warps
+    const int tok0 = cta_tok0 + blk * p.tokens_per_cta;
+    uint64_t* const bb = bars + blk * G::kBarsPerBlock;
+    const uint32_t tmem_s = tmem + blk * kTmemCols, tmem_o = tmem_s + kKeys, tmem_w = tmem_o + kD, tmem_q = tmem_w + kKeys / 2;
+    const int q_off = G::kSQ + blk * (kRows * 128);
+
+    // ---- Q (softmax warps): row of the block, bf16 -> f16; dims 0..63 to shared memory ([row][128 bytes, swizzled])
+    //      by the block's first four warps, dims 64..127 to tensor memory (row = lane, two f16 per column) by the
+    //      other four ----
+    if (warp < G::kSoftmaxWarps) {
+        const int row = 32 * (wb & 3) + lane, part = wb >> 2;
         const int head_slot = row / p.tokens_per_cta;
         const int tok = tok0 + (row - head_slot * p.tokens_per_cta);
         const int head_in_group = chunk * p.heads_per_cta + head_slot;
@@ -149,9 +177,9 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
         };
         if (part == 0) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sm + kSQ + swz128(row, c)) = load_chunk(c);
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sm + q_off + swz128(row, c)) = load_chunk(c);
         } else {
-            const uint32_t my_lane = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+            const uint32_t my_lane = static_cast<uint32_t>(32 * (wb & 3)) << 16;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t qw[16];
@@ -173,13 +201,13 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
     __syncthreads();
     tc_fence_after();
 
-    if (warp < kSoftmaxWarps) {
+    if (warp < G::kSoftmaxWarps) {
         // =============================== softmax ===============================
-        // this thread's two rows (lanes 16 (warp / 4) + lane / 4 and + 8 of the warp's quarter); its keys are
+        // this thread's two rows (lanes 16 (wb / 4) + lane / 4 and + 8 of the warp's quarter); its keys are
         // 16 a + 4 (lane % 4) + i, a and i in 0..3
         const int c2 = lane & 3;
-        const int row_a = 32 * (warp & 3) + 16 * (warp >> 2) + (lane >> 2), row_b = row_a + 8;
-        const uint32_t my_lanes16 = static_cast<uint32_t>(32 * (warp & 3) + 16 * (warp >> 2)) << 16;
+        const int row_a = 32 * (wb & 3) + 16 * (wb >> 2) + (lane >> 2), row_b = row_a + 8;
+        const uint32_t my_lanes16 = static_cast<uint32_t>(32 * (wb & 3) + 16 * (wb >> 2)) << 16;
         const int slot_a = row_a / p.tokens_per_cta, slot_b = row_b / p.tokens_per_cta;
         const int tok_a = tok0 + (row_a - slot_a * p.tokens_per_cta), tok_b = tok0 + (row_b - slot_b * p.tokens_per_cta);
         const int qpos_a = clen + tok_a, qpos_b = clen + tok_b;
@@ -187,17 +215,19 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
         float m_a = kMInit, m_b = kMInit, l_a = 0.0f, l_b = 0.0f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
-            ok = wait_phase(&bars[kBarQK0 + (j & 1)], (j >> 1) & 1, gave_up, __LINE__, p.error_word);
+            ok = wait_phase(&bb[kBarQK + (j & 1)], (j >> 1) & 1, gave_up, __LINE__, p.error_word);
             if (!ok) break;
             tc_fence_after();
             uint32_t sr[32];
             tmem_ld_frag_x8(sr, tmem_s + my_lanes16);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) pipe::mbar_arrive(&bars[kBarSRead]);          // S may be overwritten by the next product
+            if (lane == 0) pipe::mbar_arrive(&bb[kBarSRead]);            // S may be overwritten by the next product
 
-            const float* const cst = reinterpret_cast<const float*>(sm + kSCst) + (j & (kCstRing - 1)) * 3 * kKeys + 4 * c2;
-            // pair 2 (2 a + h): row a, keys 16 a + 4 c2 + 2 h + {0, 1}; pair 2 (2 a + h) + 1: the same keys of row b
+            const float* const cst = reinterpret_cast<const float*>(sm + G::kSCst) + (j & (kCstRing - 1)) * 3 * kKeys + 4 * c2;
+            // pair 2 (2 a + h): row a, keys 16 a + 4 c2 + 2 h + {0, 1}; pair 2 (2 a + h) + 1: the same keys of row b.
+            // Paired fp32 instructions (two IEEE operations per issue slot) carry the scaling, the shift by the
+            // maximum, the denominators and the rescale of O.
             float2 sv[16];
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
@@ -260,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
             l_b = fmaf(l_b, corr_b, sum_b.x + sum_b.y);
             // W and O are free once O += W_{j-1} V_{j-1} has completed
             if (j > 0) {
-                ok = wait_phase(&bars[kBarPV0 + ((j - 1) & 1)], ((j - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
+                ok = wait_phase(&bb[kBarPV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
                 if (!ok) break;
                 tc_fence_after();
             }
@@ -286,11 +316,11 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) pipe::mbar_arrive(&bars[kBarWReady]);
+            if (lane == 0) pipe::mbar_arrive(&bb[kBarWReady]);
         }
         // ---- epilogue: normalise and store this thread's two rows ----
         if (ok && n_tiles > 0)
-            ok = wait_phase(&bars[kBarPV0 + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
+            ok = wait_phase(&bb[kBarPV + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
         if (ok && n_tiles > 0) {
             tc_fence_after();
             l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -317,59 +347,60 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
                 }
             }
         }
-    } else if (warp == kIssuerWarp) {
-        // =============================== products ===============================
+    } else if (warp < G::kConvWarp0) {
+        // =============================== products of row block `blk` ===============================
         constexpr uint32_t kIdescQK = instr_desc(kKeys, false);
         constexpr uint32_t kIdescPV = instr_desc(kD, true);
         auto issue_qk = [&](int tile_j) {                     // S = Q K^T: eight products of depth 16
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t k_base = base + kSK + (tile_j & 1) * kTileBytes;
+                const uint32_t k_base = base + G::kSK + (tile_j & 1) * kTileBytes;
 #pragma unroll
                 for (int s = 0; s < 4; ++s)       // dims 0..63: both operands from shared memory
-                    umma_f16(tmem_s, smem_desc(base + kSQ + s * 32, 16), smem_desc(k_base + s * 32, 16), kIdescQK, s > 0);
+                    umma_f16(tmem_s, smem_desc(base + q_off + s * 32, 16), smem_desc(k_base + s * 32, 16), kIdescQK, s > 0);
 #pragma unroll
                 for (int s = 0; s < 4; ++s)       // dims 64..127: Q from tensor memory
                     umma_f16_ts(tmem_s, tmem_q + s * 8, smem_desc(k_base + kKeys * 128 + s * 32, 16), kIdescQK, true);
-                umma_commit(&bars[kBarQK0 + (tile_j & 1)]);
+                umma_commit(&bb[kBarQK + (tile_j & 1)]);
             }
             __syncwarp();
         };
-        bool ok = wait_phase(&bars[kBarKReady0], 0, gave_up, __LINE__, p.error_word);
+        bool ok = wait_phase(&bars[G::kBarKReady], 0, gave_up, __LINE__, p.error_word);
         if (ok) issue_qk(0);
         for (int j = 0; j < n_tiles && ok; ++j) {
             if (j + 1 < n_tiles) {
-                ok = wait_phase(&bars[kBarSRead], j & 1, gave_up, __LINE__, p.error_word) &&
-                     wait_phase(&bars[kBarKReady0 + ((j + 1) & 1)], ((j + 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
+                ok = wait_phase(&bb[kBarSRead], j & 1, gave_up, __LINE__, p.error_word) &&
+                     wait_phase(&bars[G::kBarKReady + ((j + 1) & 1)], ((j + 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
                 if (!ok) break;
                 issue_qk(j + 1);
             }
-            ok = wait_phase(&bars[kBarWReady], j & 1, gave_up, __LINE__, p.error_word) &&
-                 wait_phase(&bars[kBarVReady0 + (j & 1)], (j >> 1) & 1, gave_up, __LINE__, p.error_word);
+            ok = wait_phase(&bb[kBarWReady], j & 1, gave_up, __LINE__, p.error_word) &&
+                 wait_phase(&bars[G::kBarVReady + (j & 1)], (j >> 1) & 1, gave_up, __LINE__, p.error_word);
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t v_base = base + kSV + (j & 1) * kTileBytes;
+                const uint32_t v_base = base + G::kSV + (j & 1) * kTileBytes;
 #pragma unroll
                 for (int s = 0; s < kKeys / 16; ++s)
                     umma_f16_ts(tmem_o, tmem_w + s * 8, smem_desc(v_base + s * 2048, kKeys * 128), kIdescPV, j > 0 || s > 0);
-                umma_commit(&bars[kBarPV0 + (j & 1)]);
+                umma_commit(&bb[kBarPV + (j & 1)]);
             }
             __syncwarp();
         }
     } else {
         // =============================== conversion ===============================
-        const int t = tid - 32 * (kIssuerWarp + 1);          // 0..95
+        constexpr int kPerConv = G::kPerConv;
+        const int t = tid - 32 * G::kConvWarp0;
         const uint32_t row_stride = static_cast<uint32_t>(p.num_kv_heads) * kD;
-        // Chunk c = t + 96 i is the 16-byte piece c / 64 of row c % 64 of an operand tile (eight consecutive rows
-        // per quarter-warp: conflict-free in the raw tile and in the operand tile).  A thread copies, and later
-        // converts, only its own chunks, so no barrier stands between its copy and its conversion.  All offsets
-        // are fixed per thread; the global pointers advance by one tile per step.
+        // Chunk c = t + kConvThreads i is the 16-byte piece c / 64 of row c % 64 of an operand tile (eight
+        // consecutive rows per quarter-warp: conflict-free in the raw tile and in the operand tile).  A thread
+        // copies, and later converts, only its own chunks, so no barrier stands between its copy and its
+        // conversion.  All offsets are fixed per thread; the global pointers advance by one tile per step.
         uint32_t raw_off[kPerConv], dst_off[kPerConv], gk_off[kPerConv], gv_off[kPerConv];
         int k_key[kPerConv], v_key[kPerConv];
 #pragma unroll
         for (int i = 0; i < kPerConv; ++i) {
-            const int c = t + kConvThreads * i;
+            const int c = t + G::kConvThreads * i;
             const int r = c & (kKeys - 1), ch = (c >> 6) & 7;
             raw_off[i] = swz128(r, ch);
             dst_off[i] = (ch >> 2) * (kKeys * 128) + swz128(r, 2 * (ch & 3));       // the second half sits at ^ 16
@@ -378,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
             gk_off[i] = static_cast<uint32_t>(k_key[i]) * row_stride + ch * 16;
             gv_off[i] = static_cast<uint32_t>(v_key[i]) * row_stride + ch * 16;
         }
-        const bool has_last = t + kConvThreads * (kPerConv - 1) < kChunks;      // the sixth chunk exists in the first warp only
+        const bool has_last = t + G::kConvThreads * (kPerConv - 1) < kChunks;      // the last chunk may exist in the first warps only
         const size_t tile_bytes = static_cast<size_t>(kKeys) * row_stride;
         const uint8_t* gk = p.k + static_cast<size_t>(kvh) * kD;
         const uint8_t* gv = p.v + static_cast<size_t>(kvh) * kD;
@@ -392,13 +423,13 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
             for (int i = 0; i < kPerConv; ++i) {
                 if (i + 1 < kPerConv || has_last) {
                     const bool live = k_key[i] < room;
-                    cp16_zfill(base + kSRawK + raw_off[i], live ? gk + gk_off[i] : p.k, live);
+                    cp16_zfill(base + G::kSRawK + raw_off[i], live ? gk + gk_off[i] : p.k, live);
                 }
             }
             if (t < kKeys) {                                  // the scales stay in key order
                 const bool live = t < room;
-                cp4_zfill(base + kSRawS + t * 4, live ? gks : p.k_scale, live);
-                cp4_zfill(base + kSRawS + kKeys * 4 + t * 4, live ? gvs : p.v_scale, live);
+                cp4_zfill(base + G::kSRawS + t * 4, live ? gks : p.k_scale, live);
+                cp4_zfill(base + G::kSRawS + kKeys * 4 + t * 4, live ? gvs : p.v_scale, live);
             }
             cp_async_commit();
             gk += tile_bytes;
@@ -412,7 +443,7 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
             for (int i = 0; i < kPerConv; ++i) {
                 if (i + 1 < kPerConv || has_last) {
                     const bool live = v_key[i] < room;
-                    cp16_zfill(base + kSRawV + raw_off[i], live ? gv + gv_off[i] : p.v, live);
+                    cp16_zfill(base + G::kSRawV + raw_off[i], live ? gv + gv_off[i] : p.v, live);
                 }
             }
             cp_async_commit();
@@ -437,6 +468,14 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
                 }
             }
         };
+        // a tile buffer is free once every row block's product that read it has completed
+        auto wait_blocks = [&](int which, int buf, uint32_t parity, int where) {
+            bool all = true;
+#pragma unroll
+            for (int g = 0; g < kBlocks; ++g)
+                all = all && wait_phase(&bars[g * G::kBarsPerBlock + which + buf], parity, gave_up, where, p.error_word);
+            return all;
+        };
         issue_k();
         issue_v();
         bool ok = true;
@@ -445,31 +484,31 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
             const uint32_t freed = ((j - 2) >> 1) & 1;       // phase in which tile j - 2 released buffer `buf`
             // K of tile j, once S_{j-2} is complete
             if (j >= 2) {
-                ok = wait_phase(&bars[kBarQK0 + buf], freed, gave_up, __LINE__, p.error_word);
+                ok = wait_blocks(kBarQK, buf, freed, __LINE__);
                 if (!ok) break;
             }
             cp_async_wait<1>();                                          // K rows and scales of tile j
-            convert_rows(kSRawK, kSK + buf * kTileBytes);
+            convert_rows(G::kSRawK, G::kSK + buf * kTileBytes);
             if (t < kKeys) {      // K scale x softmax scale x log2(e), log2 of the V scale, its inverse
-                const float* const sc = reinterpret_cast<const float*>(sm + kSRawS);
-                float* const cst = reinterpret_cast<float*>(sm + kSCst) + (j & (kCstRing - 1)) * 3 * kKeys;
+                const float* const sc = reinterpret_cast<const float*>(sm + G::kSRawS);
+                float* const cst = reinterpret_cast<float*>(sm + G::kSCst) + (j & (kCstRing - 1)) * 3 * kKeys;
                 const float lg = fmaxf(lg2f(sc[kKeys + t]), kLgFloor);
                 cst[t] = sc[t] * p.scale_log2e;
                 cst[kKeys + t] = lg;
                 cst[2 * kKeys + t] = ex2f(-lg);
             }
             fence_async_smem();
-            pipe::mbar_arrive(&bars[kBarKReady0 + buf]);
+            pipe::mbar_arrive(&bars[G::kBarKReady + buf]);
             issue_k();                                                   // tile j + 1 (all zeros past the last one)
             // V of tile j, once O += W_{j-2} V_{j-2} is complete
             if (j >= 2) {
-                ok = wait_phase(&bars[kBarPV0 + buf], freed, gave_up, __LINE__, p.error_word);
+                ok = wait_blocks(kBarPV, buf, freed, __LINE__);
                 if (!ok) break;
             }
             cp_async_wait<1>();                                          // V rows of tile j
-            convert_rows(kSRawV, kSV + buf * kTileBytes);
+            convert_rows(G::kSRawV, G::kSV + buf * kTileBytes);
             fence_async_smem();
-            pipe::mbar_arrive(&bars[kBarVReady0 + buf]);
+            pipe::mbar_arrive(&bars[G::kBarVReady + buf]);
             issue_v();
         }
         cp_async_wait<0>();
@@ -479,16 +518,27 @@ __global__ void __launch_bounds__(kThreads, 2) flash_prefill_ws_kernel(const Arg
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(G::kTmem) : "memory");
     }
 }
 
 }  // namespace ws
 
-// Launcher of the role-split form; `a` is filled in by launch_flash_prefill_tc.
-int launch_flash_prefill_ws(const tc::Args& a, dim3 grid, cudaStream_t stream, const char* fn) {
-    (void)host::setup<&ws::flash_prefill_ws_kernel, ws::kThreads, ws::kSmemBytes>();
-    host::launch<ws::flash_prefill_ws_kernel>(grid, dim3(ws::kThreads), static_cast<size_t>(ws::kSmemBytes), stream, a);
+// Launcher of the role-split forms; `a` is filled in by launch_flash_prefill_tc (tokens_per_cta per row block).
+// Two row blocks per CTA when that still gives every SM two CTAs' worth of work, else one.
+int launch_flash_prefill_ws(const tc::Args& a, int blocks, cudaStream_t stream, const char* fn) {
+    const unsigned grid_y = static_cast<unsigned>(a.num_kv_heads * a.head_chunks);
+    if (blocks == 2) {
+        using G = ws::Geo<2>;
+        const dim3 grid(static_cast<unsigned>((a.n_new + 2 * a.tokens_per_cta - 1) / (2 * a.tokens_per_cta)), grid_y);
+        (void)host::setup<&ws::flash_prefill_ws_kernel<2>, G::kThreads, G::kSmemBytes>();
+        host::launch<ws::flash_prefill_ws_kernel<2>>(grid, dim3(G::kThreads), static_cast<size_t>(G::kSmemBytes), stream, a);
+    } else {
+        using G = ws::Geo<1>;
+        const dim3 grid(static_cast<unsigned>((a.n_new + a.tokens_per_cta - 1) / a.tokens_per_cta), grid_y);
+        (void)host::setup<&ws::flash_prefill_ws_kernel<1>, G::kThreads, G::kSmemBytes>();
+        host::launch<ws::flash_prefill_ws_kernel<1>>(grid, dim3(G::kThreads), static_cast<size_t>(G::kSmemBytes), stream, a);
+    }
     return host::check_launch(fn);
 }
 

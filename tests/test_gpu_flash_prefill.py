@@ -98,7 +98,7 @@ def test_flash_prefill_matches_exact_attention_and_reference(orc, ref, n_new, ca
     try:
         # 16 or 32 query rows per warp (mma.sync); 128 rows per CTA in tensor memory (tcgen05) with 1, 2 or 4
         # threads sharing a row, and (3, the default) the accumulator-fragment form
-        for tiles, parts in ((1, 0), (2, 0), (3, 1), (3, 2), (3, 3), (3, 4), (3, 5)):
+        for tiles, parts in ((1, 0), (2, 0), (3, 1), (3, 2), (3, 3), (3, 4), (3, 5), (3, 6)):
             K.tune("prefill_tiles", tiles)
             K.tune("prefill_parts", parts)
             key = tiles if tiles < 3 else 10 * tiles + parts
@@ -119,6 +119,7 @@ def test_flash_prefill_matches_exact_attention_and_reference(orc, ref, n_new, ca
         check(outs[30 + parts], exact_bits, exact, f"this library, tensor-memory form, {parts} thread(s) per row")
     check(outs[33], exact_bits, exact, "this library, tensor-memory form, accumulator-fragment reads")
     check(outs[35], exact_bits, exact, "this library, tensor-memory form, warps split by role")
+    check(outs[36], exact_bits, exact, "this library, tensor-memory form, warps split by role, two row blocks per CTA")
     check(out_naive, exact_bits, exact, "reference naive kernel", significance=64)
     a, b = out_naive.float().flatten(), out.float().flatten()
     if flavour != "spread":
