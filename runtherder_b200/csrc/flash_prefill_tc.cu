@@ -538,14 +538,20 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     const dim3 grid(static_cast<unsigned>((n_new + a.tokens_per_cta - 1) / a.tokens_per_cta),
                     static_cast<unsigned>(num_kv_heads * a.head_chunks));
     RH_REQUIRE(grid.y <= 65535u, RH_ERR_UNSUPPORTED_DIM, "%s: too many kv heads", fn);
-    // "prefill_parts": 0 or 3 the fragment form; 1|2|4 threads per score row (one lane = one row);
-    // +20 pads the shared-memory request so that one CTA fits per SM (a measuring aid)
+    // +20 pads the shared-memory request of this file's forms so that one CTA fits per SM (a measuring aid)
     const int knob = host::tuning(host::kPrefillParts);
     const int parts = knob >= 20 ? knob - 20 : knob;
     const size_t smem = knob >= 20 ? 120u * 1024u : static_cast<size_t>(tc::kSmemBytes);
     constexpr size_t kOptIn = 120u * 1024u;   // the padded request is the largest one
-    if (parts == 5 || parts == 6) return launch_flash_prefill_ws(a, parts - 4, stream, fn);
-    if (parts <= 0 || parts == 3) {
+    // Default: the role-split form (flash_prefill_ws.cu), with two row blocks per CTA once the one-block grid
+    // would put more than one CTA on an SM anyway.  "prefill_parts" 5 | 6 force one | two blocks; 3 selects the
+    // fragment form of this file and 1 | 2 | 4 its forms with that many threads per score row.
+    if (parts <= 0 || parts == 5 || parts == 6) {
+        const long long ctas_one = static_cast<long long>(grid.x) * grid.y;
+        const int blocks = parts == 5 ? 1 : (parts == 6 ? 2 : (ctas_one > host::num_sms() ? 2 : 1));
+        return launch_flash_prefill_ws(a, blocks, stream, fn);
+    }
+    if (parts == 3) {
         (void)host::setup<&tc::flash_prefill_tc_kernel<2, true>, 256, kOptIn>();
         host::launch<tc::flash_prefill_tc_kernel<2, true>>(grid, dim3(256), smem, stream, a);
     } else if (parts == 1) {
