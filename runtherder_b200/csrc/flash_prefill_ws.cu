@@ -84,11 +84,24 @@ __device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volat
             : "r"(addr), "r"(parity)
             : "memory");
         if (ok != 0) return true;
-        if (*gave_up != 0) return false;
+        if ((i & 15) == 15 && *gave_up != 0) return false;     // looked at now and then: a poll is a shared-memory access
     }
     *gave_up = 1;
     if (error_word != nullptr) atomicCAS(error_word, 0, (where << 8) | 1);
     return false;
+}
+
+// Barrier among the `count` threads that use named barrier `id`, returning the OR of their predicates.
+__device__ __forceinline__ bool group_or(int id, int count, bool pred) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out)
+        : "r"(id), "r"(count), "r"(static_cast<uint32_t>(pred))
+        : "memory");
+    return out != 0;
 }
 
 // the key whose K row becomes row r of the K operand tile (S column 16a + 8h + 2c + e holds key 16a + 4c + 2h + e)
@@ -298,11 +311,11 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             if (j > 0 && __any_sync(0xffffffffu, corr_a != 1.0f || corr_b != 1.0f)) {
                 const float2 ca = splat2(corr_a), cb2 = splat2(corr_b);
 #pragma unroll 1
-                for (int cb = 0; cb < kD; cb += 32) {
-                    uint32_t ov[16];
-                    tmem_ld_frag_x4(ov, tmem_o + my_lanes16 + cb);
+                for (int cb = 0; cb < kD; cb += 64) {        // two round trips through tensor memory
+                    uint32_t ov[32];
+                    tmem_ld_frag_x8(ov, tmem_o + my_lanes16 + cb);
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
+                    for (int g = 0; g < 8; ++g) {
                         const float2 oa = mul2_rn(make_float2(__uint_as_float(ov[4 * g]), __uint_as_float(ov[4 * g + 1])), ca);
                         const float2 ob = mul2_rn(make_float2(__uint_as_float(ov[4 * g + 2]), __uint_as_float(ov[4 * g + 3])), cb2);
                         ov[4 * g] = __float_as_uint(oa.x);
@@ -310,7 +323,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
                         ov[4 * g + 2] = __float_as_uint(ob.x);
                         ov[4 * g + 3] = __float_as_uint(ob.y);
                     }
-                    tmem_st_frag_x4(tmem_o + my_lanes16 + cb, ov);
+                    tmem_st_frag_x8(tmem_o + my_lanes16 + cb, ov);
                 }
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -392,22 +405,25 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
         constexpr int kPerConv = G::kPerConv;
         const int t = tid - 32 * G::kConvWarp0;
         const uint32_t row_stride = static_cast<uint32_t>(p.num_kv_heads) * kD;
-        // Chunk c = t + kConvThreads i is the 16-byte piece c / 64 of row c % 64 of an operand tile (eight
-        // consecutive rows per quarter-warp: conflict-free in the raw tile and in the operand tile).  A thread
-        // copies, and later converts, only its own chunks, so no barrier stands between its copy and its
-        // conversion.  All offsets are fixed per thread; the global pointers advance by one tile per step.
-        uint32_t raw_off[kPerConv], dst_off[kPerConv], gk_off[kPerConv], gv_off[kPerConv];
+        // A raw tile holds the rows in operand order, [row][128 bytes, swizzled].  It is copied with eight
+        // consecutive threads on the eight 16-byte pieces of one row (whole 128-byte lines of the cache) and
+        // converted with eight consecutive threads on the same piece of eight consecutive rows (conflict-free
+        // in the raw tile and in the operand tile); the conversion group meets at a named barrier in between.
+        // All offsets are fixed per thread; the global pointers advance by one tile per step.
+        uint32_t copy_off[kPerConv], raw_off[kPerConv], dst_off[kPerConv], gk_off[kPerConv], gv_off[kPerConv];
         int k_key[kPerConv], v_key[kPerConv];
 #pragma unroll
         for (int i = 0; i < kPerConv; ++i) {
             const int c = t + G::kConvThreads * i;
-            const int r = c & (kKeys - 1), ch = (c >> 6) & 7;
+            const int cr = (c >> 3) & (kKeys - 1), cch = c & 7;             // the copy's row and piece
+            copy_off[i] = swz128(cr, cch);
+            k_key[i] = key_of_k_row(cr);
+            v_key[i] = cr;
+            gk_off[i] = static_cast<uint32_t>(k_key[i]) * row_stride + cch * 16;
+            gv_off[i] = static_cast<uint32_t>(v_key[i]) * row_stride + cch * 16;
+            const int r = c & (kKeys - 1), ch = (c >> 6) & 7;               // the conversion's row and piece
             raw_off[i] = swz128(r, ch);
             dst_off[i] = (ch >> 2) * (kKeys * 128) + swz128(r, 2 * (ch & 3));       // the second half sits at ^ 16
-            k_key[i] = key_of_k_row(r);
-            v_key[i] = r;
-            gk_off[i] = static_cast<uint32_t>(k_key[i]) * row_stride + ch * 16;
-            gv_off[i] = static_cast<uint32_t>(v_key[i]) * row_stride + ch * 16;
         }
         const bool has_last = t + G::kConvThreads * (kPerConv - 1) < kChunks;      // the last chunk may exist in the first warps only
         const size_t tile_bytes = static_cast<size_t>(kKeys) * row_stride;
@@ -423,7 +439,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             for (int i = 0; i < kPerConv; ++i) {
                 if (i + 1 < kPerConv || has_last) {
                     const bool live = k_key[i] < room;
-                    cp16_zfill(base + G::kSRawK + raw_off[i], live ? gk + gk_off[i] : p.k, live);
+                    cp16_zfill(base + G::kSRawK + copy_off[i], live ? gk + gk_off[i] : p.k, live);
                 }
             }
             if (t < kKeys) {                                  // the scales stay in key order
@@ -443,7 +459,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             for (int i = 0; i < kPerConv; ++i) {
                 if (i + 1 < kPerConv || has_last) {
                     const bool live = v_key[i] < room;
-                    cp16_zfill(base + G::kSRawV + raw_off[i], live ? gv + gv_off[i] : p.v, live);
+                    cp16_zfill(base + G::kSRawV + copy_off[i], live ? gv + gv_off[i] : p.v, live);
                 }
             }
             cp_async_commit();
@@ -483,11 +499,9 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             const int buf = j & 1;
             const uint32_t freed = ((j - 2) >> 1) & 1;       // phase in which tile j - 2 released buffer `buf`
             // K of tile j, once S_{j-2} is complete
-            if (j >= 2) {
-                ok = wait_blocks(kBarQK, buf, freed, __LINE__);
-                if (!ok) break;
-            }
-            cp_async_wait<1>();                                          // K rows and scales of tile j
+            if (j >= 2) ok = wait_blocks(kBarQK, buf, freed, __LINE__);
+            cp_async_wait<1>();                                          // this thread's K pieces and scales of tile j
+            if (group_or(1, G::kConvThreads, !ok)) { ok = false; break; }    // everyone's pieces have landed
             convert_rows(G::kSRawK, G::kSK + buf * kTileBytes);
             if (t < kKeys) {      // K scale x softmax scale x log2(e), log2 of the V scale, its inverse
                 const float* const sc = reinterpret_cast<const float*>(sm + G::kSRawS);
@@ -499,16 +513,16 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             }
             fence_async_smem();
             pipe::mbar_arrive(&bars[G::kBarKReady + buf]);
+            named_sync(2, G::kConvThreads);                  // the raw K tile has been read by all
             issue_k();                                                   // tile j + 1 (all zeros past the last one)
             // V of tile j, once O += W_{j-2} V_{j-2} is complete
-            if (j >= 2) {
-                ok = wait_blocks(kBarPV, buf, freed, __LINE__);
-                if (!ok) break;
-            }
-            cp_async_wait<1>();                                          // V rows of tile j
+            if (j >= 2) ok = wait_blocks(kBarPV, buf, freed, __LINE__);
+            cp_async_wait<1>();                                          // this thread's V pieces of tile j
+            if (group_or(1, G::kConvThreads, !ok)) { ok = false; break; }
             convert_rows(G::kSRawV, G::kSV + buf * kTileBytes);
             fence_async_smem();
             pipe::mbar_arrive(&bars[G::kBarVReady + buf]);
+            named_sync(2, G::kConvThreads);
             issue_v();
         }
         cp_async_wait<0>();
