@@ -844,7 +844,10 @@ def run_prefill_attention(args, cfg, dev, emit=True):
     ms, clocks = timed(ours, K)
     peak, peak_kind = measured_tensor_peak()
     achieved = flops / (ms * 1e-3) / 1e12
-    tc_form = not any(t.startswith("prefill_tiles=1") or t.startswith("prefill_tiles=2") for t in (args.tune or []))
+    tunes = args.tune or []
+    tc_form = not any(t.startswith("prefill_tiles=1") or t.startswith("prefill_tiles=2") for t in tunes)
+    parts = [t.split("=", 1)[1] for t in tunes if t.startswith("prefill_parts=")]
+    tc_kernel = "flash_prefill_tc_kernel" if parts and parts[-1] in ("1", "2", "3", "4") else "flash_prefill_ws_kernel"
     line = {"metric": "flash-prefill TFLOP/s", "value": round(achieved, 1), "unit": "TFLOP/s", "n_gpus": 1, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "replicas only",
             "vs_baseline": None, "dtype": "f32",
@@ -854,10 +857,10 @@ def run_prefill_attention(args, cfg, dev, emit=True):
                        "kv_heads": Hkv, "head_dim": D, "cache_len": 0, "sets": n_sets, "flops_per_call": flops,
                        "l2": "q + out of one call are 2 x %.0f MB; %d sets used in turn" % (T * Hq * D * 2 / 1e6, n_sets)},
             "gpu_launches": K, "launches_per_step": 1, "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "flash_prefill_tc_kernel" if tc_form else "flash_prefill_kernel", "achieved": round(achieved, 1), "peak": peak,
+            "roofline": {"bound": "tensor", "kernel": tc_kernel if tc_form else "flash_prefill_kernel", "achieved": round(achieved, 1), "peak": peak,
                          "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}", "traffic": None,
                          "note": ("tcgen05.mma kernel (S and O in tensor memory); the E4M3->f16 conversion, the per-key scales "
-                                  "and the softmax run on the CUDA cores beside it") if tc_form else
+                                  "and the softmax run on the CUDA cores beside it, in warps of their own in the default form") if tc_form else
                                  ("mma.sync kernel: its own ceiling is the legacy tensor path (one m16n8k16 per 8 cycles "
                                   "per SM sub-partition = 576 TFLOP/s at 1.9 GHz), not the tcgen05 figure the peak was measured with")}}
     if not args.no_refcuda:

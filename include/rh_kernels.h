@@ -279,8 +279,10 @@ int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host);
  * without the programmatic-dependent-launch attribute; by default each kernel may be scheduled
  * while the previous kernel of its stream drains and orders itself on the device before its first
  * memory access, so stream semantics are unchanged), "prefill_tiles" (1|2: the mma.sync forms of the prefill
- * attention kernel with one or two 16-row tiles per warp; default: the tcgen05 form with S and O in tensor
- * memory), "prefill_parts" (1|2|4 threads share a query row of the tcgen05 form; default 2); value <= 0 restores
+ * attention kernel with one or two 16-row tiles per warp; default: the tcgen05 forms with S and O in tensor
+ * memory), "prefill_parts" (which tcgen05 form: default the role-split one, with 5 | 6 forcing one | two row
+ * blocks per CTA; 1|2|4 = the single-role form with that many threads per score row, 3 = the single-role form
+ * with the scores read in accumulator-fragment shape); value <= 0 restores
  * the default.  Returns RH_ERR_INVALID_ARG for an unknown key. */
 int rh_tune(const char* key, int value);
 
