@@ -70,8 +70,12 @@ struct Geo {
 enum BlockBar { kBarQK = 0, kBarPV = 2, kBarSRead = 4, kBarWReady = 5 };
 
 constexpr int kTries = 1 << 20;
+constexpr int kLazyNs = 100;      // pause between polls of the product and conversion warps
 
-// Bounded wait that also ends when another thread of the CTA has given up.
+// Bounded wait that also ends when another thread of the CTA has given up.  kBackoffNs > 0 sleeps between
+// tries: for the roles whose reaction time is not on the critical path (a poll is a shared-memory access and
+// an issue slot taken from the softmax warps).
+template <int kBackoffNs = 0>
 __device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volatile int* gave_up, int where, int* error_word) {
     const uint32_t addr = pipe::smem_u32(bar);
     for (int i = 0; i < kTries; ++i) {      // a try blocks for a while in hardware before it reports failure
@@ -85,6 +89,7 @@ __device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volat
             : "memory");
         if (ok != 0) return true;
         if ((i & 15) == 15 && *gave_up != 0) return false;     // looked at now and then: a poll is a shared-memory access
+        if constexpr (kBackoffNs > 0) __nanosleep(kBackoffNs);
     }
     *gave_up = 1;
     if (error_word != nullptr) atomicCAS(error_word, 0, (where << 8) | 1);
@@ -378,17 +383,17 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             }
             __syncwarp();
         };
-        bool ok = wait_phase(&bars[G::kBarKReady], 0, gave_up, __LINE__, p.error_word);
+        bool ok = wait_phase<kLazyNs>(&bars[G::kBarKReady], 0, gave_up, __LINE__, p.error_word);
         if (ok) issue_qk(0);
         for (int j = 0; j < n_tiles && ok; ++j) {
             if (j + 1 < n_tiles) {
-                ok = wait_phase(&bb[kBarSRead], j & 1, gave_up, __LINE__, p.error_word) &&
-                     wait_phase(&bars[G::kBarKReady + ((j + 1) & 1)], ((j + 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
+                ok = wait_phase<kLazyNs>(&bb[kBarSRead], j & 1, gave_up, __LINE__, p.error_word) &&
+                     wait_phase<kLazyNs>(&bars[G::kBarKReady + ((j + 1) & 1)], ((j + 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
                 if (!ok) break;
                 issue_qk(j + 1);
             }
-            ok = wait_phase(&bb[kBarWReady], j & 1, gave_up, __LINE__, p.error_word) &&
-                 wait_phase(&bars[G::kBarVReady + (j & 1)], (j >> 1) & 1, gave_up, __LINE__, p.error_word);
+            ok = wait_phase<kLazyNs>(&bb[kBarWReady], j & 1, gave_up, __LINE__, p.error_word) &&
+                 wait_phase<kLazyNs>(&bars[G::kBarVReady + (j & 1)], (j >> 1) & 1, gave_up, __LINE__, p.error_word);
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
@@ -489,7 +494,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             bool all = true;
 #pragma unroll
             for (int g = 0; g < kBlocks; ++g)
-                all = all && wait_phase(&bars[g * G::kBarsPerBlock + which + buf], parity, gave_up, where, p.error_word);
+                all = all && wait_phase<kLazyNs>(&bars[g * G::kBarsPerBlock + which + buf], parity, gave_up, where, p.error_word);
             return all;
         };
         issue_k();
