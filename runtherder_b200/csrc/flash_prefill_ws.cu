@@ -50,9 +50,14 @@ struct Geo {
     static constexpr int kThreads = 32 * (kConvWarp0 + kConvWarps);  // 384 or 704
     static constexpr int kPerConv = (kChunks + kConvThreads - 1) / kConvThreads;
     static constexpr int kTmem = kTmemCols * kBlocks;
+    // Two row blocks: two W buffers in tensor memory (the softmax warps then need not wait for the previous
+    // O += W V before they store the next weights) and all of Q in shared memory.  One row block: one W buffer,
+    // and the upper half of Q in the last 32 tensor-memory columns (two such CTAs share an SM's shared memory).
+    static constexpr bool kTwoW = kBlocks == 2;
+    static constexpr int kQBytes = kTwoW ? 2 * kRows * 128 : kRows * 128;
     // shared-memory map, relative to a 1024-byte aligned base
-    static constexpr int kSQ = 0;                                    // per block [128 rows][128 B]: dims 0..63 of Q
-    static constexpr int kSK = kSQ + kBlocks * kRows * 128;          // two K tiles                               32 KB
+    static constexpr int kSQ = 0;                                    // per block [1 or 2 dim blocks][128 rows][128 B] of Q
+    static constexpr int kSK = kSQ + kBlocks * kQBytes;              // two K tiles                               32 KB
     static constexpr int kSV = kSK + 2 * kTileBytes;                 // two V tiles                               32 KB
     static constexpr int kSRawK = kSV + 2 * kTileBytes;              // raw K rows                                 8 KB
     static constexpr int kSRawV = kSRawK + kKeys * kD;               // raw V rows                                 8 KB
@@ -164,13 +169,13 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
     const int n_tiles = min((total_keys + kKeys - 1) / kKeys, (clen + last_tok) / kKeys + 1);
 
     // this warp's row block (softmax and product warps) and that block's tensor memory: S 64 columns, O 128,
-    // W (f16 pairs) 32, the upper half of Q (f16 pairs) 32
+    // W (f16 pairs) 32, then the upper half of Q (f16 pairs) or a second W buffer, 32
     const int blk = warp < G::kSoftmaxWarps ? warp >> 3 : (warp < G::kConvWarp0 ? warp - G::kIssuerWarp0 : 0);
     const int wb = warp & 7;                                 // warp within the block's softmax warps
     const int tok0 = cta_tok0 + blk * p.tokens_per_cta;
     uint64_t* const bb = bars + blk * G::kBarsPerBlock;
     const uint32_t tmem_s = tmem + blk * kTmemCols, tmem_o = tmem_s + kKeys, tmem_w = tmem_o + kD, tmem_q = tmem_w + kKeys / 2;
-    const int q_off = G::kSQ + blk * (kRows * 128);
+    const int q_off = G::kSQ + blk * G::kQBytes;
 
     // ---- Q (softmax warps): row of the block, bf16 -> f16; dims 0..63 to shared memory ([row][128 bytes, swizzled])
     //      by the block's first four warps, dims 64..127 to tensor memory (row = lane, two f16 per column) by the
@@ -193,9 +198,10 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             h.w = pack_f16x2(bf_lo(w.w), bf_hi(w.w));
             return h;
         };
-        if (part == 0) {
+        if (G::kTwoW || part == 0) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(sm + q_off + swz128(row, c)) = load_chunk(c);
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(sm + q_off + part * (kRows * 128) + swz128(row, c)) = load_chunk(8 * part + c);
         } else {
             const uint32_t my_lane = static_cast<uint32_t>(32 * (wb & 3)) << 16;
 #pragma unroll
@@ -306,14 +312,28 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             }
             l_a = fmaf(l_a, corr_a, sum_a.x + sum_a.y);
             l_b = fmaf(l_b, corr_b, sum_b.x + sum_b.y);
-            // W and O are free once O += W_{j-1} V_{j-1} has completed
-            if (j > 0) {
+            const bool moved = j > 0 && __any_sync(0xffffffffu, corr_a != 1.0f || corr_b != 1.0f);
+            if constexpr (G::kTwoW) {
+                // W buffer j % 2 is free once O += W_{j-2} V_{j-2} has completed (long ago, as a rule); O may
+                // only be touched once O += W_{j-1} V_{j-1} has, which is waited for only when a maximum moved.
+                // Skipping a wait is safe for the parity test: no product of a later tile can complete before
+                // this warp has signalled "W ready" for it.
+                if (j > 1) {
+                    ok = wait_phase(&bb[kBarPV + (j & 1)], ((j - 2) >> 1) & 1, gave_up, __LINE__, p.error_word);
+                    if (!ok) break;
+                }
+                if (moved) {
+                    ok = wait_phase(&bb[kBarPV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
+                    if (!ok) break;
+                }
+                tc_fence_after();
+            } else if (j > 0) {                  // W and O are free once O += W_{j-1} V_{j-1} has completed
                 ok = wait_phase(&bb[kBarPV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
                 if (!ok) break;
                 tc_fence_after();
             }
-            tmem_st_frag_x4(tmem_w + my_lanes16, wv);
-            if (j > 0 && __any_sync(0xffffffffu, corr_a != 1.0f || corr_b != 1.0f)) {
+            tmem_st_frag_x4(tmem_w + (G::kTwoW ? (j & 1) * (kKeys / 2) : 0) + my_lanes16, wv);
+            if (moved) {
                 const float2 ca = splat2(corr_a), cb2 = splat2(corr_b);
 #pragma unroll 1
                 for (int cb = 0; cb < kD; cb += 64) {        // two round trips through tensor memory
@@ -377,8 +397,12 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
                 for (int s = 0; s < 4; ++s)       // dims 0..63: both operands from shared memory
                     umma_f16(tmem_s, smem_desc(base + q_off + s * 32, 16), smem_desc(k_base + s * 32, 16), kIdescQK, s > 0);
 #pragma unroll
-                for (int s = 0; s < 4; ++s)       // dims 64..127: Q from tensor memory
-                    umma_f16_ts(tmem_s, tmem_q + s * 8, smem_desc(k_base + kKeys * 128 + s * 32, 16), kIdescQK, true);
+                for (int s = 0; s < 4; ++s) {     // dims 64..127: Q from shared memory or from tensor memory
+                    if constexpr (G::kTwoW)
+                        umma_f16(tmem_s, smem_desc(base + q_off + kRows * 128 + s * 32, 16), smem_desc(k_base + kKeys * 128 + s * 32, 16), kIdescQK, true);
+                    else
+                        umma_f16_ts(tmem_s, tmem_q + s * 8, smem_desc(k_base + kKeys * 128 + s * 32, 16), kIdescQK, true);
+                }
                 umma_commit(&bb[kBarQK + (tile_j & 1)]);
             }
             __syncwarp();
@@ -400,7 +424,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
                 const uint32_t v_base = base + G::kSV + (j & 1) * kTileBytes;
 #pragma unroll
                 for (int s = 0; s < kKeys / 16; ++s)
-                    umma_f16_ts(tmem_o, tmem_w + s * 8, smem_desc(v_base + s * 2048, kKeys * 128), kIdescPV, j > 0 || s > 0);
+                    umma_f16_ts(tmem_o, tmem_w + (G::kTwoW ? (j & 1) * (kKeys / 2) : 0) + s * 8, smem_desc(v_base + s * 2048, kKeys * 128), kIdescPV, j > 0 || s > 0);
                 umma_commit(&bb[kBarPV + (j & 1)]);
             }
             __syncwarp();
