@@ -11,6 +11,7 @@
 //
 //   warps 0-7   softmax      wait S_j  -> load scores, release S -> scale, mask, maximum, weights
 //                            -> wait O += W_{j-1} V_{j-1} -> store W_j, rescale O -> W ready
+//                            (with two W buffers that wait happens only when a row maximum moved)
 //   warp  8     products     S_0;  per tile: [S_j read, K_{j+1} ready] S_{j+1} = Q K_{j+1}^T
 //                                            [W_j ready, V_j ready]     O += W_j V_j
 //   warps 9-11  conversion   raw E4M3 rows (cp.async, one tile ahead) -> f16 operand tiles (two buffers each) and
