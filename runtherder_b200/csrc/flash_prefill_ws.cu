@@ -1,8 +1,9 @@
 // Causal prefill attention over the FP8-E4M3 KV cache, tcgen05 form with the work of a CTA split by role.
 // Same contract as flash_prefill.cu (runtherder::kernels::flash_prefill_bf16,
 // include/runtherder/kernels/flash_prefill.cuh:27-40); same tile geometry, operand layouts and arithmetic as
-// the fragment form in flash_prefill_tc.cu (128 query rows of one kv head per CTA, key tiles of 64, scores
-// read in the accumulator-fragment shape, weights and the upper half of Q in tensor memory).
+// the fragment form in flash_prefill_tc.cu (row blocks of 128 query rows of one kv head, key tiles of 64, scores
+// read in the accumulator-fragment shape, weights in tensor memory), except that all of Q sits in shared memory
+// and the tensor-memory columns that frees hold a second buffer for the weights.
 //
 // What differs is who does what.  In flash_prefill_tc.cu every thread walks through every phase of a tile
 // and the CTA meets at two barriers per tile, so the phases add up: switching any one of them off
@@ -10,8 +11,8 @@
 // and hand tiles to one another through mbarriers, so that the phases of neighbouring tiles overlap:
 //
 //   warps 0-7   softmax      wait S_j  -> load scores, release S -> scale, mask, maximum, weights
-//                            -> wait O += W_{j-1} V_{j-1} -> store W_j, rescale O -> W ready
-//                            (with two W buffers that wait happens only when a row maximum moved)
+//                            -> store W_j (two buffers) -> only if a row maximum moved: wait for
+//                            O += W_{j-1} V_{j-1}, rescale O -> W ready
 //   warp  8     products     S_0;  per tile: [S_j read, K_{j+1} ready] S_{j+1} = Q K_{j+1}^T
 //                                            [W_j ready, V_j ready]     O += W_j V_j
 //   warps 9-11  conversion   raw E4M3 rows (cp.async, one tile ahead) -> f16 operand tiles (two buffers each) and
@@ -39,8 +40,8 @@ constexpr int kCstRing = 4;        // constants of tile j are read while those o
 constexpr int kTileBytes = 2 * kKeys * 128;              // an f16 operand tile: [2 dim blocks][64 keys][128 B]   16 KB
 
 // A CTA carries kBlocks row blocks of 128 query rows (consecutive token ranges of the same kv head and head
-// chunk) that share the converted K and V tiles: one block with two CTAs per SM, or two blocks in one CTA per
-// SM, where a tile is converted once for twice the rows.
+// chunk) that share the converted K and V tiles; one CTA per SM either way (shared memory).  Two blocks: a tile
+// is converted once for twice the rows; one block: for prompts whose grid does not exceed the SM count anyway.
 template <int kBlocks>
 struct Geo {
     static constexpr int kSoftmaxWarps = 8 * kBlocks;
@@ -51,13 +52,9 @@ struct Geo {
     static constexpr int kThreads = 32 * (kConvWarp0 + kConvWarps);  // 384 or 704
     static constexpr int kPerConv = (kChunks + kConvThreads - 1) / kConvThreads;
     static constexpr int kTmem = kTmemCols * kBlocks;
-    // Two row blocks: two W buffers in tensor memory (the softmax warps then need not wait for the previous
-    // O += W V before they store the next weights) and all of Q in shared memory.  One row block: one W buffer,
-    // and the upper half of Q in the last 32 tensor-memory columns (two such CTAs share an SM's shared memory).
-    static constexpr bool kTwoW = kBlocks == 2;
-    static constexpr int kQBytes = kTwoW ? 2 * kRows * 128 : kRows * 128;
+    static constexpr int kQBytes = 2 * kRows * 128;
     // shared-memory map, relative to a 1024-byte aligned base
-    static constexpr int kSQ = 0;                                    // per block [1 or 2 dim blocks][128 rows][128 B] of Q
+    static constexpr int kSQ = 0;                                    // per block [2 dim blocks][128 rows][128 B]: Q
     static constexpr int kSK = kSQ + kBlocks * kQBytes;              // two K tiles                               32 KB
     static constexpr int kSV = kSK + 2 * kTileBytes;                 // two V tiles                               32 KB
     static constexpr int kSRawK = kSV + 2 * kTileBytes;              // raw K rows                                 8 KB
@@ -120,7 +117,7 @@ __device__ __forceinline__ int key_of_k_row(int r) { return (r & 48) | ((r & 6) 
 
 // grid (token tiles of kBlocks * tokens_per_cta tokens, num_kv_heads * head_chunks)
 template <int kBlocks>
-__global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_prefill_ws_kernel(const Args p) {
+__global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 1) flash_prefill_ws_kernel(const Args p) {
     using G = Geo<kBlocks>;
     extern __shared__ unsigned char raw_smem[];
     const uint32_t base = (pipe::smem_u32(raw_smem) + 1023u) & ~1023u;          // shared-space address, 1 KB aligned
@@ -170,17 +167,17 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
     const int n_tiles = min((total_keys + kKeys - 1) / kKeys, (clen + last_tok) / kKeys + 1);
 
     // this warp's row block (softmax and product warps) and that block's tensor memory: S 64 columns, O 128,
-    // W (f16 pairs) 32, then the upper half of Q (f16 pairs) or a second W buffer, 32
+    // two W buffers (f16 pairs) of 32.  With two W buffers the softmax warps need not wait for the previous
+    // O += W V before they store the next weights.
     const int blk = warp < G::kSoftmaxWarps ? warp >> 3 : (warp < G::kConvWarp0 ? warp - G::kIssuerWarp0 : 0);
     const int wb = warp & 7;                                 // warp within the block's softmax warps
     const int tok0 = cta_tok0 + blk * p.tokens_per_cta;
     uint64_t* const bb = bars + blk * G::kBarsPerBlock;
-    const uint32_t tmem_s = tmem + blk * kTmemCols, tmem_o = tmem_s + kKeys, tmem_w = tmem_o + kD, tmem_q = tmem_w + kKeys / 2;
+    const uint32_t tmem_s = tmem + blk * kTmemCols, tmem_o = tmem_s + kKeys, tmem_w = tmem_o + kD;
     const int q_off = G::kSQ + blk * G::kQBytes;
 
-    // ---- Q (softmax warps): row of the block, bf16 -> f16; dims 0..63 to shared memory ([row][128 bytes, swizzled])
-    //      by the block's first four warps, dims 64..127 to tensor memory (row = lane, two f16 per column) by the
-    //      other four ----
+    // ---- Q (softmax warps): row of the block, bf16 -> f16 into shared memory ([dim block][row][128 bytes, swizzled]);
+    //      dims 0..63 by the block's first four warps, dims 64..127 by the other four ----
     if (warp < G::kSoftmaxWarps) {
         const int row = 32 * (wb & 3) + lane, part = wb >> 2;
         const int head_slot = row / p.tokens_per_cta;
@@ -199,27 +196,9 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             h.w = pack_f16x2(bf_lo(w.w), bf_hi(w.w));
             return h;
         };
-        if (G::kTwoW || part == 0) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(sm + q_off + part * (kRows * 128) + swz128(row, c)) = load_chunk(8 * part + c);
-        } else {
-            const uint32_t my_lane = static_cast<uint32_t>(32 * (wb & 3)) << 16;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                uint32_t qw[16];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 h = load_chunk(8 + 4 * half + c);
-                    qw[4 * c] = h.x;
-                    qw[4 * c + 1] = h.y;
-                    qw[4 * c + 2] = h.z;
-                    qw[4 * c + 3] = h.w;
-                }
-                tmem_st_words<16>(tmem_q + my_lane + 16 * half, qw);
-            }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        }
+        for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(sm + q_off + part * (kRows * 128) + swz128(row, c)) = load_chunk(8 * part + c);
     }
     fence_async_smem();
     tc_fence_before();
@@ -314,7 +293,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
             l_a = fmaf(l_a, corr_a, sum_a.x + sum_a.y);
             l_b = fmaf(l_b, corr_b, sum_b.x + sum_b.y);
             const bool moved = j > 0 && __any_sync(0xffffffffu, corr_a != 1.0f || corr_b != 1.0f);
-            if constexpr (G::kTwoW) {
+            {
                 // W buffer j % 2 is free once O += W_{j-2} V_{j-2} has completed (long ago, as a rule); O may
                 // only be touched once O += W_{j-1} V_{j-1} has, which is waited for only when a maximum moved.
                 // Skipping a wait is safe for the parity test: no product of a later tile can complete before
@@ -328,12 +307,8 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
                     if (!ok) break;
                 }
                 tc_fence_after();
-            } else if (j > 0) {                  // W and O are free once O += W_{j-1} V_{j-1} has completed
-                ok = wait_phase(&bb[kBarPV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
-                if (!ok) break;
-                tc_fence_after();
             }
-            tmem_st_frag_x4(tmem_w + (G::kTwoW ? (j & 1) * (kKeys / 2) : 0) + my_lanes16, wv);
+            tmem_st_frag_x4(tmem_w + (j & 1) * (kKeys / 2) + my_lanes16, wv);
             if (moved) {
                 const float2 ca = splat2(corr_a), cb2 = splat2(corr_b);
 #pragma unroll 1
@@ -398,12 +373,8 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
                 for (int s = 0; s < 4; ++s)       // dims 0..63: both operands from shared memory
                     umma_f16(tmem_s, smem_desc(base + q_off + s * 32, 16), smem_desc(k_base + s * 32, 16), kIdescQK, s > 0);
 #pragma unroll
-                for (int s = 0; s < 4; ++s) {     // dims 64..127: Q from shared memory or from tensor memory
-                    if constexpr (G::kTwoW)
-                        umma_f16(tmem_s, smem_desc(base + q_off + kRows * 128 + s * 32, 16), smem_desc(k_base + kKeys * 128 + s * 32, 16), kIdescQK, true);
-                    else
-                        umma_f16_ts(tmem_s, tmem_q + s * 8, smem_desc(k_base + kKeys * 128 + s * 32, 16), kIdescQK, true);
-                }
+                for (int s = 0; s < 4; ++s)       // dims 64..127
+                    umma_f16(tmem_s, smem_desc(base + q_off + kRows * 128 + s * 32, 16), smem_desc(k_base + kKeys * 128 + s * 32, 16), kIdescQK, true);
                 umma_commit(&bb[kBarQK + (tile_j & 1)]);
             }
             __syncwarp();
@@ -425,7 +396,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
                 const uint32_t v_base = base + G::kSV + (j & 1) * kTileBytes;
 #pragma unroll
                 for (int s = 0; s < kKeys / 16; ++s)
-                    umma_f16_ts(tmem_o, tmem_w + (G::kTwoW ? (j & 1) * (kKeys / 2) : 0) + s * 8, smem_desc(v_base + s * 2048, kKeys * 128), kIdescPV, j > 0 || s > 0);
+                    umma_f16_ts(tmem_o, tmem_w + (j & 1) * (kKeys / 2) + s * 8, smem_desc(v_base + s * 2048, kKeys * 128), kIdescPV, j > 0 || s > 0);
                 umma_commit(&bb[kBarPV + (j & 1)]);
             }
             __syncwarp();
@@ -569,7 +540,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 3 - kBlocks) flash_pre
 }  // namespace ws
 
 // Launcher of the role-split forms; `a` is filled in by launch_flash_prefill_tc (tokens_per_cta per row block).
-// Two row blocks per CTA when that still gives every SM two CTAs' worth of work, else one.
+// blocks: row blocks per CTA (the caller picks two once the one-block grid exceeds the SM count).
 int launch_flash_prefill_ws(const tc::Args& a, int blocks, cudaStream_t stream, const char* fn) {
     const unsigned grid_y = static_cast<unsigned>(a.num_kv_heads * a.head_chunks);
     if (blocks == 2) {
