@@ -10,8 +10,8 @@
  *    keeps a pointer, so every such call may be recorded into a CUDA graph.  positions /
  *    at_pos / token ids are read on the device at execution time.  The exceptions are the
  *    diagnostics, each documented where it is declared: rh_selftest, rh_selftest_static,
- *    rh_device_error and rh_selfcheck_bounded_wait synchronise (the first and the last
- *    also allocate), and rh_init is host-side set-up.
+ *    rh_device_error, rh_selfcheck_bounded_wait and rh_selfcheck_role_wait synchronise (the
+ *    first and the last two also allocate), and rh_init is host-side set-up.
  *  - Row starts must be 16-byte aligned (bf16 row length a multiple of 8).
  *  - Return value: RH_OK or an rh_status error; rh_last_error_string() gives the
  *    reason for the last failure on the calling thread.  Nothing is launched
@@ -268,6 +268,15 @@ int rh_device_error(int* error_host);
  * the error word the probe recorded (non-zero; a private word — the sticky device error word is not
  * touched), the kernel returns normally and the context stays usable.  Diagnostic: allocates, synchronises. */
 int rh_selfcheck_bounded_wait(int polls, int* gave_up_host, int* error_host);
+
+/* The same for the waits between the warp roles of the prefill attention kernel
+ * (runtherder_b200/csrc/flash_prefill_ws.cu): warp 0 waits with a limit of `tries` (16..65536) on a barrier
+ * that nothing completes and must give up, raising the CTA-wide flag; warp 1, waiting with the kernel's own
+ * limit (2^20) on another such barrier, must be released by that flag.  result_host (HOST, 4 ints): [0] 1 if
+ * warp 0's wait claimed success (0 expected), [1] the flag (1 expected), [2] the error word the probe recorded
+ * (source line << 8 | 1; a private word), [3] the tries warp 1 used (far below 2^20 expected).  The kernel
+ * returns normally and the context stays usable.  Diagnostic: allocates, synchronises. */
+int rh_selfcheck_role_wait(int tries, int* result_host);
 
 /* ---- Tuning knobs (process-wide; for experiments, defaults are the tuned values) --------- */
 

@@ -52,6 +52,7 @@ SIGNATURES = {
     "rh_selftest": [_p],
     "rh_device_error": [_p],
     "rh_selfcheck_bounded_wait": [_i, _p, _p],
+    "rh_selfcheck_role_wait": [_i, _p],
     "rh_selftest_static": [_p, _i, _p],
 }
 _RESTYPES = {"rh_status_string": C.c_char_p, "rh_last_error_string": C.c_char_p,

@@ -79,9 +79,10 @@ constexpr int kLazyNs = 100;      // pause between polls of the product and conv
 // tries: for the roles whose reaction time is not on the critical path (a poll is a shared-memory access and
 // an issue slot taken from the softmax warps).
 template <int kBackoffNs = 0>
-__device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volatile int* gave_up, int where, int* error_word) {
+__device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volatile int* gave_up, int where, int* error_word,
+                                           int tries = kTries, int* tries_used = nullptr) {
     const uint32_t addr = pipe::smem_u32(bar);
-    for (int i = 0; i < kTries; ++i) {      // a try blocks for a while in hardware before it reports failure
+    for (int i = 0; i < tries; ++i) {       // a try blocks for a while in hardware before it reports failure
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -91,12 +92,43 @@ __device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, volat
             : "r"(addr), "r"(parity)
             : "memory");
         if (ok != 0) return true;
-        if ((i & 15) == 15 && *gave_up != 0) return false;     // looked at now and then: a poll is a shared-memory access
+        if ((i & 15) == 15 && *gave_up != 0) {                 // looked at now and then: a poll is a shared-memory access
+            if (tries_used != nullptr) *tries_used = i + 1;
+            return false;
+        }
         if constexpr (kBackoffNs > 0) __nanosleep(kBackoffNs);
     }
     *gave_up = 1;
     if (error_word != nullptr) atomicCAS(error_word, 0, (where << 8) | 1);
+    if (tries_used != nullptr) *tries_used = tries;
     return false;
+}
+
+// Probe of the give-up path of wait_phase (rh_selfcheck_role_wait): warp 0 waits with a limit of `tries` on a
+// barrier that nothing completes and must give up; warp 1 waits with the kernels' own limit on another such
+// barrier and must be released by warp 0's flag long before that limit.  out: [0] warp 0's wait returned true (0
+// expected), [1] the give-up flag, [2] the error word the probe recorded (a private word), [3] tries warp 1 used.
+__global__ void role_wait_probe_kernel(int tries, int* out) {
+    __shared__ uint64_t bars[2];
+    __shared__ int flag[2];
+    if (threadIdx.x == 0) {
+        pipe::mbar_init(&bars[0], 1);
+        pipe::mbar_init(&bars[1], 1);
+        flag[0] = 0;
+        pipe::mbar_init_fence();
+    }
+    __syncthreads();
+    volatile int* const gave_up = flag;
+    if (threadIdx.x < 32) {
+        const bool ok = wait_phase(&bars[0], 0, gave_up, __LINE__, out + 2, tries);
+        if (threadIdx.x == 0) out[0] = ok ? 1 : 0;
+    } else {
+        int used = 0;
+        (void)wait_phase(&bars[1], 0, gave_up, __LINE__, nullptr, kTries, &used);
+        if (threadIdx.x == 32) out[3] = used;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) out[1] = flag[0];
 }
 
 // Barrier among the `count` threads that use named barrier `id`, returning the OR of their predicates.
@@ -538,6 +570,23 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 1) flash_prefill_ws_ke
 }
 
 }  // namespace ws
+
+extern "C" int rh_selfcheck_role_wait(int tries, int* result_host) {
+    RH_REQUIRE(result_host != nullptr, RH_ERR_INVALID_ARG, "rh_selfcheck_role_wait: null pointer");
+    RH_REQUIRE(tries >= 16 && tries <= (1 << 16), RH_ERR_INVALID_ARG, "rh_selfcheck_role_wait: tries must be in 16..65536");
+    int* scratch = nullptr;
+    if (cudaMalloc(&scratch, 4 * sizeof(int)) != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selfcheck_role_wait: cudaMalloc failed");
+    cudaMemset(scratch, 0, 4 * sizeof(int));
+    ws::role_wait_probe_kernel<<<1, 64>>>(tries, scratch);
+    if (int e = host::check_launch("role_wait_probe_kernel")) {
+        cudaFree(scratch);
+        return e;
+    }
+    const cudaError_t err = cudaMemcpy(result_host, scratch, 4 * sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(scratch);
+    if (err != cudaSuccess) return host::fail(RH_ERR_CUDA, "rh_selfcheck_role_wait: %s", cudaGetErrorString(err));
+    return RH_OK;
+}
 
 // Launcher of the role-split forms; `a` is filled in by launch_flash_prefill_tc (tokens_per_cta per row block).
 // blocks: row blocks per CTA (the caller picks two once the one-block grid exceeds the SM count).

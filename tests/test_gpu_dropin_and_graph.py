@@ -88,6 +88,27 @@ def test_bounded_wait_gives_up_and_reports():
     assert float((x * 2).sum()) == 16.0                                            # context still usable
 
 
+def test_role_wait_gives_up_raises_the_flag_and_releases_the_other_role():
+    """The waits between the warp roles of the prefill attention kernel: a wait that nothing completes runs
+    out after its limit and raises the CTA-wide flag; another role, waiting with the kernel's own limit of 2^20
+    tries, is released by the flag at once; the kernel returns normally and the context keeps working."""
+    import ctypes as C
+    from runtherder_b200 import _lib
+    result = (C.c_int * 4)(-1, -1, -1, -1)
+    _lib.call("rh_selfcheck_role_wait", 64, result)
+    claimed, flag, err, other_tries = list(result)
+    assert claimed == 0 and flag == 1
+    assert err != 0 and (err & 0xff) == 1 and (err >> 8) > 0                       # (source line << 8) | code
+    assert 0 < other_tries < 4096                                                  # released by the flag, not by its own 2^20
+    after = C.c_int(-1)
+    _lib.call("rh_device_error", C.byref(after))
+    assert after.value == 0                                                        # the sticky word is not the probe's
+    with pytest.raises(_lib.RhError):
+        _lib.call("rh_selfcheck_role_wait", 8, result)
+    x = torch.ones(8, device="cuda")
+    assert float((x * 2).sum()) == 16.0                                            # context still usable
+
+
 def test_decode_glue_advances_positions_inside_a_graph():
     """rh_stage_positions == iota + decode_pos copy; rh_decode_advance captured at the end of a step makes
     every replay of the graph see the next position and the previously sampled token, with no host copy."""
