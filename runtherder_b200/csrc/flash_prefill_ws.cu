@@ -325,19 +325,14 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 1) flash_prefill_ws_ke
             l_a = fmaf(l_a, corr_a, sum_a.x + sum_a.y);
             l_b = fmaf(l_b, corr_b, sum_b.x + sum_b.y);
             const bool moved = j > 0 && __any_sync(0xffffffffu, corr_a != 1.0f || corr_b != 1.0f);
-            {
-                // W buffer j % 2 is free once O += W_{j-2} V_{j-2} has completed (long ago, as a rule); O may
-                // only be touched once O += W_{j-1} V_{j-1} has, which is waited for only when a maximum moved.
-                // Skipping a wait is safe for the parity test: no product of a later tile can complete before
-                // this warp has signalled "W ready" for it.
-                if (j > 1) {
-                    ok = wait_phase(&bb[kBarPV + (j & 1)], ((j - 2) >> 1) & 1, gave_up, __LINE__, p.error_word);
-                    if (!ok) break;
-                }
-                if (moved) {
-                    ok = wait_phase(&bb[kBarPV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
-                    if (!ok) break;
-                }
+            // W buffer j % 2 is free: O += W_{j-2} V_{j-2} was issued before S_j by the same thread, and the commit
+            // that completed the barrier of S_j covers every product issued before it.  O may only be touched
+            // once O += W_{j-1} V_{j-1} has completed, which is waited for only when a maximum moved.  Skipping
+            // that wait on other tiles is safe for the parity test: no product of a later tile can complete
+            // before this warp has signalled "W ready" for it.
+            if (moved) {
+                ok = wait_phase(&bb[kBarPV + ((j - 1) & 1)], ((j - 1) >> 1) & 1, gave_up, __LINE__, p.error_word);
+                if (!ok) break;
                 tc_fence_after();
             }
             tmem_st_frag_x4(tmem_w + (j & 1) * (kKeys / 2) + my_lanes16, wv);
