@@ -215,11 +215,33 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_p
 
     pdl_enter();
 
+    // ---- q first: its loads do not depend on the history length and are in flight while the key range is
+    //      worked out and the first tiles are requested.  The lane's dims are those of k_lane below: runs of
+    //      kKChunk dims, 4 kKChunk apart. ----
+    constexpr int kQVecs = D / 32;                        // 16-byte pieces of q per lane
+    constexpr int kQVecsPerRun = Ring::kKChunk / 8;
+    uint4 qraw[kQVecs];
+    {
+        const __nv_bfloat16* const src = p.q + static_cast<size_t>(col_valid ? qh : 0) * D + c * Ring::kKChunk;
+#pragma unroll
+        for (int v = 0; v < kQVecs; ++v) {
+            qraw[v] = make_uint4(0u, 0u, 0u, 0u);
+            if (col_valid) qraw[v] = *reinterpret_cast<const uint4*>(src + (v / kQVecsPerRun) * 4 * Ring::kKChunk + (v % kQVecsPerRun) * 8);
+        }
+    }
+
     // ---- key range of this split: whole tiles, dealt evenly ----
     const int n_keys = *p.cache_len + 1;
     const long long total_tiles = (static_cast<long long>(n_keys) + kFdTileKeys - 1) / kFdTileKeys;
-    const int tile_lo = static_cast<int>(total_tiles * split / p.num_splits);
-    const int tile_hi = static_cast<int>(total_tiles * (split + 1) / p.num_splits);
+    int tile_lo, tile_hi;
+    if (total_tiles * (p.num_splits + 1) < (1LL << 31)) {            // the usual case: 32-bit divisions
+        const unsigned tt = static_cast<unsigned>(total_tiles), ns = static_cast<unsigned>(p.num_splits);
+        tile_lo = static_cast<int>(tt * static_cast<unsigned>(split) / ns);
+        tile_hi = static_cast<int>(tt * static_cast<unsigned>(split + 1) / ns);
+    } else {
+        tile_lo = static_cast<int>(total_tiles * split / p.num_splits);
+        tile_hi = static_cast<int>(total_tiles * (split + 1) / p.num_splits);
+    }
     const int n_tiles = tile_hi - tile_lo;
     const int start = tile_lo * kFdTileKeys;
     const int end = min(tile_hi * kFdTileKeys, n_keys);
@@ -344,19 +366,15 @@ __global__ void __launch_bounds__(kFdThreads, (D <= 128 ? 2 : 1)) flash_decode_p
     uint32_t qb0[kKWords], qb1[kKWords];
     float factor0, factor1;   // scale * log2e * 2^e of the heads of columns 2c and 2c+1
     {
-        float qf[D / 4];
-        if (col_valid) {
-            const __nv_bfloat16* src = p.q + static_cast<size_t>(qh) * D + c * Ring::kKChunk;   // same dims as k_lane
+        float qf[D / 4];     // the lane's dims in order: element i sits in word i / 2 of the pieces loaded above
 #pragma unroll
-            for (int i = 0; i < D / 4; i += 2) {
-                const int dim = (i / Ring::kKChunk) * 4 * Ring::kKChunk + i % Ring::kKChunk;
-                const __nv_bfloat162 two = *reinterpret_cast<const __nv_bfloat162*>(src + dim);
-                qf[i] = __low2float(two);
-                qf[i + 1] = __high2float(two);
+        for (int v = 0; v < kQVecs; ++v) {
+            const uint32_t w[4] = {qraw[v].x, qraw[v].y, qraw[v].z, qraw[v].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                qf[8 * v + 2 * e] = bf_lo(w[e]);
+                qf[8 * v + 2 * e + 1] = bf_hi(w[e]);
             }
-        } else {
-#pragma unroll
-            for (int i = 0; i < D / 4; ++i) qf[i] = 0.0f;
         }
         float amax = 0.0f;
 #pragma unroll
