@@ -130,6 +130,49 @@ def test_flash_prefill_matches_exact_attention_and_reference(orc, ref, n_new, ca
     assert float(torch.dot(a, f) / (a.norm() * f.norm())) >= 0.998
 
 
+@pytest.mark.parametrize("parts", [0, 6, 5, 3, 2])
+def test_zero_rows_extreme_value_scales_and_an_all_zero_value_cache(orc, parts):
+    """Keys whose K or V row is all zero (scale 0), V rows of magnitude 1e-6 and 1e+4 side by side, a run of
+    small ones: the V scale lives in the weight's exponent and in the denominators' multiplier, and both must
+    stay exact; an all-zero value cache gives exact zeros, not NaN.  Default form, the role-split forms with
+    two and one row block, and the single-role forms."""
+    from runtherder_b200 import kernels as K
+    n_new, cache_len, Hq, Hkv, D = 150, 90, 8, 2, 128
+    g = torch.Generator(device="cuda").manual_seed(23)
+    n = cache_len + n_new
+    q = (torch.randn(n_new, Hq, D, device="cuda", generator=g) * 2.0).to(torch.bfloat16)
+    k = torch.randn(n, Hkv, D, device="cuda", generator=g)
+    v = torch.randn(n, Hkv, D, device="cuda", generator=g)
+    k[5] = 0.0
+    k[130] = 0.0
+    v[7] = 0.0
+    v[9] *= 1e-6
+    v[11] *= 1e4
+    v[100:120] *= 1e-3
+    v[200] = 0.0
+    at = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kc = torch.empty(n, Hkv, D, dtype=torch.uint8, device="cuda"); vc = torch.empty_like(kc)
+    ks = torch.empty(n, Hkv, dtype=torch.float32, device="cuda"); vs = torch.empty_like(ks)
+    K.quantize_kv_fp8(kc, ks, k.to(torch.bfloat16), at, 1, n * Hkv, D)
+    K.quantize_kv_fp8(vc, vs, v.to(torch.bfloat16), at, 1, n * Hkv, D)
+    assert float(ks[5].abs().max()) == 0.0 and float(vs[7].abs().max()) == 0.0
+    cl = torch.tensor([cache_len], dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(D)
+    exact_bits, exact = orc.attention_causal_fp8(to_np(q), to_np(kc), to_np(vc), to_np(ks), to_np(vs), cache_len, scale)
+    try:
+        K.tune("prefill_parts", parts)
+        out = torch.full((n_new, Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
+        K.flash_prefill_bf16(out, q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
+        torch.cuda.synchronize()
+        check(out, exact_bits, exact, f"prefill_parts={parts}")
+        vc.zero_(); vs.zero_()
+        K.flash_prefill_bf16(out, q, kc, vc, ks, vs, n_new, cl, Hq, Hkv, D, scale)
+        torch.cuda.synchronize()
+        assert float(out.float().abs().max()) == 0.0
+    finally:
+        K.tune("prefill_parts", 0)
+
+
 def test_prefill_then_decode_agree_on_the_last_token(orc):
     """The last token of a prefill is a decode step over the same cache: both entry points must land on the
     same exact value."""
