@@ -232,9 +232,11 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 1) flash_prefill_ws_ke
         for (int c = 0; c < 8; ++c)
             *reinterpret_cast<uint4*>(sm + q_off + part * (kRows * 128) + swz128(row, c)) = load_chunk(8 * part + c);
     }
+    // Q is in place for the product warps once the softmax warps have stored it; the conversion warps do not
+    // touch it and go straight to their first copies, which then overlap the loading of Q.
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    if (warp < G::kConvWarp0) named_sync(3, 32 * G::kConvWarp0);
     tc_fence_after();
 
     if (warp < G::kSoftmaxWarps) {
