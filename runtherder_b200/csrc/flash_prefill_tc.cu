@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
     const int head_slot = row / p.tokens_per_cta;
     const int tok = tok0 + (row - head_slot * p.tokens_per_cta);
     const int head_in_group = chunk * p.heads_per_cta + head_slot;
-    const bool row_valid = head_in_group < p.group && tok < p.n_new;
+    const bool row_valid = head_slot < p.heads_per_cta && head_in_group < p.group && tok < p.n_new;   // rows past the block's head slots idle
     const int qh = kvh * p.group + head_in_group;
 
     // ---- one-time set-up: barriers, tensor memory ----
@@ -454,7 +454,8 @@ __global__ void __launch_bounds__(128 * kParts, 2) flash_prefill_tc_kernel(const
             l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
             const float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
             const int hig_a = chunk * p.heads_per_cta + slot_a, hig_b = chunk * p.heads_per_cta + slot_b;
-            const bool valid_a = hig_a < p.group && tok_a < p.n_new, valid_b = hig_b < p.group && tok_b < p.n_new;
+            const bool valid_a = slot_a < p.heads_per_cta && hig_a < p.group && tok_a < p.n_new;
+            const bool valid_b = slot_b < p.heads_per_cta && hig_b < p.group && tok_b < p.n_new;
             __nv_bfloat16* const dst_a = p.out + (static_cast<size_t>(valid_a ? tok_a : 0) * p.num_q_heads + (valid_a ? kvh * p.group + hig_a : 0)) * kD + 2 * c2;
             __nv_bfloat16* const dst_b = p.out + (static_cast<size_t>(valid_b ? tok_b : 0) * p.num_q_heads + (valid_b ? kvh * p.group + hig_b : 0)) * kD + 2 * c2;
 #pragma unroll 1
@@ -531,9 +532,12 @@ int launch_flash_prefill_tc(void* out, const void* q, const uint8_t* k, const ui
     a.num_q_heads = num_q_heads;
     a.num_kv_heads = num_kv_heads;
     a.group = num_q_heads / num_kv_heads;
-    a.heads_per_cta = a.group >= 3 ? 4 : a.group;          // 3 heads ride in a 4-slot tile (one idle)
+    // The query heads of a kv head are dealt evenly over as few row blocks as hold them at four heads each
+    // (3 -> 3, 5 -> 3 + 2, 6 -> 3 + 3, 7 -> 4 + 3), and a block takes as many tokens as fit its 128 rows (three
+    // heads: 42 tokens, two rows idle), so no head slot of a block stays empty.
+    a.head_chunks = (a.group + 3) / 4;
+    a.heads_per_cta = (a.group + a.head_chunks - 1) / a.head_chunks;
     a.tokens_per_cta = tc::kRows / a.heads_per_cta;
-    a.head_chunks = (a.group + a.heads_per_cta - 1) / a.heads_per_cta;
     a.scale_log2e = scale * tc::kLog2e;
     const dim3 grid(static_cast<unsigned>((n_new + a.tokens_per_cta - 1) / a.tokens_per_cta),
                     static_cast<unsigned>(num_kv_heads * a.head_chunks));

@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 1) flash_prefill_ws_ke
         const int head_slot = row / p.tokens_per_cta;
         const int tok = tok0 + (row - head_slot * p.tokens_per_cta);
         const int head_in_group = chunk * p.heads_per_cta + head_slot;
-        const bool row_valid = head_in_group < p.group && tok < p.n_new;
+        const bool row_valid = head_slot < p.heads_per_cta && head_in_group < p.group && tok < p.n_new;   // rows past the block's head slots idle
         const int qh = kvh * p.group + head_in_group;
         const __nv_bfloat16* src = p.q + (static_cast<size_t>(row_valid ? tok : 0) * p.num_q_heads + (row_valid ? qh : 0)) * kD;
         auto load_chunk = [&](int cidx) {
@@ -372,7 +372,8 @@ __global__ void __launch_bounds__(Geo<kBlocks>::kThreads, 1) flash_prefill_ws_ke
             l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
             const float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
             const int hig_a = chunk * p.heads_per_cta + slot_a, hig_b = chunk * p.heads_per_cta + slot_b;
-            const bool valid_a = hig_a < p.group && tok_a < p.n_new, valid_b = hig_b < p.group && tok_b < p.n_new;
+            const bool valid_a = slot_a < p.heads_per_cta && hig_a < p.group && tok_a < p.n_new;
+            const bool valid_b = slot_b < p.heads_per_cta && hig_b < p.group && tok_b < p.n_new;
             __nv_bfloat16* const dst_a = p.out + (static_cast<size_t>(valid_a ? tok_a : 0) * p.num_q_heads + (valid_a ? kvh * p.group + hig_a : 0)) * kD + 2 * c2;
             __nv_bfloat16* const dst_b = p.out + (static_cast<size_t>(valid_b ? tok_b : 0) * p.num_q_heads + (valid_b ? kvh * p.group + hig_b : 0)) * kD + 2 * c2;
 #pragma unroll 1
