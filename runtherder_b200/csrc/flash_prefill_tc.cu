@@ -2,7 +2,7 @@
 // (tcgen05.mma, accumulators in tensor memory).  Same contract as flash_prefill.cu
 // (runtherder::kernels::flash_prefill_bf16, include/runtherder/kernels/flash_prefill.cuh:27-40).
 //
-// A CTA owns 128 query rows of one kv head — up to four query heads x 32 (64, 128) consecutive tokens —
+// A CTA owns 128 query rows of one kv head — four query heads x 32 consecutive tokens (three x 42, two x 64, one x 128) —
 // and walks the causal key tiles of 64 keys with 128 x kParts threads (kParts threads share a row: each
 // takes 64 / kParts keys of the row's scores and 128 / kParts columns of its output):
 //   raw E4M3 rows of the tile (cp.async, each thread its own chunks)
