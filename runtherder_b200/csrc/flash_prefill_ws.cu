@@ -7,8 +7,10 @@
 //
 // What differs is who does what.  In flash_prefill_tc.cu every thread walks through every phase of a tile
 // and the CTA meets at two barriers per tile, so the phases add up: switching any one of them off
-// (conversion, products, loads) shortens the kernel by that phase's share.  Here twelve warps take three roles
-// and hand tiles to one another through mbarriers, so that the phases of neighbouring tiles overlap:
+// (conversion, products, loads) shortens the kernel by that phase's share.  Here the warps take three roles
+// and hand tiles to one another through mbarriers, so that the phases of neighbouring tiles overlap (one row
+// block per CTA shown; with two, warps 0-15 are the softmax warps of blocks 0 and 1, warps 16-17 their product
+// warps and warps 18-21 the conversion warps, whose tiles both blocks share):
 //
 //   warps 0-7   softmax      wait S_j  -> load scores, release S -> scale, mask, maximum, weights
 //                            -> store W_j (two buffers) -> only if a row maximum moved: wait for
