@@ -97,6 +97,16 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def note_device_error(line):
+    """Reads the library's sticky device error word into the line; a kernel whose bounded wait gave up has
+    produced no valid result, so a non-zero word ends the run instead of reporting a number."""
+    from runtherder_b200 import kernels as Kn
+    word = Kn.device_error()
+    line["device_error"] = word
+    if word != 0:
+        raise SystemExit(f"bench: a kernel gave up a bounded wait (device error word {word:#x}, source line {word >> 8})")
+
+
 def sweep_config(cfg, world, rows_per_gpu):
     """The `config` object of the throughput-sweep line; both arms print the same one."""
     ops, per_row = step_bytes_per_row(cfg)
@@ -499,6 +509,7 @@ def main():
         del ins, outs
         torch.cuda.empty_cache()
         line["secondary"] = secondary_attention(args, dev)
+    note_device_error(line)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -682,6 +693,7 @@ def run_layer_chain(args, cfg, world, rank, dev, barrier, max_over_ranks):
             line["ref_cuda"] = time_reference_chain(cfg, ins, outs, rows, L, n_sets, total_bytes, use_graph, max(3, min(K, 20)), partial)
         except Exception as exc:
             line["ref_cuda"] = {"unavailable": str(exc)[:200]}
+    note_device_error(line)
     if rank == 0:
         print(json.dumps(line), flush=True)
 
@@ -785,6 +797,7 @@ def run_decode_attention(args, cfg, dev, emit=True):
                                     "sample": f"one call ({depth} keys, {Hq} heads) of the double-precision oracle, {dt:.2f} s"}
         except Exception as exc:
             line["cpu_baseline"] = {"unavailable": str(exc)[:200]}
+    note_device_error(line)
     if emit:
         print(json.dumps(line), flush=True)
     return line
@@ -893,6 +906,7 @@ def run_prefill_attention(args, cfg, dev, emit=True):
                                     "sample": f"the last {n_s} of {T} tokens through the double-precision oracle, {dt:.2f} s"}
         except Exception as exc:
             line["cpu_baseline"] = {"unavailable": str(exc)[:200]}
+    note_device_error(line)
     if emit:
         print(json.dumps(line), flush=True)
     return line

@@ -89,6 +89,15 @@ def rmsnorm_add_last_row(y_last, x, residual, g, num_tokens: int, hidden_dim: in
          _ptr(residual, _BF, n, "residual"), _ptr(g, _BF, hidden_dim, "g"), num_tokens, hidden_dim, eps, _stream(stream))
 
 
+def device_error() -> int:
+    """rh_device_error: the sticky per-device word a bounded wait records into when it gives up
+    ((source line << 8) | 1; 0 = no kernel has given up so far).  Synchronises the device."""
+    import ctypes
+    word = ctypes.c_int(-1)
+    call("rh_device_error", ctypes.byref(word))
+    return int(word.value)
+
+
 def init(device: int = 0) -> None:
     """rh_init: makes every kernel of the library resident and set up on `device`, so that even the first
     call of an entry point may be recorded into a CUDA graph."""
