@@ -147,6 +147,8 @@ int rh_flash_decode_split_bf16(void* out, const void* q, const uint8_t* k, const
  * head_dim must be 128 (as in the reference).  Operands narrow to f16 before the tensor-core
  * products as in the reference (q magnitudes must lie in f16's range); accumulation and softmax
  * are fp32.  Results are within one bf16 ulp of the exact value (tests/test_gpu_flash_prefill.py).
+ * The default form runs on tcgen05.mma (one CTA per SM holding 256 or all 512 of its tensor-memory columns for
+ * its lifetime; out 16-byte aligned); an out that is only 4-byte aligned takes an mma.sync form.
  * Replaces flash_prefill_bf16 (include/runtherder/kernels/flash_prefill.cuh:27-40,
  * src/kernels/flash_prefill.cu:213-241; called from src/attention/adaptive.cu:37-40). */
 int rh_flash_prefill_bf16(void* out, const void* q, const uint8_t* k, const uint8_t* v, const float* k_scale,
